@@ -1,0 +1,126 @@
+"""The oracle against the vectors produced by the reference's own eager model
+(tests/golden/make_golden.py), plus the documented tie / sentinel conventions."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import msa_oracle as O
+
+NAMES = ["dq_proxy", "dk_proxy", "dq", "dk", "dv"]
+SCALE = 128 ** -0.5
+
+
+def _inputs(cfg):
+    return O.make_inputs(cfg["b"], cfg["s"], cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"],
+                         seed=cfg["seed"])
+
+
+def _close(a, ref, tol):
+    ref = torch.as_tensor(ref)
+    err = (a.double() - ref.double()).abs().max().item()
+    bound = tol * max(1.0, ref.abs().max().item())
+    assert err <= bound, (err, bound)
+
+
+@pytest.mark.parametrize("kind", ["sparse", "warmup"])
+def test_closed_forms_match_reference_vectors(golden_dir, kind):
+    g = np.load(os.path.join(golden_dir, f"{kind}_small.npz"))
+    cfg = json.loads(str(g["config"]))
+    ins = _inputs(cfg)
+    np.testing.assert_allclose([float(t.double().sum()) for t in ins], g["input_checksum"], rtol=0, atol=1e-6)
+    qp, kp, q, k, v, do = ins
+    if kind == "sparse":
+        r = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 1.0)
+    else:
+        r = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 1.0)
+    _close(r["out"], g["out"], 2e-6)
+    _close(r["kl"], g["kl"], 2e-6)
+    for n in NAMES:
+        _close(r[n], g[n], 2e-6)
+
+
+@pytest.mark.parametrize("kind", ["sparse", "warmup"])
+def test_eager_restatement_matches_reference_vectors(golden_dir, kind):
+    g = np.load(os.path.join(golden_dir, f"{kind}_small.npz"))
+    cfg = json.loads(str(g["config"]))
+    qp, kp, q, k, v, do = _inputs(cfg)
+    if kind == "sparse":
+        fn = lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE)
+    else:
+        fn = lambda *t: O.eager_warmup(*t, SCALE)
+    out, kl, grads = O.eager_forward_backward(fn, (qp, kp, q, k, v), do, 1.0)
+    _close(out, g["out"], 1e-6)
+    _close(kl, g["kl"], 1e-6)
+    for n, gr in zip(NAMES, grads):
+        _close(gr, g[n], 1e-6)
+
+
+@pytest.mark.parametrize("kind", ["sparse", "warmup"])
+def test_config1_summary(golden_dir, kind):
+    with open(os.path.join(golden_dir, "c1_summary.json")) as f:
+        summ = json.load(f)
+    cfg = summ["config"]
+    qp, kp, q, k, v, do = _inputs(cfg)
+    if kind == "sparse":
+        r = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 1.0)
+    else:
+        r = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 1.0)
+    for name, s in summ[kind].items():
+        t = r[name].double().reshape(-1)
+        scale = max(1.0, max(abs(x) for x in s["sample"]))
+        got = t[torch.tensor(s["sample_idx"])] if t.numel() > 1 else t
+        assert (got - torch.tensor(s["sample"], dtype=torch.float64)).abs().max().item() <= 5e-6 * scale, name
+        assert abs(float(t.pow(2).sum().sqrt()) - s["l2"]) <= 1e-5 * max(1.0, s["l2"]), name
+
+
+def test_grad_kl_none_gives_zero_proxy_grads():
+    qp, kp, q, k, v, do = O.make_inputs(1, 256, 2, 1, 1, 1, seed=3)
+    r = O.sparse_forward_backward(qp, kp, q, k, v, 128, SCALE, do, None)
+    assert r["dq_proxy"].abs().max().item() == 0.0 and r["dk_proxy"].abs().max().item() == 0.0
+
+
+def test_stable_topk_lower_index_wins_and_sentinel():
+    nb = 6
+    sc = torch.full((1, 1, nb * 128, nb), float("-inf"))
+    # row in block 3: blocks 0..3 visible; scores tie between block 1 and 2
+    q = 3 * 128 + 5
+    sc[0, 0, q, :4] = torch.tensor([0.5, 1.0, 1.0, -2.0])
+    idx = O.stable_topk(sc, 3)
+    assert idx[0, 0, q].tolist() == [3, 1, 2]            # local first (+inf), then tie -> lower index
+    # row in block 0 has a single visible block: remaining slots are the sentinel NB
+    sc[0, 0, 7, 0] = 0.25
+    idx = O.stable_topk(sc, 3)
+    assert idx[0, 0, 7].tolist() == [0, nb, nb]
+
+
+def test_reverse_index_is_canonical():
+    qp, kp, *_ = O.make_inputs(2, 640, 4, 2, 4, 2, seed=5)
+    idx, _ = O.select_blocks(qp, kp, SCALE, 3)
+    nb = 5
+    row_ptr, col_q, edge_pos = O.reverse_index(idx, nb)
+    b, hp, s, kb = idx.shape
+    assert row_ptr[0].item() == 0 and row_ptr[-1].item() == col_q.numel()
+    seen = 0
+    for bp in range(b * hp):
+        for j in range(nb):
+            lo, hi = row_ptr[bp * nb + j].item(), row_ptr[bp * nb + j + 1].item()
+            qs = col_q[lo:hi]
+            assert (qs[1:] > qs[:-1]).all()                        # ascending, unique
+            assert (qs // 128 >= j).all()                          # causal
+            want = ((idx.view(b * hp, s, kb)[bp] == j).any(-1)).nonzero().squeeze(1)
+            assert torch.equal(qs.long(), want)
+            seen += hi - lo
+    assert seen == col_q.numel()
+    valid = edge_pos >= 0
+    assert valid.sum().item() == col_q.numel()
+    # edge_pos inverts col_q
+    qgrid = torch.arange(s).view(1, 1, s, 1).expand_as(idx)
+    assert torch.equal(col_q[edge_pos[valid].long()].long(), qgrid[valid])
+
+
+def test_flop_count_config2():
+    assert O.pairs_selected(8192, 16) == 14290944
+    assert abs(O.flops_sparse_fwd_bwd(2, 8192, 32, 16) - 1.639e12) < 1e9
