@@ -1,0 +1,69 @@
+"""ctypes binding of libflash_msa_b200.so.  There is no fallback: if the library is missing or a
+call is rejected, an exception is raised."""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+from ctypes import c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libflash_msa_b200.so")
+HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "flash_msa_b200.h")
+
+FMSA_OK = 0
+_ERRORS = {
+    -1: (ValueError, "invalid argument (shape, alignment or null pointer)"),
+    -2: (NotImplementedError, "request outside the implemented envelope"),
+    -3: (RuntimeError, "workspace too small"),
+    -4: (RuntimeError, "CUDA runtime refused the launch"),
+}
+
+
+class FmsaTensor(ctypes.Structure):
+    """Mirror of ``fmsa_tensor``: base pointer + element strides of a (B,H,S,128) bf16 tensor."""
+    _fields_ = [("ptr", c_void_p), ("stride_b", c_int64), ("stride_h", c_int64), ("stride_s", c_int64)]
+
+
+_lib = None
+
+
+def declared_symbols() -> list[str]:
+    """Entry points declared in include/flash_msa_b200.h."""
+    with open(HEADER_PATH) as f:
+        text = f.read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fmsa_[a-z0-9_]+)\s*\(", text)))
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m flash_msa_b200.build` "
+                "(flash_msa_b200 has no CPU or PyTorch fallback)")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(lib):
+    P = c_void_p
+    lib.fmsa_abi_version.restype = c_int
+    lib.fmsa_abi_version.argtypes = []
+    lib.fmsa_umma_selftest.restype = c_int
+    lib.fmsa_umma_selftest.argtypes = [P, P, P, c_int, c_int, c_int, P, P]
+    lib.fmsa_select_topk.restype = c_int
+    lib.fmsa_select_topk.argtypes = [P, P, c_int64, c_int32, c_int32, P]
+    lib.fmsa_reverse_index_workspace_bytes.restype = c_size_t
+    lib.fmsa_reverse_index_workspace_bytes.argtypes = [c_int64, c_int32]
+    lib.fmsa_reverse_index.restype = c_int
+    lib.fmsa_reverse_index.argtypes = [P, P, P, P, c_int64, c_int32, c_int32, P, c_size_t, P]
+
+
+def check(status: int, what: str) -> None:
+    if status == FMSA_OK:
+        return
+    exc, msg = _ERRORS.get(status, (RuntimeError, f"status {status}"))
+    raise exc(f"{what}: {msg}")

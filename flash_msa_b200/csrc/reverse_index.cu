@@ -1,0 +1,177 @@
+// Deterministic reverse index: a CSR that lists, for every (batch, proxy head, key block), the
+// query positions that selected that block, in ascending order.
+//
+// Four small kernels, no global atomics and no host synchronisation:
+//   1. count : one CTA per (batch*proxy head, query block) builds a shared-memory bitmap
+//              "row r selected key block j" and writes the per-(query block, key block) counts;
+//   2. colscan: one thread per (batch*proxy head, key block) turns the counts of its column into
+//              exclusive offsets over the query blocks and records the column total;
+//   3. rowscan: a single CTA turns the totals into row_ptr;
+//   4. fill  : the bitmap is rebuilt and every edge gets position
+//              row_ptr + block offset + (number of lower rows of its block that chose the key block).
+// The edge rule `0 <= kb < NB && kb <= q/128` is the reference's
+// (flash_msa/csrc/reverse_index_cuda.cu:41); its atomics-based slot assignment (:118) is replaced
+// by ranks, so the output is a pure function of the input.
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace fmsa {
+namespace {
+
+// Shared bitmap: words[j*4 + w] holds rows 32w..32w+31 of the query block for key block j.
+__device__ __forceinline__ void build_bitmap(uint32_t* words, const int32_t* idx_rows, int NB, int Kb, int qblk) {
+    for (int t = threadIdx.x; t < NB * 4; t += blockDim.x) words[t] = 0u;
+    __syncthreads();
+    const int r = threadIdx.x;   // 128 threads: one per row
+    const int32_t* row = idx_rows + static_cast<int64_t>(r) * Kb;
+    for (int s = 0; s < Kb; ++s) {
+        const int j = row[s];
+        if (static_cast<unsigned>(j) < static_cast<unsigned>(NB) && j <= qblk) atomicOr(&words[j * 4 + (r >> 5)], 1u << (r & 31));
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(128) rix_count_kernel(const int32_t* __restrict__ idx, uint8_t* __restrict__ counts,
+                                                        int S, int NB, int Kb) {
+    extern __shared__ uint32_t words[];
+    const int qblk = blockIdx.x;
+    const int64_t bp = blockIdx.y;
+    build_bitmap(words, idx + (bp * S + static_cast<int64_t>(qblk) * kBlock) * Kb, NB, Kb, qblk);
+    uint8_t* crow = counts + (bp * NB + qblk) * NB;
+    for (int j = threadIdx.x; j <= qblk; j += blockDim.x) {
+        const int c = __popc(words[j * 4]) + __popc(words[j * 4 + 1]) + __popc(words[j * 4 + 2]) + __popc(words[j * 4 + 3]);
+        crow[j] = static_cast<uint8_t>(c);   // <= 128
+    }
+}
+
+__global__ void rix_colscan_kernel(const uint8_t* __restrict__ counts, int32_t* __restrict__ blk_off,
+                                   int32_t* __restrict__ totals, int64_t rows_bh, int NB) {
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= rows_bh * NB) return;
+    const int64_t bp = t / NB;
+    const int j = static_cast<int>(t % NB);
+    int run = 0;
+    for (int i = j; i < NB; ++i) {
+        const int64_t at = (bp * NB + i) * NB + j;
+        blk_off[at] = run;
+        run += counts[at];
+    }
+    totals[t] = run;
+}
+
+__global__ void __launch_bounds__(1024) rix_rowscan_kernel(const int32_t* __restrict__ totals,
+                                                           int32_t* __restrict__ row_ptr, int64_t n) {
+    __shared__ int64_t part[1024];
+    const int tid = threadIdx.x;
+    const int64_t per = (n + 1023) / 1024;
+    const int64_t lo = tid * per, hi = (lo + per < n) ? lo + per : n;
+    int64_t sum = 0;
+    for (int64_t i = lo; i < hi; ++i) sum += totals[i];
+    part[tid] = sum;
+    __syncthreads();
+    // Hillis-Steele inclusive scan over 1024 partials
+    for (int off = 1; off < 1024; off <<= 1) {
+        const int64_t v = (tid >= off) ? part[tid - off] : 0;
+        __syncthreads();
+        part[tid] += v;
+        __syncthreads();
+    }
+    int64_t run = part[tid] - sum;
+    for (int64_t i = lo; i < hi; ++i) {
+        row_ptr[i] = static_cast<int32_t>(run);
+        run += totals[i];
+    }
+    if (tid == 1023) row_ptr[n] = static_cast<int32_t>(part[1023]);
+}
+
+__global__ void __launch_bounds__(128) rix_fill_kernel(const int32_t* __restrict__ idx, const int32_t* __restrict__ blk_off,
+                                                       const int32_t* __restrict__ row_ptr, int32_t* __restrict__ col_q,
+                                                       int32_t* __restrict__ edge_pos, int S, int NB, int Kb) {
+    extern __shared__ uint32_t words[];
+    const int qblk = blockIdx.x;
+    const int64_t bp = blockIdx.y;
+    const int64_t row0 = bp * S + static_cast<int64_t>(qblk) * kBlock;
+    build_bitmap(words, idx + row0 * Kb, NB, Kb, qblk);
+    const int r = threadIdx.x;
+    const int q = qblk * kBlock + r;
+    const int32_t* row = idx + (row0 + r) * Kb;
+    int32_t* erow = edge_pos + (row0 + r) * Kb;
+    const int w = r >> 5;
+    const uint32_t below = (1u << (r & 31)) - 1u;
+    for (int s = 0; s < Kb; ++s) {
+        const int j = row[s];
+        int pos = -1;
+        if (static_cast<unsigned>(j) < static_cast<unsigned>(NB) && j <= qblk) {
+            int rank = __popc(words[j * 4 + w] & below);
+            for (int ww = 0; ww < w; ++ww) rank += __popc(words[j * 4 + ww]);
+            pos = row_ptr[bp * NB + j] + blk_off[(bp * NB + qblk) * NB + j] + rank;
+            col_q[pos] = q;
+        }
+        erow[s] = pos;
+    }
+}
+
+struct RixWorkspace {
+    uint8_t* counts;
+    int32_t* blk_off;
+    int32_t* totals;
+    size_t bytes;
+};
+
+RixWorkspace carve(void* base, int64_t rows_bh, int NB) {
+    RixWorkspace w;
+    const size_t n2 = static_cast<size_t>(rows_bh) * NB * NB;
+    size_t off = 0;
+    w.counts = reinterpret_cast<uint8_t*>(static_cast<char*>(base) + off);
+    off += static_cast<size_t>(round_up(static_cast<int64_t>(n2), 256));
+    w.blk_off = reinterpret_cast<int32_t*>(static_cast<char*>(base) + off);
+    off += static_cast<size_t>(round_up(static_cast<int64_t>(n2 * 4), 256));
+    w.totals = reinterpret_cast<int32_t*>(static_cast<char*>(base) + off);
+    off += static_cast<size_t>(round_up(static_cast<int64_t>(rows_bh) * NB * 4, 256));
+    w.bytes = off;
+    return w;
+}
+
+}  // namespace
+
+// Launch sequence shared with any other entry point that supplies its own scratch memory.
+int reverse_index_launch(const int32_t* block_indices, int32_t* row_ptr, int32_t* col_q, int32_t* edge_pos,
+                         int64_t rows_bh, int32_t S, int32_t Kb, void* scratch, cudaStream_t st) {
+    const int NB = S / kBlock;
+    const RixWorkspace w = carve(scratch, rows_bh, NB);
+    const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(rows_bh));
+    const size_t smem = static_cast<size_t>(NB) * 16;
+    rix_count_kernel<<<grid, 128, smem, st>>>(block_indices, w.counts, S, NB, Kb);
+    const int64_t cols = rows_bh * NB;
+    rix_colscan_kernel<<<static_cast<unsigned>((cols + 127) / 128), 128, 0, st>>>(w.counts, w.blk_off, w.totals, rows_bh, NB);
+    rix_rowscan_kernel<<<1, 1024, 0, st>>>(w.totals, row_ptr, cols);
+    rix_fill_kernel<<<grid, 128, smem, st>>>(block_indices, w.blk_off, row_ptr, col_q, edge_pos, S, NB, Kb);
+    return check_launch();
+}
+
+size_t reverse_index_scratch_bytes(int64_t rows_bh, int32_t S) {
+    return carve(nullptr, rows_bh, S / kBlock).bytes;
+}
+
+}  // namespace fmsa
+
+extern "C" size_t fmsa_reverse_index_workspace_bytes(int64_t rows_bh, int32_t S) {
+    if (rows_bh <= 0 || S <= 0 || S % fmsa::kBlock != 0) return 0;
+    return fmsa::reverse_index_scratch_bytes(rows_bh, S);
+}
+
+extern "C" int fmsa_reverse_index(const int32_t* block_indices, int32_t* row_ptr, int32_t* col_q, int32_t* edge_pos,
+                                  int64_t rows_bh, int32_t S, int32_t top_k_blocks, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(block_indices && row_ptr && col_q && edge_pos && workspace);
+    FMSA_REQUIRE(rows_bh > 0 && rows_bh <= 65535 && S > 0 && S % kBlock == 0);
+    const int NB = S / kBlock;
+    FMSA_REQUIRE(top_k_blocks >= 1 && top_k_blocks <= NB);
+    FMSA_REQUIRE(rows_bh * static_cast<int64_t>(S) * top_k_blocks < 0x7fffffffLL);
+    if (NB > 2048) return FMSA_ERR_UNSUPPORTED;   // bitmap must fit in shared memory (NB*16 bytes)
+    FMSA_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0);
+    if (workspace_bytes < reverse_index_scratch_bytes(rows_bh, S)) return FMSA_ERR_WORKSPACE;
+    return reverse_index_launch(block_indices, row_ptr, col_q, edge_pos, rows_bh, S, top_k_blocks, workspace,
+                                static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,263 @@
+// Blackwell (sm_100a) device primitives shared by every tensor-core kernel of the library:
+// mbarriers with bounded waits, tensor-memory (TMEM) allocation, tcgen05.mma issue with
+// shared-memory matrix descriptors, TMEM loads, cp.async row gathers into the 128-byte
+// swizzled operand layout, and TMA tile loads.
+//
+// Operand tile convention used everywhere: a tile is 128 rows x 128 bf16 columns, stored as two
+// "panels" of 64 columns.  Panel p starts at byte p*16384; row r of a panel starts at r*128;
+// the 16-byte chunk c (0..7) of that row sits at chunk position c ^ (r & 7)  (the SWIZZLE_128B
+// pattern, tile base 1024-byte aligned).  The same bytes serve
+//   * as a K-major operand   (rows = M or N index, columns = reduction index), and
+//   * as an MN-major operand (rows = reduction index, columns = M or N index),
+// which is what lets one gathered Q tile feed both S = Q K^T and dK = dS^T Q.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fmsa {
+
+constexpr int kBlock = 128;              // tokens per key / query block
+constexpr int kHeadDim = 128;            // head dimension (fixed by the reference: flash_msa.py:54-55)
+constexpr int kTileBytes = 128 * 128 * 2;
+constexpr int kPanelBytes = 128 * 64 * 2;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Status words written by kernels into the caller's status buffer (0 = ok).
+constexpr int kStatusWaitTimeout = 1;    // a bounded mbarrier wait gave up
+constexpr int kStatusBadIndex = 2;       // an index read from metadata was out of range
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// mbarrier
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about two seconds of wall time and returns false.  Callers vote
+// on the result with a block-wide barrier so that the whole CTA leaves together.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (global_timer_ns() - t0 > 2000000000ull) return false;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// proxy / tcgen05 fences
+// ---------------------------------------------------------------------------------------------
+// Makes shared-memory writes done with ordinary stores or cp.async visible to the async proxy
+// (tcgen05.mma and TMA read shared memory through it).
+__device__ __forceinline__ void fence_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// TMEM allocation (one full warp executes these)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05.mma (kind::f16: bf16 x bf16 -> fp32 in TMEM), M = 128, one CTA
+// ---------------------------------------------------------------------------------------------
+// Instruction descriptor: D fp32, A/B bf16, M = 128, N = n; a_mn / b_mn select MN-major operands.
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool a_mn, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+// Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Descriptor of reduction step `ks` (16 reduction elements each, 8 steps per 128) of a tile used
+// K-major (rows are the M/N index).  Eight-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int ks) {
+    return umma_desc(tile + (ks >> 2) * kPanelBytes + (ks & 3) * 32, 16, 1024);
+}
+// Same tile used MN-major (rows are the reduction index): a step is 16 rows = 2048 bytes; the two
+// 64-column halves of the M/N extent are one panel (16384 bytes) apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int ks) {
+    return umma_desc(tile + ks * 2048, kPanelBytes, 1024);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// One full 128x128x128 product D (+)= A * B^T issued by the calling thread (8 instructions).
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void umma_tile_128(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, bool accumulate) {
+    constexpr uint32_t idesc = umma_idesc(128, A_MN, B_MN);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t ad = A_MN ? desc_mnmajor(a_tile, ks) : desc_kmajor(a_tile, ks);
+        const uint64_t bd = B_MN ? desc_mnmajor(b_tile, ks) : desc_kmajor(b_tile, ks);
+        umma_bf16(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// TMEM loads: warp w of a warpgroup reads lanes 32*(w%4)..+31; thread i gets lane 32*(w%4)+i
+// and 32 consecutive fp32 columns.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// TMEM address of (lane quarter of this warp, column).
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp_in_group, int col) {
+    return base + (static_cast<uint32_t>(warp_in_group * 32) << 16) + static_cast<uint32_t>(col);
+}
+
+// ---------------------------------------------------------------------------------------------
+// cp.async row gather into a swizzled tile
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;   // src-size 0 writes 16 zero bytes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint32_t swz_offset(int row, int chunk16) {
+    // chunk16: 16-byte chunk index 0..15 within the 256-byte row
+    return static_cast<uint32_t>((chunk16 >> 3) * kPanelBytes + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4));
+}
+
+// Every thread of the CTA calls this.  Row r of the tile is copied from `base + rows[r]*stride`
+// (elements); a negative row id produces a row of zeros.  `rows` may live in shared memory.
+template <int NTHREADS>
+__device__ __forceinline__ void gather_tile_async(uint32_t tile, const __nv_bfloat16* base, int64_t stride,
+                                                  const int* rows, int tid) {
+#pragma unroll 4
+    for (int it = tid; it < 128 * 16; it += NTHREADS) {
+        const int r = it >> 4, c16 = it & 15;
+        const int row = rows[r];
+        const bool ok = row >= 0;
+        const __nv_bfloat16* src = base + static_cast<int64_t>(ok ? row : 0) * stride + c16 * 8;
+        cp_async_16(tile + swz_offset(r, c16), src, ok);
+    }
+}
+// Contiguous variant: tile row r comes from `base + (row0 + r)*stride`.
+template <int NTHREADS>
+__device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat16* base, int64_t stride, int tid) {
+#pragma unroll 4
+    for (int it = tid; it < 128 * 16; it += NTHREADS) {
+        const int r = it >> 4, c16 = it & 15;
+        cp_async_16(tile + swz_offset(r, c16), base + static_cast<int64_t>(r) * stride + c16 * 8, true);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// TMA: 2-D tile load (64 columns x 128 rows box, SWIZZLE_128B) signalled on an mbarrier
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// small math helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+}  // namespace fmsa

@@ -1,0 +1,81 @@
+/* C ABI of libflash_msa_b200.so: hand-written sm_100a kernels for the Flash-MSA training path.
+ *
+ * Conventions
+ *  - Every entry point returns an int status: FMSA_OK, or a negative FMSA_ERR_* for a rejected
+ *    call (nothing was launched).  Kernels report device-side trouble (a bounded wait that ran
+ *    out, an out-of-range index in metadata) in a caller-provided int32 status word on the
+ *    device, never by trapping.
+ *  - All pointers are device pointers unless stated otherwise.  The library never allocates or
+ *    frees device memory; the caller owns every buffer, including workspaces whose size the
+ *    *_workspace_bytes functions report.
+ *  - Launches go to the given stream and never synchronise with the host.
+ *  - Activations are bf16 with head dimension 128 and 128-token blocks.  A 4-D activation
+ *    (B, H, S, 128) is described by its base pointer and element strides for B, H and S; the
+ *    last dimension must be contiguous and rows 16-byte aligned.
+ *
+ * File:line citations refer to the reference project nanduruganesh/flash-msa.
+ */
+#ifndef FLASH_MSA_B200_H
+#define FLASH_MSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FMSA_OK 0
+#define FMSA_ERR_ARGUMENT (-1)    /* shape / alignment / null pointer */
+#define FMSA_ERR_UNSUPPORTED (-2) /* valid request outside the implemented envelope */
+#define FMSA_ERR_WORKSPACE (-3)   /* workspace too small */
+#define FMSA_ERR_CUDA (-4)        /* the CUDA runtime refused the launch */
+
+#define FMSA_MAX_TOPK_BLOCKS 128
+
+/* Strided (B, H, S, 128) bf16 activation. */
+typedef struct {
+    const void* ptr;
+    int64_t stride_b, stride_h, stride_s; /* in elements */
+} fmsa_tensor;
+
+/* Library ABI version (bumped on any signature change). */
+int fmsa_abi_version(void);
+
+/* Test hook: one 128x128x128 tcgen05 product D = A_eff * B_eff^T computed exactly the way the
+ * attention kernels do it (cp.async or TMA staging into the swizzled tile layout, one TMEM
+ * accumulator, tcgen05.ld read-back).  a/b: row-major [128][128] bf16; d: [128][128] fp32.
+ * a_mn / b_mn = 1 uses the stored matrix transposed (MN-major operand).  use_tma = 1 stages A
+ * and B with cp.async.bulk.tensor instead of cp.async.  status: int32[1].
+ * No counterpart in the reference (its kernels use warp-level mma.sync). */
+int fmsa_umma_selftest(const void* a, const void* b, float* d, int a_mn, int b_mn, int use_tma, int* status,
+                       void* stream);
+
+/* Per-row top-k over materialised block scores.
+ * Replaces the running top-k of the reference select kernel
+ * (flash_msa/msa_select_cutedsl.py:310-329, 370-392): total order (score descending, block
+ * index ascending), the row's own block forced first, slots without a causally valid block set
+ * to the sentinel NB.
+ *   block_scores  fp32 [rows_bh, S, NB]   (rows_bh = B*Hp; entries with block > q/128 are ignored)
+ *   block_indices int32 [rows_bh, S, Kb]
+ * Kb <= FMSA_MAX_TOPK_BLOCKS. */
+int fmsa_select_topk(const float* block_scores, int32_t* block_indices, int64_t rows_bh, int32_t S,
+                     int32_t top_k_blocks, void* stream);
+
+/* Deterministic reverse index (CSR) of the selection.
+ * Replaces build_reverse_index_cuda / build_sparse_attention_metadata_cuda
+ * (flash_msa/reverse_index_cuda.py:139-270; flash_msa/csrc/reverse_index_cuda.cu:19-233):
+ * an entry (q, slot) is an edge iff 0 <= kb < NB and kb <= q/128 (reverse_index_cuda.cu:41).
+ *   row_ptr  int32 [rows_bh*NB + 1]   CSR row (bp*NB + kb) lists the queries that chose kb
+ *   col_q    int32 [rows_bh*S*Kb]     query positions, ascending inside a row; first row_ptr[last] used
+ *   edge_pos int32 [rows_bh, S, Kb]   CSR position of each slot, -1 when the slot is not an edge
+ * Unlike the reference no host synchronisation happens and the order inside a row is fixed. */
+size_t fmsa_reverse_index_workspace_bytes(int64_t rows_bh, int32_t S);
+int fmsa_reverse_index(const int32_t* block_indices, int32_t* row_ptr, int32_t* col_q, int32_t* edge_pos,
+                       int64_t rows_bh, int32_t S, int32_t top_k_blocks, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_MSA_B200_H */
