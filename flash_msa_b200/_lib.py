@@ -60,6 +60,22 @@ def _declare(lib):
     lib.fmsa_reverse_index_workspace_bytes.argtypes = [c_int64, c_int32]
     lib.fmsa_reverse_index.restype = c_int
     lib.fmsa_reverse_index.argtypes = [P, P, P, P, c_int64, c_int32, c_int32, P, c_size_t, P]
+    T = ctypes.POINTER(FmsaTensor)
+    PB = ctypes.POINTER(FmsaProblem)
+    lib.fmsa_select_scores.restype = c_int
+    lib.fmsa_select_scores.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P]
+    lib.fmsa_fwd_partial_slots.restype = c_int64
+    lib.fmsa_fwd_partial_slots.argtypes = [PB, c_int32, c_int32]
+    lib.fmsa_sparse_fwd.restype = c_int
+    lib.fmsa_sparse_fwd.argtypes = [PB, T, T, T, T, T, P, P, P, P, c_int64, c_int32, c_int32, c_int32, c_int32, P, P, P]
+    lib.fmsa_sparse_fwd_combine.restype = c_int
+    lib.fmsa_sparse_fwd_combine.argtypes = [PB, P, P, P, P, P, P, P, c_int32, c_int32, c_int32, P]
+
+
+class FmsaProblem(ctypes.Structure):
+    """Mirror of ``fmsa_problem``."""
+    _fields_ = [("B", c_int32), ("S", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("Hp", c_int32),
+                ("Hpkv", c_int32), ("top_k_blocks", c_int32), ("scale", c_float)]
 
 
 def check(status: int, what: str) -> None:

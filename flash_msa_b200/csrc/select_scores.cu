@@ -1,0 +1,162 @@
+// Proxy block scores: the tensor-core half of block selection.
+//
+// For every (batch, proxy head, query row q) and every causally visible key block j <= q/128
+//     block_scores[q][j] = max over visible keys k of block j of  scale * Qp[q] . Kp[k]
+// (flash_msa/tests/testing_model.py:75-88; the reference kernel computes the same maxima inside
+// msa_select_cutedsl.py:238-306 but rounds each score to bf16 first, which this kernel does not).
+// Entries with j > q/128 are left untouched; the top-k kernel never reads them.
+//
+// One CTA owns a 128-row query tile of one (batch, proxy head) and walks the key blocks 0..i.
+// Warp-specialised: warp 0 feeds K tiles by TMA through a two-stage ring, warp 1 issues
+// tcgen05.mma into one of two TMEM accumulators, warps 2-5 read an accumulator back (one row per
+// thread), take the masked row maximum and stage it in shared memory so that global stores are
+// row-contiguous.
+#include "host_common.h"
+#include "sm100.cuh"
+#include "tma_host.h"
+
+namespace fmsa {
+namespace {
+
+constexpr int kScoreStageCols = 16;   // key blocks staged per flush
+
+struct ScoreSmem {
+    uint64_t q_full, k_full[2], k_empty[2], s_full[2], s_empty[2];
+    uint32_t tmem_slot;
+    float stage[128][kScoreStageCols + 1];
+};
+
+__global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                            const __grid_constant__ CUtensorMap tmap_k,
+                                                            float* __restrict__ block_scores, int Hp, int pg, int S,
+                                                            int NB, float scale, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tile_q = tiles, tile_k0 = tiles + kTileBytes;
+    ScoreSmem* sm = reinterpret_cast<ScoreSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 3 * kTileBytes);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = NB - 1 - static_cast<int>(blockIdx.x);   // longest tiles first
+    const int bp = blockIdx.y;
+    const int b = bp / Hp, p = bp % Hp, kph = p / pg;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(&sm->q_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&sm->k_full[i]), 1);
+            mbar_init(smem_u32(&sm->k_empty[i]), 1);
+            mbar_init(smem_u32(&sm->s_full[i]), 1);
+            mbar_init(smem_u32(&sm->s_empty[i]), 128);
+        }
+        fence_mbar_init();
+        prefetch_tmap(&tmap_q);
+        prefetch_tmap(&tmap_k);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&sm->tmem_slot), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm->tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(smem_u32(&sm->q_full), kTileBytes);
+            tma_load_tile(tile_q, &tmap_q, qt * kBlock, p, b, smem_u32(&sm->q_full));
+            for (int j = 0; j <= qt && ok; ++j) {
+                const int st = j & 1;
+                if (j >= 2) ok = mbar_wait(smem_u32(&sm->k_empty[st]), ((j >> 1) - 1) & 1);
+                if (!ok) break;
+                mbar_arrive_expect_tx(smem_u32(&sm->k_full[st]), kTileBytes);
+                tma_load_tile(tile_k0 + st * kTileBytes, &tmap_k, j * kBlock, kph, b, smem_u32(&sm->k_full[st]));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            ok = mbar_wait(smem_u32(&sm->q_full), 0);
+            for (int j = 0; j <= qt && ok; ++j) {
+                const int st = j & 1;
+                ok = mbar_wait(smem_u32(&sm->k_full[st]), (j >> 1) & 1);
+                if (ok && j >= 2) ok = mbar_wait(smem_u32(&sm->s_empty[st]), ((j >> 1) - 1) & 1);
+                if (!ok) break;
+                tc_fence_after_sync();
+                umma_tile_128<false, false>(tmem + st * 128, tile_q, tile_k0 + st * kTileBytes, false);
+                umma_commit(smem_u32(&sm->k_empty[st]));
+                umma_commit(smem_u32(&sm->s_full[st]));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;            // TMEM lane quarter this warp may read
+        const int r = quarter * 32 + lane;        // row of the query tile
+        for (int j = 0; j <= qt; ++j) {
+            const int st = j & 1;
+            ok = mbar_wait(smem_u32(&sm->s_full[st]), (j >> 1) & 1);
+            if (!ok) break;   // every lane of the warp waits on the same phase: uniform
+            tc_fence_after_sync();
+            float m = -INFINITY;
+            const int limit = (j == qt) ? r : 127;   // last visible key column of this row
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_addr(tmem + st * 128, quarter, c), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float x = __uint_as_float(v[i]) * scale;
+                    m = (c + i <= limit) ? fmaxf(m, x) : m;
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&sm->s_empty[st]));
+            sm->stage[r][j % kScoreStageCols] = m;
+            if ((j % kScoreStageCols) == kScoreStageCols - 1 || j == qt) {
+                __syncwarp();
+                const int j0 = j - (j % kScoreStageCols);
+                const int ncol = j - j0 + 1;
+                // the warp owns rows quarter*32 .. +31 of the stage: write them row-contiguously
+                for (int e = lane; e < 32 * kScoreStageCols; e += 32) {
+                    const int rr = e / kScoreStageCols, cc = e % kScoreStageCols;
+                    if (cc < ncol) {
+                        float* orow = block_scores + (static_cast<int64_t>(bp) * S + qt * kBlock + quarter * 32 + rr) * NB;
+                        orow[j0 + cc] = sm->stage[quarter * 32 + rr][cc];
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+    if (!ok) atomicMax(status, kStatusWaitTimeout);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace
+}  // namespace fmsa
+
+extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores,
+                                  int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t* status,
+                                  void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && block_scores && status);
+    FMSA_REQUIRE(B > 0 && Hp > 0 && Hpkv > 0 && Hp % Hpkv == 0 && S > 0 && S % kBlock == 0);
+    FMSA_REQUIRE(static_cast<int64_t>(B) * Hp <= 65535);
+    FMSA_REQUIRE(tma_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
+    FMSA_REQUIRE(tma_compatible(k_proxy->ptr, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s));
+    CUtensorMap tq, tk;
+    if (!make_tmap_bhsd(&tq, q_proxy->ptr, B, Hp, S, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s, 128) ||
+        !make_tmap_bhsd(&tk, k_proxy->ptr, B, Hpkv, S, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s, 128))
+        return FMSA_ERR_CUDA;
+    const int NB = S / kBlock;
+    const size_t smem = 3 * kTileBytes + 1024 + sizeof(ScoreSmem);
+    if (cudaFuncSetAttribute(select_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+        return FMSA_ERR_CUDA;
+    const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(B * Hp));
+    select_scores_kernel<<<grid, 192, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB,
+                                                                                scale, status);
+    return check_launch();
+}

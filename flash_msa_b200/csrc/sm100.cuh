@@ -239,6 +239,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
         : "memory");
 }
 
+// 4-D variant for (B, H, S, 128) activations: coordinates {column, s, h, b}.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int x, int s, int h, int b, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(s), "r"(h), "r"(b), "r"(bar)
+        : "memory");
+}
+// Loads the 128-row tile starting at sequence position s0 of (b, h) as two 64-column panels.
+// The caller has already posted expect_tx(kTileBytes) on `bar`.
+__device__ __forceinline__ void tma_load_tile(uint32_t tile, const void* tmap, int s0, int h, int b, uint32_t bar) {
+    tma_load_4d(tile, tmap, 0, s0, h, b, bar);
+    tma_load_4d(tile + kPanelBytes, tmap, 64, s0, h, b, bar);
+}
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // small math helpers
 // ---------------------------------------------------------------------------------------------

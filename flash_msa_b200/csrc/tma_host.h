@@ -39,4 +39,27 @@ inline bool make_tmap_rows(CUtensorMap* map, const void* base, uint64_t rows, ui
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Strided (B, H, S, 128) bf16 activation as a 4-D map {128, S, H, B}; element strides as in
+// fmsa_tensor.  Box = 64 columns x `box_rows` sequence positions of one (batch, head).
+inline bool make_tmap_bhsd(CUtensorMap* map, const void* base, uint64_t B, uint64_t H, uint64_t S, int64_t stride_b,
+                           int64_t stride_h, int64_t stride_s, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {128, S, H, B};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(stride_s) * 2, static_cast<cuuint64_t>(stride_h) * 2,
+                                   static_cast<cuuint64_t>(stride_b) * 2};
+    const cuuint32_t box[4] = {64, box_rows, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A TMA-loadable activation: last dimension contiguous, every stride a multiple of 8 elements
+// (16 bytes), base 16-byte aligned.
+inline bool tma_compatible(const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0 && ss >= 128 &&
+           sb > 0 && sh > 0;
+}
+
 }  // namespace fmsa

@@ -4,9 +4,13 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import ctypes
+
 import torch
 
 from . import _lib
+
+ctypes_byref = ctypes.byref
 
 BLOCK_SIZE = 128
 
@@ -84,3 +88,107 @@ def build_reverse_index(block_indices: torch.Tensor) -> ReverseIndex:
                                       edge_pos.data_ptr(), b * hp, s, kb, ws.data_ptr(), ws_bytes, _stream(dev)),
                "fmsa_reverse_index")
     return ReverseIndex(row_ptr, col_q, edge_pos, b, hp, s, kb)
+
+
+# ----------------------------------------------------------------------------------------------
+# tensor-core kernels
+# ----------------------------------------------------------------------------------------------
+
+def _as_kernel_input(t: torch.Tensor) -> torch.Tensor:
+    """Kernels read (B,H,S,128) bf16 with a contiguous last dimension and 16-byte aligned rows;
+    anything else (for instance an odd storage offset) is copied once."""
+    ok = (t.stride(3) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.stride(2) % 8 == 0
+          and t.stride(2) >= 128 and t.data_ptr() % 16 == 0 and t.stride(0) > 0 and t.stride(1) > 0)
+    return t if ok else t.contiguous()
+
+
+def _tensor_arg(t: torch.Tensor) -> "_lib.FmsaTensor":
+    return _lib.FmsaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _problem(q, k, q_proxy, k_proxy, top_k_blocks, scale) -> "_lib.FmsaProblem":
+    b, hq, s, _ = q.shape
+    return _lib.FmsaProblem(b, s, hq, k.shape[1], q_proxy.shape[1], k_proxy.shape[1], int(top_k_blocks), float(scale))
+
+
+def check_status(status: torch.Tensor, what: str) -> None:
+    """Reads the device status word (synchronises).  Used by tests and debug mode only."""
+    code = int(status.item())
+    if code != 0:
+        names = {1: "a bounded device-side wait timed out", 2: "an out-of-range index was found in metadata"}
+        raise RuntimeError(f"{what}: {names.get(code, code)}")
+
+
+def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, status=None) -> torch.Tensor:
+    """fp32 block scores [B,Hp,S,NB]; entries of future blocks are left unwritten."""
+    _require_cuda(q_proxy, k_proxy)
+    if q_proxy.dtype != torch.bfloat16 or k_proxy.dtype != torch.bfloat16:
+        raise TypeError(f"flash_msa_b200 supports bf16 activations, got {q_proxy.dtype}")
+    b, hp, s, d = q_proxy.shape
+    qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
+    dev = qp.device
+    scores = torch.empty(b, hp, s, s // BLOCK_SIZE, dtype=torch.float32, device=dev)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.fmsa_select_scores(_tensor_arg(qp), _tensor_arg(kp), scores.data_ptr(), b, hp, kp.shape[1], s,
+                                      float(scale), status.data_ptr(), _stream(dev)), "fmsa_select_scores")
+    return scores
+
+
+def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_blocks: int, return_scores=False):
+    """Counterpart of the reference's select_blocks (flash_msa/msa_select_cutedsl.py:481-538)."""
+    if q_proxy.ndim != 4 or k_proxy.ndim != 4:
+        raise ValueError("q_proxy and k_proxy must have shape (B, H, S, D)")
+    if int(num_blocks) != q_proxy.shape[2] // BLOCK_SIZE:
+        raise ValueError("num_blocks does not match q_proxy sequence length")
+    scores = proxy_block_scores(q_proxy, k_proxy, scale)
+    idx = select_topk(scores, top_k_blocks)
+    return (idx, scores) if return_scores else idx
+
+
+# Upper bound on the bytes of forward partials held at once; larger problems run in several passes
+# over (batch, KV head) groups.
+MAX_PARTIAL_BYTES = 8 << 30
+
+
+def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, with_proxy=True, status=None):
+    """Sparse (or dense warmup) forward.  Returns (out [B,S,Hq*D] bf16, lse [B,Hq,S] fp32,
+    lse_proxy [B,Hp,S] fp32 or None)."""
+    _require_cuda(q, k, v)
+    lib = _lib.load()
+    q, k, v = (_as_kernel_input(t.detach()) for t in (q, k, v))
+    qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
+    b, hq, s, d = q.shape
+    hkv, hp = k.shape[1], qp.shape[1]
+    mpp = hq // hp
+    dev = q.device
+    pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale)
+    out = torch.empty(b, s, hq * d, dtype=q.dtype, device=dev)
+    lse = torch.empty(b, hq, s, dtype=torch.float32, device=dev)
+    lse_proxy = torch.empty(b, hp, s, dtype=torch.float32, device=dev) if with_proxy else None
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    counter = torch.empty(1, dtype=torch.int32, device=dev)
+    groups = b * hkv
+    per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
+    bytes_per_slot = mpp * d * 2 + (mpp + 1) * 4
+    gstep = max(1, min(groups, MAX_PARTIAL_BYTES // max(1, per_group * bytes_per_slot)))
+    slots = per_group * gstep
+    o_part = torch.empty(slots * mpp * d, dtype=q.dtype, device=dev)
+    lse_part = torch.empty(slots * (mpp + 1), dtype=torch.float32, device=dev)
+    row_ptr = 0 if dense else rix.row_ptr.data_ptr()
+    col_q = 0 if dense else rix.col_q.data_ptr()
+    edge_pos = 0 if dense else rix.edge_pos.data_ptr()
+    st = _stream(dev)
+    for g0 in range(0, groups, gstep):
+        gc = min(gstep, groups - g0)
+        _lib.check(lib.fmsa_sparse_fwd(ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp),
+                                       _tensor_arg(kp), row_ptr, col_q, o_part.data_ptr(), lse_part.data_ptr(), slots,
+                                       g0, gc, int(with_proxy), int(dense), counter.data_ptr(), status.data_ptr(), st),
+                   "fmsa_sparse_fwd")
+        _lib.check(lib.fmsa_sparse_fwd_combine(ctypes_byref(pb), o_part.data_ptr(), lse_part.data_ptr(), edge_pos, row_ptr,
+                                               out.data_ptr(), lse.data_ptr(),
+                                               lse_proxy.data_ptr() if with_proxy else 0, g0, gc, int(dense), st),
+                   "fmsa_sparse_fwd_combine")
+    return out, lse, lse_proxy

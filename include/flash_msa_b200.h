@@ -39,6 +39,14 @@ typedef struct {
     int64_t stride_b, stride_h, stride_s; /* in elements */
 } fmsa_tensor;
 
+/* Head configuration of one call.  Hq main query heads, Hkv key/value heads, Hp proxy query heads,
+ * Hpkv proxy key heads; Hq % Hp == 0, Hq % Hkv == 0, Hp % Hkv == 0, Hp % Hpkv == 0.
+ * top_k_blocks = top_k / 128 (ignored by the dense warmup paths). */
+typedef struct {
+    int32_t B, S, Hq, Hkv, Hp, Hpkv, top_k_blocks;
+    float scale;
+} fmsa_problem;
+
 /* Library ABI version (bumped on any signature change). */
 int fmsa_abi_version(void);
 
@@ -74,6 +82,40 @@ size_t fmsa_reverse_index_workspace_bytes(int64_t rows_bh, int32_t S);
 int fmsa_reverse_index(const int32_t* block_indices, int32_t* row_ptr, int32_t* col_q, int32_t* edge_pos,
                        int64_t rows_bh, int32_t S, int32_t top_k_blocks, void* workspace, size_t workspace_bytes,
                        void* stream);
+
+/* Proxy block scores: block_scores[b,p,q,j] = max over the causally visible keys k of block j of
+ * scale * Qp[b,p,q] . Kp[b,p/pg,k], fp32, for every j <= q/128 (entries with j > q/128 are not
+ * written).  Replaces the scoring half of the reference select kernel
+ * (flash_msa/msa_select_cutedsl.py:149-306) and follows the eager definition
+ * (flash_msa/tests/testing_model.py:75-88); scores are NOT rounded to bf16.
+ *   q_proxy (B,Hp,S,128), k_proxy (B,Hpkv,S,128) bf16;  block_scores fp32 [B,Hp,S,S/128];  status int32[1]. */
+int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores, int32_t B,
+                       int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t* status, void* stream);
+
+/* Sparse forward, stage 1: per-edge partial attention (key-block stationary).
+ * Replaces sparse_flash_varlen_forward (flash_msa/sparse_flash_varlen.py:92-261: local-block
+ * FlashAttention call + chunked paged-varlen calls + torch gathers) and, with with_proxy = 1, the
+ * second pass of the same machinery that the reference runs for the proxy log-sum-exp
+ * (flash_msa/msa_select_cutedsl.py:541-581).
+ * Work is restricted to the (batch, KV head) groups g_begin .. g_begin+g_count-1 (g = b*Hkv + kvh)
+ * so that the partial buffers can be bounded: fmsa_fwd_partial_slots() gives the number of edge
+ * slots the pass needs;
+ *   o_part   bf16 [slots, Hq/Hp, 128]       lse_part fp32 [slots, Hq/Hp + 1]
+ * dense = 1 ignores row_ptr/col_q and runs every causal (query block, key block) pair: the warmup
+ * forward (flash_msa/warmup/msa_forward_cutedsl_warmup.py:22-67).
+ * counter: int32[1] scratch (reset by the call);  status: int32[1]. */
+int64_t fmsa_fwd_partial_slots(const fmsa_problem* pb, int32_t g_count, int32_t dense);
+int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
+                    const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const int32_t* row_ptr,
+                    const int32_t* col_q, void* o_part, float* lse_part, int64_t part_slots, int32_t g_begin,
+                    int32_t g_count, int32_t with_proxy, int32_t dense, int32_t* counter, int32_t* status, void* stream);
+
+/* Sparse forward, stage 2: merge the partials of each query row (the job of the reference's
+ * merge_attention_chunk / merge_lse_chunk kernels, flash_msa/csrc/reverse_index_cuda.cu:235-354).
+ *   out bf16 [B, S, Hq*128]   lse fp32 [B, Hq, S]   lse_proxy fp32 [B, Hp, S] or NULL */
+int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_part, const float* lse_part,
+                            const int32_t* edge_pos, const int32_t* row_ptr, void* out, float* lse, float* lse_proxy,
+                            int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,31 @@
+"""Helpers shared by the GPU parity tests."""
+import torch
+
+from oracle import msa_oracle as O
+
+SCALE = 128 ** -0.5
+
+
+def bf16_inputs(cfg, device="cuda", layout="bhsd", skew=False):
+    """Seeded inputs, rounded to bf16.  layout "bshd" returns (B,H,S,D) views of (B,S,H,D)
+    storage, the layout the reference's callers pass (flash_msa/tests/testing_model.py:173-185)."""
+    ts = O.make_inputs(cfg["b"], cfg["s"], cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"], seed=cfg.get("seed", 0),
+                       dtype=torch.bfloat16, device=device, skew=skew)
+    qp, kp, q, k, v, do = ts
+    if layout == "bshd":
+        qp, kp, q, k, v = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (qp, kp, q, k, v))
+    return qp, kp, q, k, v, do
+
+
+def max_err(a, ref):
+    return (a.double() - ref.double()).abs().max().item()
+
+
+def yardstick_check(name, got, ref32, ref16, floor):
+    """Error of the kernel against the fp32 oracle must stay within twice the error of the
+    reference's own bf16 eager arithmetic against the same oracle (plus a small absolute floor
+    for tensors whose bf16 error happens to be tiny)."""
+    e_k = max_err(got, ref32)
+    e_y = max_err(ref16, ref32)
+    assert e_k <= 2.0 * e_y + floor, f"{name}: kernel err {e_k:.3e} vs yardstick {e_y:.3e}"
+    return e_k, e_y
