@@ -1,0 +1,137 @@
+"""Autograd boundary: the reference's public functions with the same arguments, layouts, return
+values and error behaviour (flash_msa/flash_msa.py:19-64, 129-278;
+flash_msa/warmup/flash_msa_warmup.py:6-106), on top of the sm_100a kernels."""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+BLOCK_SIZE = 128
+MAX_TOP_K_BLOCKS = 128
+
+# Set to True to read the device status word after every call (synchronises; for debugging).
+DEBUG_CHECK_STATUS = False
+
+
+def _validate_inputs(q_proxy, k_proxy, q, k, v, top_k, sparse: bool):
+    if q_proxy.ndim != 4 or k_proxy.ndim != 4 or q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("all attention tensors must have shape (B, H, S, D)")
+    b, n_proxy_heads, s, head_dim = q_proxy.shape
+    bk, n_proxy_kv_heads, sk, dk = k_proxy.shape
+    bq, n_heads, sq, dq = q.shape
+    bm, n_kv_heads, sm, dm = k.shape
+    bv, n_v_heads, sv, dv = v.shape
+    if not (b == bk == bq == bm == bv and s == sk == sq == sm == sv and head_dim == dk == dq == dm == dv
+            and n_kv_heads == n_v_heads):
+        raise ValueError("q_proxy, k_proxy, q, k, and v must agree on batch, sequence, head dimension, "
+                         "and KV head count")
+    if s % BLOCK_SIZE != 0:
+        raise ValueError(f"sequence length must be divisible by {BLOCK_SIZE}, got {s}")
+    if n_proxy_heads % n_proxy_kv_heads != 0:
+        raise ValueError("n_proxy_heads must be divisible by n_proxy_kv_heads")
+    if n_heads % n_kv_heads != 0:
+        raise ValueError("n_heads must be divisible by n_kv_heads")
+    if n_heads % n_proxy_heads != 0:
+        raise ValueError("n_heads must be divisible by n_proxy_heads")
+    if head_dim != 128:
+        raise NotImplementedError("Headdim must be 128")
+    if n_proxy_heads < n_kv_heads or n_proxy_heads % n_kv_heads != 0:
+        raise NotImplementedError("n_proxy_heads must be a multiple of n_kv_heads")
+    dts = {t.dtype for t in (q_proxy, k_proxy, q, k, v)}
+    if len(dts) != 1 or q.dtype != torch.bfloat16:
+        raise TypeError(f"flash_msa_b200 supports bf16 activations of one dtype, got {sorted(map(str, dts))}")
+    num_blocks = s // BLOCK_SIZE
+    if not sparse:
+        return num_blocks, 0
+    if int(top_k) % BLOCK_SIZE != 0:
+        raise ValueError(f"top_k must be divisible by {BLOCK_SIZE}, got {top_k}")
+    top_k_blocks = int(top_k) // BLOCK_SIZE
+    if not 1 <= top_k_blocks <= num_blocks:
+        raise ValueError(f"top_k selects {top_k_blocks} blocks, but sequence has {num_blocks} blocks")
+    if top_k_blocks > MAX_TOP_K_BLOCKS:
+        raise NotImplementedError(f"No more than {MAX_TOP_K_BLOCKS} blocks / topk={MAX_TOP_K_BLOCKS * BLOCK_SIZE} supported")
+    return num_blocks, top_k_blocks
+
+
+def _require_cuda(q):
+    if q.device.type != "cuda":
+        raise RuntimeError("flash_msa_b200 requires CUDA tensors (there is no CPU path)")
+
+
+def _maybe_check(status, what):
+    if DEBUG_CHECK_STATUS:
+        ops.check_status(status, what)
+
+
+class _SparseAttentionFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale):
+        num_blocks, top_k_blocks = _validate_inputs(q_proxy, k_proxy, q, k, v, int(top_k), True)
+        _require_cuda(q)
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        scores = ops.proxy_block_scores(q_proxy, k_proxy, float(scale), status=status)
+        block_indices = ops.select_topk(scores, top_k_blocks)
+        del scores
+        rix = ops.build_reverse_index(block_indices)
+        out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), rix, status=status)
+        _maybe_check(status, "flash_msa_func forward")
+        # kl_loss is a placeholder whose gradient switches the KL branch of the backward on
+        # (reference: flash_msa/msa_forward_cutedsl.py:69)
+        kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
+        ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, rix.row_ptr, rix.col_q)
+        ctx.scale = float(scale)
+        ctx.top_k_blocks = top_k_blocks
+        ctx.block_indices = block_indices      # kept for inspection by tests (not a saved tensor)
+        return out, kl_loss
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_kl):
+        q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, row_ptr, col_q = ctx.saved_tensors
+        b, _, s, _ = q.shape
+        if grad_out is None:
+            grad_out = torch.zeros_like(out)
+        rix = ops.ReverseIndex(row_ptr, col_q, None, b, q_proxy.shape[1], s, ctx.top_k_blocks)
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
+                                                      ctx.scale, rix, grad_kl, status=status)
+        _maybe_check(status, "flash_msa_func backward")
+        return dqp, dkp, dq, dk, dv, None, None
+
+
+class _WarmupSparseAttentionFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale):
+        _ = int(top_k)                         # accepted and ignored, as in the reference
+        _validate_inputs(q_proxy, k_proxy, q, k, v, 0, False)
+        if q.device.type != "cuda":
+            raise RuntimeError("warmup MSA forward requires CUDA tensors")
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), None, dense=True,
+                                                         status=status)
+        _maybe_check(status, "flash_msa_warmup_func forward")
+        kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
+        ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy)
+        ctx.scale = float(scale)
+        return out, kl_loss
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_kl):
+        q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy = ctx.saved_tensors
+        if grad_out is None:
+            grad_out = torch.zeros_like(out)
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
+                                                      ctx.scale, None, grad_kl, dense=True, status=status)
+        _maybe_check(status, "flash_msa_warmup_func backward")
+        return dqp, dkp, dq, dk, dv, None, None
+
+
+def sparse_attention(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
+    """Block-sparse top-k GQA attention.  Returns ``(attn_out [B,S,Hq*D], kl_loss placeholder)``."""
+    return _SparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale))
+
+
+def sparse_attention_warmup(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
+    """Dense causal warmup attention with full-sequence proxy KL gradients."""
+    return _WarmupSparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale))

@@ -15,6 +15,13 @@ inline int check_launch() {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Head-count relations every entry point relies on (the reference checks the same ones in
+// flash_msa/flash_msa.py:44-53 and flash_msa/warmup/flash_msa_warmup.py:34-43).
+inline bool problem_ok(const fmsa_problem* pb) {
+    return pb && pb->B > 0 && pb->S > 0 && pb->S % 128 == 0 && pb->Hq > 0 && pb->Hkv > 0 && pb->Hp > 0 && pb->Hpkv > 0 &&
+           pb->Hq % pb->Hkv == 0 && pb->Hq % pb->Hp == 0 && pb->Hp % pb->Hpkv == 0 && pb->Hp % pb->Hkv == 0;
+}
+
 inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
 }  // namespace fmsa

@@ -456,11 +456,6 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
     }
 }
 
-bool problem_ok(const fmsa_problem* pb) {
-    return pb && pb->B > 0 && pb->S > 0 && pb->S % kBlock == 0 && pb->Hq > 0 && pb->Hkv > 0 && pb->Hp > 0 && pb->Hpkv > 0 &&
-           pb->Hq % pb->Hkv == 0 && pb->Hq % pb->Hp == 0 && pb->Hp % pb->Hpkv == 0 && pb->Hp % pb->Hkv == 0;
-}
-
 }  // namespace
 }  // namespace fmsa
 

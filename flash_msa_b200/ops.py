@@ -192,3 +192,57 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
                                                lse_proxy.data_ptr() if with_proxy else 0, g0, gc, int(dense), st),
                    "fmsa_sparse_fwd_combine")
     return out, lse, lse_proxy
+
+
+def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy, scale, rix, grad_kl, *, dense=False,
+                       status=None):
+    """Fused backward.  ``out`` is the [B,S,Hq*D] forward output, ``grad_out`` its upstream gradient,
+    ``grad_kl`` the upstream gradient of kl_loss (0-dim tensor) or None.  Returns
+    (dq_proxy, dk_proxy, dq, dk, dv) in the input dtype, shaped like the inputs."""
+    _require_cuda(q, k, v, grad_out)
+    lib = _lib.load()
+    q, k, v = (_as_kernel_input(t.detach()) for t in (q, k, v))
+    qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
+    b, hq, s, d = q.shape
+    hkv, hp, hpkv = k.shape[1], qp.shape[1], kp.shape[1]
+    dev = q.device
+    st = _stream(dev)
+    pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale)
+    with_kl = grad_kl is not None
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    counter = torch.empty(1, dtype=torch.int32, device=dev)
+
+    go = grad_out.detach().reshape(b, s, hq, d)
+    if go.dtype != q.dtype:
+        go = go.to(q.dtype)
+    go = go.permute(0, 2, 1, 3)                       # (B,Hq,S,D) view, no copy
+    go = _as_kernel_input(go)
+    delta = torch.empty(b, hq, s, dtype=torch.float32, device=dev)
+    _lib.check(lib.fmsa_bwd_delta(out.data_ptr(), _tensor_arg(go), delta.data_ptr(), b, s, hq, st), "fmsa_bwd_delta")
+
+    dq_acc = torch.zeros(b, hq, s, d, dtype=torch.float32, device=dev)
+    dk = torch.empty(b, hkv, s, d, dtype=q.dtype, device=dev)
+    dv = torch.empty(b, hkv, s, d, dtype=q.dtype, device=dev)
+    if with_kl:
+        dqp_acc = torch.zeros(b, hp, s, d, dtype=torch.float32, device=dev)
+        dkp_acc = torch.zeros(b, hpkv, s, d, dtype=torch.float32, device=dev)
+    _lib.check(lib.fmsa_sparse_bwd(
+        ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp), _tensor_arg(go),
+        lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(),
+        0 if dense else rix.row_ptr.data_ptr(), 0 if dense else rix.col_q.data_ptr(),
+        dq_acc.data_ptr(), dqp_acc.data_ptr() if with_kl else 0, dkp_acc.data_ptr() if with_kl else 0,
+        dk.data_ptr(), dv.data_ptr(), int(with_kl), int(dense), counter.data_ptr(), status.data_ptr(), st), "fmsa_sparse_bwd")
+
+    dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
+    _lib.check(lib.fmsa_cast_scaled(dq_acc.data_ptr(), dq.data_ptr(), dq_acc.numel(), 0, st), "fmsa_cast_scaled")
+    if with_kl:
+        gk = grad_kl.detach().to(device=dev, dtype=torch.float32).reshape(1)
+        dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
+        dkp = torch.empty(b, hpkv, s, d, dtype=q.dtype, device=dev)
+        _lib.check(lib.fmsa_cast_scaled(dqp_acc.data_ptr(), dqp.data_ptr(), dqp_acc.numel(), gk.data_ptr(), st), "fmsa_cast_scaled")
+        _lib.check(lib.fmsa_cast_scaled(dkp_acc.data_ptr(), dkp.data_ptr(), dkp_acc.numel(), gk.data_ptr(), st), "fmsa_cast_scaled")
+    else:
+        dqp = torch.zeros(b, hp, s, d, dtype=q.dtype, device=dev)
+        dkp = torch.zeros(b, hpkv, s, d, dtype=q.dtype, device=dev)
+    return dqp, dkp, dq, dk, dv

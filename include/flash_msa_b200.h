@@ -117,6 +117,34 @@ int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_part, const fl
                             const int32_t* edge_pos, const int32_t* row_ptr, void* out, float* lse, float* lse_proxy,
                             int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
 
+/* delta[b,h,q] = sum_d out[b,q,h,d] * d_out[b,q,h,d], fp32 [B,Hq,S].
+ * Replaces the torch expression at flash_msa/flash_msa.py:99.  out is the contiguous
+ * [B,S,Hq*128] forward output; d_out is described as a (B,Hq,S,128) view. */
+int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int32_t B, int32_t S, int32_t Hq,
+                   void* stream);
+
+/* Fused backward over the selected edges (dense = 1: over every causal block pair, the warmup
+ * backward).  Replaces run_fused_backward (flash_msa/msa_backward_cutedsl.py:944-1114) and
+ * run_warmup_backward (flash_msa/warmup/msa_backward_cutedsl_warmup.py:117-191).
+ *   d_out      (B,Hq,S,128) view of the upstream gradient
+ *   lse, delta fp32 [B,Hq,S];  lse_proxy fp32 [B,Hp,S]
+ *   dq_acc fp32 [B,Hq,S,128], dqp_acc fp32 [B,Hp,S,128], dkp_acc fp32 [B,Hpkv,S,128]: ZEROED by the
+ *              caller, accumulated with red.add; dqp/dkp already carry scale/(B*Hp*S)
+ *   dk, dv     bf16 [B,Hkv,S,128], written exactly once per element
+ * with_kl = 0 skips the proxy work (the reference does the same when no gradient reaches kl_loss,
+ * flash_msa/flash_msa.py:104-106) and ignores q_proxy, k_proxy, lse_proxy, dqp_acc, dkp_acc.
+ * counter: int32[1] scratch;  status: int32[1]. */
+int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
+                    const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out, const float* lse,
+                    const float* lse_proxy, const float* delta, const int32_t* row_ptr, const int32_t* col_q,
+                    float* dq_acc, float* dqp_acc, float* dkp_acc, void* dk, void* dv, int32_t with_kl, int32_t dense,
+                    int32_t* counter, int32_t* status, void* stream);
+
+/* dst[i] = bf16(src[i] * f), f = *scale_ptr (a device scalar, e.g. the upstream gradient of
+ * kl_loss: flash_msa/flash_msa.py:122-125) or 1 when scale_ptr is NULL.  n % 4 == 0.
+ * Replaces the fp32 -> input-dtype casts at flash_msa/msa_backward_cutedsl.py:1075-1081. */
+int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -301,9 +301,9 @@ def warmup_forward_backward(q_proxy, k_proxy, q, k, v, scale, d_out,
 # reference's own tests run.
 # ----------------------------------------------------------------------------
 
-def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale):
-    """Line-by-line restatement of testing_model.py:61-169 with stable top-k.
-    Differentiable; returns ``(attn_out [B,S,Hq*D], kl_loss)``."""
+def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None):
+    """Line-by-line restatement of testing_model.py:61-169 with stable top-k (or a given
+    selection).  Differentiable; returns ``(attn_out [B,S,Hq*D], kl_loss)``."""
     b, hp, s, d = q_proxy.shape
     hq, hkv, hpkv = q.shape[1], k.shape[1], k_proxy.shape[1]
     nb = s // BLOCK
@@ -316,7 +316,10 @@ def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale):
     future = torch.triu(torch.ones(s, s, device=dev, dtype=torch.bool), diagonal=1)
     proxy_scores = proxy_scores.masked_fill(future, float("-inf"))
     block_scores = proxy_scores.view(b, hp, s, nb, BLOCK).amax(dim=-1)
-    idx = stable_topk(block_scores.detach(), kb).to(torch.int64)        # sentinel nb
+    if block_indices is None:
+        idx = stable_topk(block_scores.detach().float(), kb).to(torch.int64)        # sentinel nb
+    else:
+        idx = block_indices.to(torch.int64)
     block_mask = torch.zeros(b, hp, s, nb + 1, dtype=torch.bool, device=dev)
     block_mask.scatter_(3, idx, True)
     block_mask = block_mask[..., :nb]

@@ -1,0 +1,104 @@
+"""Backward parity on the GPU through the public autograd API: dQ, dK, dV, dQp, dKp of the sparse
+and the warmup function against the fp32 oracle, with the reference's bf16 eager arithmetic as the
+error yardstick (tolerance: at most twice its error, plus a small floor)."""
+import pytest
+import torch
+
+from oracle import msa_oracle as O
+from tests.gpu_util import SCALE, bf16_inputs, max_err, yardstick_check
+
+pytestmark = pytest.mark.gpu
+NAMES = ["dq_proxy", "dk_proxy", "dq", "dk", "dv"]
+
+CFGS = {
+    "tiny": dict(b=1, s=512, hq=4, hkv=1, hp=2, hpkv=1, kb=2, seed=1),
+    "c1": dict(b=2, s=1024, hq=8, hkv=2, hp=2, hpkv=2, kb=4, seed=0),
+    "mpp6": dict(b=1, s=2048, hq=12, hkv=2, hp=2, hpkv=1, kb=5, seed=2),
+    "ref_default": dict(b=1, s=2048, hq=16, hkv=2, hp=4, hpkv=1, kb=4, seed=67),
+    "pg2": dict(b=1, s=1536, hq=8, hkv=2, hp=4, hpkv=4, kb=3, seed=4),
+}
+
+
+@pytest.fixture(scope="module")
+def fm():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import flash_msa_b200
+    from flash_msa_b200 import api
+    api.DEBUG_CHECK_STATUS = True
+    return flash_msa_b200
+
+
+def _run_kernel(fn, tensors, do, top_k, grad_kl):
+    leaves = [t.detach().clone().requires_grad_(True) for t in tensors]
+    out, kl = fn(*leaves, top_k, SCALE)
+    assert kl.item() == 0.0 and kl.dtype == torch.float32
+    loss = (out.float() * do.float()).sum()
+    if grad_kl is not None:
+        loss = loss + grad_kl * kl
+    loss.backward()
+    return out, [t.grad for t in leaves], out.grad_fn
+
+
+def _floors(ref):
+    return 1e-3 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("grad_kl", [1.0, 0.37, None])
+@pytest.mark.parametrize("name", list(CFGS))
+def test_sparse_backward(fm, name, grad_kl):
+    cfg = CFGS[name]
+    if grad_kl != 1.0 and name not in ("tiny", "c1"):
+        pytest.skip("grad_kl variants covered on the small shapes")
+    qp, kp, q, k, v, do = bf16_inputs(cfg, layout="bshd" if name == "c1" else "bhsd")
+    out, grads, node = _run_kernel(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, grad_kl)
+    idx = node.block_indices
+    r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, grad_kl, block_indices=idx)
+    _, _, g16 = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE, block_indices=idx),
+                                         (qp, kp, q, k, v), do, grad_kl)
+    for n, got, y in zip(NAMES, grads, g16):
+        assert got.shape == r32[n].shape and got.dtype == torch.bfloat16
+        if grad_kl is None and n in ("dq_proxy", "dk_proxy"):
+            assert got.abs().max().item() == 0.0
+            continue
+        yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
+
+
+@pytest.mark.parametrize("grad_kl", [1.0, None])
+@pytest.mark.parametrize("name", ["tiny", "c1", "mpp6"])
+def test_warmup_backward(fm, name, grad_kl):
+    cfg = CFGS[name]
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    out, grads, _ = _run_kernel(fm.flash_msa_warmup_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, grad_kl)
+    r32 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, grad_kl)
+    _, _, g16 = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, SCALE), (qp, kp, q, k, v), do, grad_kl)
+    o16 = O.warmup_forward(qp, kp, q, k, v, SCALE, dtype=torch.bfloat16)["out"]
+    yardstick_check("out", out, r32["out"], o16, 1e-3)
+    for n, got, y in zip(NAMES, grads, g16):
+        if grad_kl is None and n in ("dq_proxy", "dk_proxy"):
+            assert got.abs().max().item() == 0.0
+            continue
+        yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
+
+
+def test_grad_out_none_and_error_behaviour(fm):
+    cfg = CFGS["tiny"]
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    # only kl_loss feeds the loss: main gradients are zero, proxy gradients are not
+    leaves = [t.detach().clone().requires_grad_(True) for t in (qp, kp, q, k, v)]
+    out, kl = fm.flash_msa_func(*leaves, 256, SCALE)
+    kl.backward()
+    assert leaves[2].grad.abs().max().item() == 0.0 and leaves[4].grad.abs().max().item() == 0.0
+    assert leaves[0].grad.abs().max().item() > 0.0
+    with pytest.raises(ValueError):
+        fm.flash_msa_func(qp, kp, q, k, v, 200, SCALE)                  # top_k not a multiple of 128
+    with pytest.raises(ValueError):
+        fm.flash_msa_func(qp, kp, q, k, v, 128 * 64, SCALE)             # more blocks than the sequence has
+    with pytest.raises(ValueError):
+        fm.flash_msa_func(qp[:, :, :500], kp, q, k, v, 256, SCALE)      # shapes disagree
+    with pytest.raises(NotImplementedError):
+        fm.flash_msa_func(qp[..., :64], kp[..., :64], q[..., :64], k[..., :64], v[..., :64], 256, SCALE)
+    with pytest.raises(TypeError):
+        fm.flash_msa_func(qp.float(), kp.float(), q.float(), k.float(), v.float(), 256, SCALE)
+    with pytest.raises(RuntimeError):
+        fm.flash_msa_warmup_func(qp.cpu(), kp.cpu(), q.cpu(), k.cpu(), v.cpu(), 256, SCALE)
