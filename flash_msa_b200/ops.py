@@ -15,6 +15,37 @@ ctypes_byref = ctypes.byref
 BLOCK_SIZE = 128
 
 
+# Instrumentation used by the benchmark: when KERNEL_EVENTS is a list, every C-ABI launch is
+# bracketed by CUDA events on the launching stream and (name, start, end) is appended.
+# LAUNCHES counts the kernels launched by this library since import.
+KERNEL_EVENTS = None
+LAUNCHES = 0
+
+
+def _launch(name: str, n_kernels: int, status: int, device) -> None:
+    global LAUNCHES
+    _lib.check(status, name)
+    LAUNCHES += n_kernels
+
+
+class _Timed:
+    def __init__(self, name, device):
+        self.name, self.device = name, device
+
+    def __enter__(self):
+        if KERNEL_EVENTS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.device))
+        return self
+
+    def __exit__(self, *exc):
+        if KERNEL_EVENTS is not None:
+            self.end.record(torch.cuda.current_stream(self.device))
+            KERNEL_EVENTS.append((self.name, self.start, self.end))
+        return False
+
+
 def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -50,8 +81,9 @@ def select_topk(block_scores: torch.Tensor, top_k_blocks: int) -> torch.Tensor:
     block_scores = block_scores.contiguous()
     out = torch.empty(b, hp, s, int(top_k_blocks), dtype=torch.int32, device=block_scores.device)
     lib = _lib.load()
-    _lib.check(lib.fmsa_select_topk(block_scores.data_ptr(), out.data_ptr(), b * hp, s, int(top_k_blocks),
-                                    _stream(out.device)), "fmsa_select_topk")
+    with _Timed("select_topk", out.device):
+        _launch("fmsa_select_topk", 1, lib.fmsa_select_topk(block_scores.data_ptr(), out.data_ptr(), b * hp, s,
+                                                          int(top_k_blocks), _stream(out.device)), out.device)
     return out
 
 
@@ -84,9 +116,10 @@ def build_reverse_index(block_indices: torch.Tensor) -> ReverseIndex:
     edge_pos = torch.empty(b, hp, s, kb, dtype=torch.int32, device=dev)
     ws_bytes = lib.fmsa_reverse_index_workspace_bytes(b * hp, s)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    _lib.check(lib.fmsa_reverse_index(block_indices.data_ptr(), row_ptr.data_ptr(), col_q.data_ptr(),
-                                      edge_pos.data_ptr(), b * hp, s, kb, ws.data_ptr(), ws_bytes, _stream(dev)),
-               "fmsa_reverse_index")
+    with _Timed("reverse_index", dev):
+        _launch("fmsa_reverse_index", 4, lib.fmsa_reverse_index(block_indices.data_ptr(), row_ptr.data_ptr(),
+                                                              col_q.data_ptr(), edge_pos.data_ptr(), b * hp, s, kb,
+                                                              ws.data_ptr(), ws_bytes, _stream(dev)), dev)
     return ReverseIndex(row_ptr, col_q, edge_pos, b, hp, s, kb)
 
 
@@ -131,8 +164,10 @@ def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: floa
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     lib = _lib.load()
-    _lib.check(lib.fmsa_select_scores(_tensor_arg(qp), _tensor_arg(kp), scores.data_ptr(), b, hp, kp.shape[1], s,
-                                      float(scale), status.data_ptr(), _stream(dev)), "fmsa_select_scores")
+    with _Timed("select_scores", dev):
+        _launch("fmsa_select_scores", 1, lib.fmsa_select_scores(_tensor_arg(qp), _tensor_arg(kp), scores.data_ptr(), b, hp,
+                                                              kp.shape[1], s, float(scale), status.data_ptr(),
+                                                              _stream(dev)), dev)
     return scores
 
 
@@ -183,14 +218,15 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
     st = _stream(dev)
     for g0 in range(0, groups, gstep):
         gc = min(gstep, groups - g0)
-        _lib.check(lib.fmsa_sparse_fwd(ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp),
-                                       _tensor_arg(kp), row_ptr, col_q, o_part.data_ptr(), lse_part.data_ptr(), slots,
-                                       g0, gc, int(with_proxy), int(dense), counter.data_ptr(), status.data_ptr(), st),
-                   "fmsa_sparse_fwd")
-        _lib.check(lib.fmsa_sparse_fwd_combine(ctypes_byref(pb), o_part.data_ptr(), lse_part.data_ptr(), edge_pos, row_ptr,
-                                               out.data_ptr(), lse.data_ptr(),
-                                               lse_proxy.data_ptr() if with_proxy else 0, g0, gc, int(dense), st),
-                   "fmsa_sparse_fwd_combine")
+        with _Timed("attn_fwd", dev):
+            _launch("fmsa_sparse_fwd", 1, lib.fmsa_sparse_fwd(
+                ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp), row_ptr,
+                col_q, o_part.data_ptr(), lse_part.data_ptr(), slots, g0, gc, int(with_proxy), int(dense),
+                counter.data_ptr(), status.data_ptr(), st), dev)
+        with _Timed("fwd_combine", dev):
+            _launch("fmsa_sparse_fwd_combine", 1, lib.fmsa_sparse_fwd_combine(
+                ctypes_byref(pb), o_part.data_ptr(), lse_part.data_ptr(), edge_pos, row_ptr, out.data_ptr(), lse.data_ptr(),
+                lse_proxy.data_ptr() if with_proxy else 0, g0, gc, int(dense), st), dev)
     return out, lse, lse_proxy
 
 
@@ -219,7 +255,8 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     go = go.permute(0, 2, 1, 3)                       # (B,Hq,S,D) view, no copy
     go = _as_kernel_input(go)
     delta = torch.empty(b, hq, s, dtype=torch.float32, device=dev)
-    _lib.check(lib.fmsa_bwd_delta(out.data_ptr(), _tensor_arg(go), delta.data_ptr(), b, s, hq, st), "fmsa_bwd_delta")
+    with _Timed("bwd_delta", dev):
+        _launch("fmsa_bwd_delta", 1, lib.fmsa_bwd_delta(out.data_ptr(), _tensor_arg(go), delta.data_ptr(), b, s, hq, st), dev)
 
     dq_acc = torch.zeros(b, hq, s, d, dtype=torch.float32, device=dev)
     dk = torch.empty(b, hkv, s, d, dtype=q.dtype, device=dev)
@@ -227,21 +264,26 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     if with_kl:
         dqp_acc = torch.zeros(b, hp, s, d, dtype=torch.float32, device=dev)
         dkp_acc = torch.zeros(b, hpkv, s, d, dtype=torch.float32, device=dev)
-    _lib.check(lib.fmsa_sparse_bwd(
-        ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp), _tensor_arg(go),
-        lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(),
-        0 if dense else rix.row_ptr.data_ptr(), 0 if dense else rix.col_q.data_ptr(),
-        dq_acc.data_ptr(), dqp_acc.data_ptr() if with_kl else 0, dkp_acc.data_ptr() if with_kl else 0,
-        dk.data_ptr(), dv.data_ptr(), int(with_kl), int(dense), counter.data_ptr(), status.data_ptr(), st), "fmsa_sparse_bwd")
+    with _Timed("attn_bwd", dev):
+        _launch("fmsa_sparse_bwd", 1, lib.fmsa_sparse_bwd(
+            ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
+            _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(),
+            0 if dense else rix.row_ptr.data_ptr(), 0 if dense else rix.col_q.data_ptr(),
+            dq_acc.data_ptr(), dqp_acc.data_ptr() if with_kl else 0, dkp_acc.data_ptr() if with_kl else 0,
+            dk.data_ptr(), dv.data_ptr(), int(with_kl), int(dense), counter.data_ptr(), status.data_ptr(), st), dev)
 
     dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
-    _lib.check(lib.fmsa_cast_scaled(dq_acc.data_ptr(), dq.data_ptr(), dq_acc.numel(), 0, st), "fmsa_cast_scaled")
+    with _Timed("cast", dev):
+        _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dq_acc.data_ptr(), dq.data_ptr(), dq_acc.numel(), 0, st), dev)
     if with_kl:
         gk = grad_kl.detach().to(device=dev, dtype=torch.float32).reshape(1)
         dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
         dkp = torch.empty(b, hpkv, s, d, dtype=q.dtype, device=dev)
-        _lib.check(lib.fmsa_cast_scaled(dqp_acc.data_ptr(), dqp.data_ptr(), dqp_acc.numel(), gk.data_ptr(), st), "fmsa_cast_scaled")
-        _lib.check(lib.fmsa_cast_scaled(dkp_acc.data_ptr(), dkp.data_ptr(), dkp_acc.numel(), gk.data_ptr(), st), "fmsa_cast_scaled")
+        with _Timed("cast", dev):
+            _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dqp_acc.data_ptr(), dqp.data_ptr(), dqp_acc.numel(),
+                                                              gk.data_ptr(), st), dev)
+            _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dkp_acc.data_ptr(), dkp.data_ptr(), dkp_acc.numel(),
+                                                              gk.data_ptr(), st), dev)
     else:
         dqp = torch.zeros(b, hp, s, d, dtype=q.dtype, device=dev)
         dkp = torch.zeros(b, hpkv, s, d, dtype=q.dtype, device=dev)
