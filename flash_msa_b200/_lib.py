@@ -60,6 +60,8 @@ def _declare(lib):
     lib.fmsa_reverse_index_workspace_bytes.argtypes = [c_int64, c_int32]
     lib.fmsa_reverse_index.restype = c_int
     lib.fmsa_reverse_index.argtypes = [P, P, P, P, c_int64, c_int32, c_int32, P, c_size_t, P]
+    lib.fmsa_reverse_index_static.restype = c_int
+    lib.fmsa_reverse_index_static.argtypes = [P, P, P, P, c_int64, c_int32, c_int32, P]
     T = ctypes.POINTER(FmsaTensor)
     PB = ctypes.POINTER(FmsaProblem)
     lib.fmsa_select_scores.restype = c_int

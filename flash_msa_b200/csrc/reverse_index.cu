@@ -12,6 +12,8 @@
 // The edge rule `0 <= kb < NB && kb <= q/128` is the reference's
 // (flash_msa/csrc/reverse_index_cuda.cu:41); its atomics-based slot assignment (:118) is replaced
 // by ranks, so the output is a pure function of the input.
+#include <mutex>
+
 #include "host_common.h"
 #include "sm100.cuh"
 
@@ -153,7 +155,52 @@ size_t reverse_index_scratch_bytes(int64_t rows_bh, int32_t S) {
     return carve(nullptr, rows_bh, S / kBlock).bytes;
 }
 
+// -------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch lives in the library image.
+// -------------------------------------------------------------------------------------------
+// Every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_rix_static_scratch[FMSA_STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle for the runtime, not a device address, so the
+// address is asked for once per device (with that device current) and cached.
+static int static_scratch_address(void** out) {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {nullptr};
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FMSA_ERR_CUDA;
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_rix_static_scratch) != cudaSuccess || p == nullptr) return FMSA_ERR_CUDA;
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return FMSA_OK;
+}
+
 }  // namespace fmsa
+
+extern "C" int fmsa_reverse_index_static(const int32_t* block_indices, int32_t* row_ptr, int32_t* col_q,
+                                         int32_t* edge_pos, int64_t rows_bh, int32_t S, int32_t top_k_blocks,
+                                         void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(block_indices && row_ptr && col_q && edge_pos);
+    FMSA_REQUIRE(rows_bh > 0 && rows_bh <= 65535 && S > 0 && S % kBlock == 0);
+    const int NB = S / kBlock;
+    FMSA_REQUIRE(top_k_blocks >= 1 && top_k_blocks <= NB);
+    FMSA_REQUIRE(rows_bh * static_cast<int64_t>(S) * top_k_blocks < 0x7fffffffLL);
+    if (NB > 2048) return FMSA_ERR_UNSUPPORTED;
+    // the problem must fit the built-in scratch; larger ones need fmsa_reverse_index and a workspace
+    if (reverse_index_scratch_bytes(rows_bh, S) > static_cast<size_t>(FMSA_STATIC_SCRATCH_BYTES)) return FMSA_ERR_WORKSPACE;
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != FMSA_OK) return rc;
+    // Nothing in the scratch has to start at zero: every count, offset and total a kernel reads
+    // was written earlier in the same call, so stale contents of a previous call are never seen.
+    return reverse_index_launch(block_indices, row_ptr, col_q, edge_pos, rows_bh, S, top_k_blocks, scratch,
+                                static_cast<cudaStream_t>(stream));
+}
 
 extern "C" size_t fmsa_reverse_index_workspace_bytes(int64_t rows_bh, int32_t S) {
     if (rows_bh <= 0 || S <= 0 || S % fmsa::kBlock != 0) return 0;

@@ -123,6 +123,39 @@ def build_reverse_index(block_indices: torch.Tensor) -> ReverseIndex:
     return ReverseIndex(row_ptr, col_q, edge_pos, b, hp, s, kb)
 
 
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def build_reverse_index_static(block_indices: torch.Tensor, row_ptr: torch.Tensor, col_q: torch.Tensor,
+                               edge_pos: torch.Tensor) -> ReverseIndex:
+    """Reverse index through the allocation-free entry point: the caller passes the three output
+    tensors and the library uses the scratch array built into its image instead of a workspace.
+    Meant for hosts that cannot allocate device memory around the call (a frozen memory plan, an
+    FFI binding that owns only inputs and outputs).  Limits: the problem's scratch need must not
+    exceed STATIC_SCRATCH_BYTES (ValueError otherwise); calls that may overlap on the GPU race on
+    the shared array, so keep them ordered on one stream; the first call on a device should come
+    before any stream capture."""
+    _require_cuda(block_indices, row_ptr, col_q, edge_pos)
+    if block_indices.dtype != torch.int32 or block_indices.ndim != 4 or not block_indices.is_contiguous():
+        raise TypeError("block_indices must be contiguous int32 [B,Hp,S,Kb]")
+    b, hp, s, kb = block_indices.shape
+    nb = s // BLOCK_SIZE
+    if (row_ptr.numel() < b * hp * nb + 1 or col_q.numel() < b * hp * s * kb or edge_pos.numel() < b * hp * s * kb
+            or any(t.dtype != torch.int32 or not t.is_contiguous() for t in (row_ptr, col_q, edge_pos))):
+        raise ValueError("output tensors are too small or not contiguous int32")
+    lib = _lib.load()
+    need = lib.fmsa_reverse_index_workspace_bytes(b * hp, s)
+    if need > STATIC_SCRATCH_BYTES:
+        raise ValueError(f"reverse index of this size needs {need} bytes of scratch, more than the {STATIC_SCRATCH_BYTES} "
+                         "bytes built into the library; use build_reverse_index (caller-provided workspace)")
+    dev = block_indices.device
+    with _Timed("reverse_index", dev):
+        _launch("fmsa_reverse_index_static", 4, lib.fmsa_reverse_index_static(
+            block_indices.data_ptr(), row_ptr.data_ptr(), col_q.data_ptr(), edge_pos.data_ptr(), b * hp, s, kb,
+            _stream(dev)), dev)
+    return ReverseIndex(row_ptr, col_q, edge_pos.view(b, hp, s, kb), b, hp, s, kb)
+
+
 # ----------------------------------------------------------------------------------------------
 # tensor-core kernels
 # ----------------------------------------------------------------------------------------------

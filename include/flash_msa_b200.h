@@ -83,6 +83,25 @@ int fmsa_reverse_index(const int32_t* block_indices, int32_t* row_ptr, int32_t* 
                        int64_t rows_bh, int32_t S, int32_t top_k_blocks, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* Reverse index for callers that cannot hand the library any device memory of their own.
+ * (No counterpart in the reference, whose wrappers allocate their workspaces with torch.)
+ * Some hosts own nothing but the input and output tensors: a thin FFI binding without a device
+ * allocator, or a runtime whose memory plan is frozen before the step runs, so that neither it nor
+ * this library may call cudaMalloc.  For them the scratch of fmsa_reverse_index is a fixed array of
+ * FMSA_STATIC_SCRATCH_BYTES inside the library image (each GPU that loads the library keeps it
+ * until the process ends).  Same inputs, outputs and results as fmsa_reverse_index.
+ *  - Problems whose scratch need (fmsa_reverse_index_workspace_bytes) exceeds
+ *    FMSA_STATIC_SCRATCH_BYTES are refused with FMSA_ERR_WORKSPACE; nothing is launched.
+ *  - The call allocates and frees nothing.  Its first call on a device looks the array's device
+ *    address up once (cudaGetSymbolAddress, with that device current); make that first call before
+ *    any stream capture begins.
+ *  - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *    (different streams without an ordering) race and give wrong results.  Calls ordered on one
+ *    stream are safe; nothing needs clearing between them. */
+#define FMSA_STATIC_SCRATCH_BYTES (8 << 20)
+int fmsa_reverse_index_static(const int32_t* block_indices, int32_t* row_ptr, int32_t* col_q, int32_t* edge_pos,
+                              int64_t rows_bh, int32_t S, int32_t top_k_blocks, void* stream);
+
 /* Proxy block scores: block_scores[b,p,q,j] = max over the causally visible keys k of block j of
  * scale * Qp[b,p,q] . Kp[b,p/pg,k], fp32, for every j <= q/128 (entries with j > q/128 are not
  * written).  Replaces the scoring half of the reference select kernel
