@@ -39,6 +39,9 @@ WORKLOADS = {
     # name: (B, S, Hq, Hkv, Hp, Hpkv, Kb, warmup-mode)
     "c2": dict(b=2, s=8192, hq=32, hkv=8, hp=8, hpkv=8, kb=16, dense=False,
                desc="sparse MSA fwd+bwd, B=2 S=8192 Hq=32 Hkv=8 Hp=8 Hpkv=8 D=128 top_k=16 blocks, causal, N(0,1) bf16"),
+    # a quarter of c2 (same S, top_k and head ratios): the small case used for ncu captures
+    "c2q": dict(b=1, s=8192, hq=16, hkv=4, hp=4, hpkv=4, kb=16, dense=False,
+                desc="sparse MSA fwd+bwd, quarter of c2: B=1 S=8192 Hq=16 Hkv=4 Hp=4 Hpkv=4 D=128 top_k=16 blocks"),
     "c3": dict(b=4, s=4096, hq=32, hkv=8, hp=8, hpkv=8, kb=1, dense=True,
                desc="MSA warmup fwd+bwd, B=4 S=4096 Hq=32 Hkv=8 Hp=8 Hpkv=8 D=128, dense causal + proxy KL"),
     "c5": dict(b=1, s=65536, hq=64, hkv=8, hp=16, hpkv=8, kb=32, dense=False,
