@@ -79,7 +79,7 @@ class _SparseAttentionFunction(torch.autograd.Function):
         # kl_loss is a placeholder whose gradient switches the KL branch of the backward on
         # (reference: flash_msa/msa_forward_cutedsl.py:69)
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
-        ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, rix.row_ptr, rix.col_q)
+        ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, rix.row_ptr, rix.col_q, rix.edge_pos)
         ctx.scale = float(scale)
         ctx.top_k_blocks = top_k_blocks
         ctx.block_indices = block_indices      # kept for inspection by tests (not a saved tensor)
@@ -87,11 +87,11 @@ class _SparseAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out, grad_kl):
-        q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, row_ptr, col_q = ctx.saved_tensors
+        q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, row_ptr, col_q, edge_pos = ctx.saved_tensors
         b, _, s, _ = q.shape
         if grad_out is None:
             grad_out = torch.zeros_like(out)
-        rix = ops.ReverseIndex(row_ptr, col_q, None, b, q_proxy.shape[1], s, ctx.top_k_blocks)
+        rix = ops.ReverseIndex(row_ptr, col_q, edge_pos, b, q_proxy.shape[1], s, ctx.top_k_blocks)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
                                                       ctx.scale, rix, grad_kl, status=status)

@@ -20,4 +20,53 @@ __host__ __device__ __forceinline__ int64_t dense_row_offset(int j, int S) {
     return static_cast<int64_t>(j) * S - static_cast<int64_t>(kBlock) * j * (j - 1) / 2;
 }
 
+// -------------------------------------------------------------------------------------------
+// Work decomposition shared by the forward and the backward.
+//
+// A reverse-index row (batch, proxy head, key block j) can hold anything from one chunk of 128
+// query rows to all S - 128*j later rows (a "sink" block).  To keep the persistent CTAs balanced a
+// row is cut into sub-units of at most kChunksPerSubUnit chunks.  The number of rows is only known
+// on the device, so the sub-units are enumerated for the worst case (NB - j chunks) and a CTA that
+// draws a sub-unit beyond the real end of its row simply skips it.
+//
+// Order: (batch, KV head) group major, then key block ascending (long rows first), then sub-unit,
+// then proxy head of the group.  Group-major order keeps the rows that the active CTAs gather from
+// and reduce into (a few heads of Q, dO, dQ) resident in L2.
+// -------------------------------------------------------------------------------------------
+constexpr int kChunksPerSubUnit = 8;
+
+// sum_{R=1..n} ceil(R / C)
+__host__ __device__ __forceinline__ int64_t ceil_sum(int n, int C) {
+    const int64_t a = n / C, b = n % C;
+    return C * (a * (a + 1) / 2) + (a + 1) * b;
+}
+// sub-units of key blocks 0..j-1 of one (group, proxy head): sum_{j'<j} ceil((NB-j')/C)
+__host__ __device__ __forceinline__ int64_t subunits_before(int j, int NB, int C) {
+    return ceil_sum(NB, C) - ceil_sum(NB - j, C);
+}
+__host__ __device__ __forceinline__ int64_t subunits_per_group(int NB, int ppk, int C) {
+    return ceil_sum(NB, C) * ppk;
+}
+
+struct SubUnit {
+    int g, j, pp, chunk0;
+};
+__device__ __forceinline__ SubUnit decode_subunit(int64_t u, int NB, int ppk) {
+    constexpr int C = kChunksPerSubUnit;
+    const int64_t per_group = subunits_per_group(NB, ppk, C);
+    SubUnit su;
+    su.g = static_cast<int>(u / per_group);
+    const int64_t r = u % per_group;
+    su.pp = static_cast<int>(r % ppk);
+    const int64_t x = r / ppk;
+    int lo = 0, hi = NB - 1;   // largest j with subunits_before(j) <= x
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (subunits_before(mid, NB, C) <= x) lo = mid; else hi = mid - 1;
+    }
+    su.j = lo;
+    su.chunk0 = static_cast<int>(x - subunits_before(lo, NB, C)) * C;
+    return su;
+}
+
 }  // namespace fmsa

@@ -22,6 +22,10 @@ constexpr int kBlock = 128;              // tokens per key / query block
 constexpr int kHeadDim = 128;            // head dimension (fixed by the reference: flash_msa.py:54-55)
 constexpr int kTileBytes = 128 * 128 * 2;
 constexpr int kPanelBytes = 128 * 64 * 2;
+#ifndef FMSA_SPIN_SLEEP_NS
+#define FMSA_SPIN_SLEEP_NS 100
+#endif
+constexpr unsigned kSpinSleepNs = FMSA_SPIN_SLEEP_NS;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -76,6 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(kSpinSleepNs);   // keep the pollers off the shared-memory pipe the tensor core reads through
         }
         if (global_timer_ns() - t0 > 2000000000ull) return false;
     }
@@ -135,31 +140,51 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int ks) {
     return umma_desc(tile + ks * 2048, kPanelBytes, 1024);
 }
 
+// `elect` != 0 selects the lane that really issues.  The predicate sits inside the instruction so
+// that a whole warp can run the issue sequence without diverging: a lone lane that branches away
+// from its warp after a block barrier was measured to be scheduled thousands of cycles late.
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
+                                          uint32_t accumulate, uint32_t elect = 1u) {
     asm volatile(
         "{\n"
-        ".reg .pred p;\n"
+        ".reg .pred p, q;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "setp.ne.b32 q, %5, 0;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
         "}\n" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(elect)
         : "memory");
 }
 // Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void umma_commit(uint32_t bar, uint32_t elect = 1u) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %1, 0;\n"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n" ::"r"(bar),
+        "r"(elect)
+        : "memory");
 }
 
 // One full 128x128x128 product D (+)= A * B^T issued by the calling thread (8 instructions).
+// The descriptors of the eight reduction steps differ from the first one only in the 14-bit
+// address field (a tile lies below 256 KB, so the field never carries): K-major steps advance by
+// 32 bytes inside a panel and jump to the second panel after four steps; MN-major steps advance
+// by 16 rows = 2048 bytes.  Adding the encoded step to the low word keeps the issue loop at a few
+// instructions per MMA, which matters because a single thread feeds the tensor core.
 template <bool A_MN, bool B_MN>
-__device__ __forceinline__ void umma_tile_128(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, bool accumulate) {
+__device__ __forceinline__ void umma_tile_128(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, bool accumulate,
+                                              uint32_t elect = 1u) {
     constexpr uint32_t idesc = umma_idesc(128, A_MN, B_MN);
+    const uint64_t a0 = A_MN ? desc_mnmajor(a_tile, 0) : desc_kmajor(a_tile, 0);
+    const uint64_t b0 = B_MN ? desc_mnmajor(b_tile, 0) : desc_kmajor(b_tile, 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t ad = A_MN ? desc_mnmajor(a_tile, ks) : desc_kmajor(a_tile, ks);
-        const uint64_t bd = B_MN ? desc_mnmajor(b_tile, ks) : desc_kmajor(b_tile, ks);
-        umma_bf16(d_tmem, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+        constexpr uint32_t kPanel = kPanelBytes >> 4;
+        const uint32_t astep = A_MN ? ks * (2048u >> 4) : ((ks >> 2) * kPanel + (ks & 3) * 2u);
+        const uint32_t bstep = B_MN ? ks * (2048u >> 4) : ((ks >> 2) * kPanel + (ks & 3) * 2u);
+        umma_bf16(d_tmem, a0 + astep, b0 + bstep, idesc, (accumulate || ks > 0) ? 1u : 0u, elect);
     }
 }
 
@@ -176,6 +201,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }
@@ -229,6 +263,36 @@ __device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat
     }
 }
 
+// Lean 512-thread variants used by the attention kernels.  Thread `tid` always moves the same
+// 16-byte chunk column of rows tid/16 + 32k (k = 0..3), so its swizzled destination offset is a
+// per-thread constant plus k * 4096 bytes; only the source row changes.
+struct GatherLane {
+    uint32_t dst_off;   // swizzled offset of (row tid/16, chunk tid%16) inside a tile
+    int r0;             // tid / 16
+    int col;            // element offset of the chunk inside the 128-element row
+};
+__device__ __forceinline__ GatherLane make_gather_lane(int tid) {
+    GatherLane g;
+    g.r0 = tid >> 4;
+    g.col = (tid & 15) * 8;
+    g.dst_off = swz_offset(g.r0, tid & 15);
+    return g;
+}
+__device__ __forceinline__ void gather_tile_512(uint32_t tile, const __nv_bfloat16* base, int64_t stride, const int* rows,
+                                                const GatherLane& g) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int row = rows[g.r0 + 32 * k];
+        const bool ok = row >= 0;
+        cp_async_16(tile + g.dst_off + k * 4096, base + static_cast<int64_t>(ok ? row : 0) * stride + g.col, ok);
+    }
+}
+__device__ __forceinline__ void load_tile_512(uint32_t tile, const __nv_bfloat16* base, int64_t stride, const GatherLane& g) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        cp_async_16(tile + g.dst_off + k * 4096, base + static_cast<int64_t>(g.r0 + 32 * k) * stride + g.col, true);
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA: 2-D tile load (64 columns x 128 rows box, SWIZZLE_128B) signalled on an mbarrier
 // ---------------------------------------------------------------------------------------------
@@ -269,6 +333,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// Stores 16 accumulator values of a TRANSPOSED tile (this lane = head-dimension index d, value i =
+// output row row0+i) as bf16: the 32 lanes of a warp write 64 contiguous bytes of one output row per
+// instruction.  `dst` points at (row row0, element d); rows are `rstride` elements apart; rows >=
+// nvalid are skipped (the test is uniform over the warp).  (Exchanging values between lane pairs
+// to write packed 4-byte pairs was measured slower than one bf16 per lane.)
+__device__ __forceinline__ void store_transposed_bf16_16(__nv_bfloat16* dst, int64_t rstride, const uint32_t (&v)[16],
+                                                         int row0, int nvalid) {
+    if (row0 + 16 <= nvalid) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i * rstride] = __float2bfloat16_rn(__uint_as_float(v[i]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (row0 + i < nvalid) dst[i * rstride] = __float2bfloat16_rn(__uint_as_float(v[i]));
+    }
+}
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");

@@ -20,6 +20,8 @@
 // flash_msa/flash_msa.py:99-125 (delta, 1/(B*Hp*S), grad_kl applied afterwards on the device).
 // `dense` mode is the warmup backward (flash_msa/warmup/msa_backward_cutedsl_warmup.py:117-191):
 // every causal (query block, key block) pair, with the schedule implied instead of built on the host.
+#include <cuda_fp16.h>
+
 #include "host_common.h"
 #include "msa_common.cuh"
 #include "sm100.cuh"
@@ -37,45 +39,73 @@ struct BwdParams {
     const float *lse, *lse_proxy, *delta;   // [B,Hq,S], [B,Hp,S], [B,Hq,S]
     const int32_t* row_ptr;
     const int32_t* col_q;
-    float *dq_acc, *dqp_acc, *dkp_acc;      // fp32 [B,Hq,S,128], [B,Hp,S,128], [B,Hpkv,S,128], zero-initialised
-    __nv_bfloat16 *dk, *dv;                 // [B,Hkv,S,128]
+    __nv_bfloat16* dq_part;    // [(edge - edge_base) * mpp + head][128]: per-edge dQ contributions
+    __nv_bfloat16* dqp_part;   // [(edge - edge_base)][128]: per-edge dQp contributions (already * scale/(B*Hp*S))
+    // fp32, zero-initialised: [B,Hpkv,S,128], [B,Hkv,S,128] x2
+    float *dkp_acc, *dk_acc, *dv_acc;
     int32_t* counter;
     int32_t* status;
     int S, NB, Hq, Hkv, Hp, Hpkv, mpp, ppk, pg;
-    int units_g;     // number of (batch, KV head) groups
+    int g_begin, G;
+    int64_t n_subunits;
     int with_kl, dense;
     float scale, scale_log2e, kl_out_scale;   // kl_out_scale = scale / (B*Hp*S)
 };
 
 struct BwdSmem {
-    uint64_t bar_kv, bar_a, bar_b;
+    uint64_t bar_kv, bar_a, bar_dq, bar_dv, bar_dk;
     uint32_t tmem_slot;
     int32_t unit;
-    int32_t rows[2][128];
+    int32_t rows[3][128];
 };
 
-constexpr int kBwdThreads = 256;
-constexpr size_t kBwdSmemBytes = 6 * kTileBytes + 1024 + sizeof(BwdSmem);
+constexpr int kBwdWorkers = 512;            // 16 worker warps
+constexpr int kBwdThreads = kBwdWorkers + 32;   // + one warp whose lane 0 only issues tcgen05.mma
+constexpr size_t kBwdSmemBytes = 7 * kTileBytes + 1024 + sizeof(BwdSmem);
 
+// Roles.  Worker warp w (0..15) may read TMEM lanes 32*(w%4)..+31 and owns the 32 accumulator
+// columns starting at 32*(w/4).  Warp 16 is the MMA issuer: a thread that issues tcgen05.mma is held
+// while the tensor core's queue is full, so it must not carry any other work.
+//
+// Shared memory: K_j, V_j (resident), two Q buffers (rows gathered one tile ahead), one dO buffer
+// (refilled as soon as dV has consumed it), P and dS.
+// TMEM (512 columns): [0,128) S, then dKp^T in a proxy tile; [128,256) dP, then dQ^T / dQp^T;
+// [256,384) dV^T; [384,512) dK^T.
+//
+// Products of the second group are issued TRANSPOSED (M = head dimension): a TMEM lane is then a
+// head-dimension index and a column a row of the output, so the 32 lanes of a warp write 32
+// consecutive elements of ONE output row per instruction.
+//
+// Per tile:   issuer:  [S ahead] dP | ......... | dQ^T dV^T dK^T S(next) |
+//             workers: gather Q(next), wait | P, dS | wait dQ, store it; refill dO; (dKp) |
+// dQ and dQp leave the kernel as bf16 per-edge partial rows (summed per query row by
+// bwd_combine_kernel): fp32 atomics for them would move ~6 GB through the L2 atomic units per step.
 __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
                                                                     const BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t tile_k = tiles, tile_v = tiles + kTileBytes;
-    const uint32_t tile_q = tiles + 2 * kTileBytes, tile_do = tiles + 3 * kTileBytes;
-    const uint32_t tile_p = tiles + 4 * kTileBytes, tile_ds = tiles + 5 * kTileBytes;
-    BwdSmem* sm = reinterpret_cast<BwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 6 * kTileBytes);
+    const uint32_t tile_q0 = tiles + 2 * kTileBytes, tile_do = tiles + 4 * kTileBytes;
+    const uint32_t tile_p = tiles + 5 * kTileBytes, tile_ds = tiles + 6 * kTileBytes;
+    BwdSmem* sm = reinterpret_cast<BwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 7 * kTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quarter = warp & 3, half = warp >> 2;
-    const int row = quarter * 32 + lane, c0 = half * 64;
-    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_a = smem_u32(&sm->bar_a), bar_b = smem_u32(&sm->bar_b);
+    const bool worker = warp < 16;
+    const bool issuer = (warp == 16);            // the whole warp runs the issue sequence ...
+    const uint32_t elect = (lane == 0) ? 1u : 0u;   // ... and only this lane's instructions take effect
+    const int quarter = warp & 3, cg = (warp >> 2) & 3;
+    const int row = quarter * 32 + lane, c0 = cg * 32;
+    const GatherLane glane = make_gather_lane(tid & 511);
+    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_a = smem_u32(&sm->bar_a), bar_dq = smem_u32(&sm->bar_dq);
+    const uint32_t bar_dv = smem_u32(&sm->bar_dv), bar_dk = smem_u32(&sm->bar_dk);
 
     if (tid == 0) {
         mbar_init(bar_kv, 1);
         mbar_init(bar_a, 1);
-        mbar_init(bar_b, 1);
+        mbar_init(bar_dq, 1);
+        mbar_init(bar_dv, 1);
+        mbar_init(bar_dk, 1);
         fence_mbar_init();
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
@@ -92,297 +122,467 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
 
     const int hpc = P.mpp + (P.with_kl ? 1 : 0);
     const float inv_mpp = 1.f / static_cast<float>(P.mpp);
-    uint32_t ph_kv = 0, ph_a = 0, ph_b = 0;
-    bool bad = false;
+    const int64_t edge_base = P.dense ? dense_edge_base(static_cast<int64_t>(P.g_begin) * P.ppk, P.S, P.NB)
+                                      : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
+    uint32_t ph_kv = 0, ph_a = 0, ph_dq = 0, ph_dv = 0, ph_dk = 0;
+    bool bad = false;   // a bounded wait gave up: later waits are skipped, the status word is set at the end
 
     for (;;) {
         if (tid == 0) sm->unit = atomicAdd(P.counter, 1);
         __syncthreads();
         const int u = sm->unit;
         __syncthreads();
-        if (u >= P.units_g * P.NB) break;
-        const int j = u / P.units_g;
-        const int g = u % P.units_g;
+        if (u >= P.n_subunits) break;
+        const SubUnit su = decode_subunit(u, P.NB, P.ppk);
+        const int j = su.j;
+        const int g = P.g_begin + su.g;
         const int b = g / P.Hkv, kvh = g % P.Hkv;
+        const int p = kvh * P.ppk + su.pp;
+        const int kph = p / P.pg;
+        const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
+        int64_t e0;
+        int n;
+        if (P.dense) {
+            e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(j, P.S);
+            n = P.S - j * kBlock;
+        } else {
+            e0 = P.row_ptr[bp * P.NB + j];
+            n = P.row_ptr[bp * P.NB + j + 1] - static_cast<int>(e0);
+        }
+        const int chunk0 = su.chunk0;
+        const int chunk1 = min((n + kBlock - 1) / kBlock, chunk0 + kChunksPerSubUnit);
+        if (chunk1 <= chunk0) continue;   // this sub-unit lies beyond the end of the row
         if (tid == 0) {
             mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
             tma_load_tile(tile_k, &tmap_k, j * kBlock, kvh, b, bar_kv);
             tma_load_tile(tile_v, &tmap_v, j * kBlock, kvh, b, bar_kv);
         }
-        bool kv_ready = false;
-        bool kv_acc = false;   // dK/dV accumulators hold something
+        const int ntiles = (chunk1 - chunk0) * hpc;
+        const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
+        const __nv_bfloat16* do_b = P.dout + static_cast<int64_t>(b) * P.do_sb;
+        const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
+        const __nv_bfloat16* kp_blk = P.kp + static_cast<int64_t>(b) * P.kp_sb + static_cast<int64_t>(kph) * P.kp_sh +
+                                      static_cast<int64_t>(j) * kBlock * P.kp_ss;
 
-        for (int pp = 0; pp < P.ppk; ++pp) {
-            const int p = kvh * P.ppk + pp;
-            const int kph = p / P.pg;
-            const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
-            int64_t e0 = 0;
-            int n;
-            if (P.dense) {
-                n = P.S - j * kBlock;
-            } else {
-                e0 = P.row_ptr[bp * P.NB + j];
-                n = P.row_ptr[bp * P.NB + j + 1] - static_cast<int>(e0);
+        auto stage_rows = [&](int chunk, int rb) {
+            if (tid < kBlock) {
+                const int at = chunk * kBlock + tid;
+                int qid = -1;
+                if (at < n) {
+                    qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
+                    if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
+                        atomicMax(P.status, kStatusBadIndex);
+                        qid = -1;
+                    }
+                }
+                sm->rows[rb][tid] = qid;
             }
-            if (n <= 0) continue;
-            const int nchunks = (n + kBlock - 1) / kBlock;
-            const int ntiles = nchunks * hpc;
-            const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
-            const __nv_bfloat16* do_b = P.dout + static_cast<int64_t>(b) * P.do_sb;
-            const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
-            const __nv_bfloat16* kp_blk = P.kp + static_cast<int64_t>(b) * P.kp_sb + static_cast<int64_t>(kph) * P.kp_sh +
-                                          static_cast<int64_t>(j) * kBlock * P.kp_ss;
+        };
+        // Q rows of a tile (main head hh or the proxy head) into Q buffer `par` (workers only)
+        auto gather_q = [&](int hh, int rb, int par) {
+            const uint32_t dst = tile_q0 + par * kTileBytes;
+            if (hh < P.mpp)
+                gather_tile_512(dst, q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh, P.q_ss, sm->rows[rb], glane);
+            else
+                gather_tile_512(dst, qp_bp, P.qp_ss, sm->rows[rb], glane);
+        };
+        // dO rows of a main tile, or the proxy keys Kp_j of a proxy tile, into the dO buffer
+        auto gather_do = [&](int hh, int rb) {
+            if (hh < P.mpp)
+                gather_tile_512(tile_do, do_b + static_cast<int64_t>(p * P.mpp + hh) * P.do_sh, P.do_ss, sm->rows[rb], glane);
+            else
+                load_tile_512(tile_do, kp_blk, P.kp_ss, glane);
+        };
 
-            auto stage_rows = [&](int chunk) {
-                if (tid < kBlock) {
-                    const int at = chunk * kBlock + tid;
-                    int qid = -1;
-                    if (at < n) {
-                        qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
-                        if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
-                            atomicMax(P.status, kStatusBadIndex);
-                            qid = -1;
+        // ---- prologue: operands of tile 0, S of tile 0 ----
+        stage_rows(chunk0, 0);
+        if (ntiles > 1 && hpc == 1) stage_rows(chunk0 + 1, 1);
+        __syncthreads();
+        if (worker) {
+            gather_q(0, 0, 0);
+            gather_do(0, 0);
+            cp_async_commit();
+            cp_async_wait<0>();
+            fence_async_smem();
+        }
+        __syncthreads();
+        if (issuer) {
+            if (!bad) bad = !mbar_wait(bar_kv, ph_kv);
+            tc_fence_after_sync();
+            umma_tile_128<false, false>(t_s, tile_q0, tile_k, false, elect);   // S(0); tile 0 is always a main head
+        }
+        ph_kv ^= 1;
+        bool s_issued = true;
+        bool kv_acc = false;       // dK/dV accumulators hold something
+        bool dk_pending = false;   // bar_dk of the previous tile has not been waited for yet
+
+        // sum over the main heads of P for this thread's 32 columns: the KL teacher.  Kept as packed
+        // fp16 pairs (values in [0,1], at most Hq/Hp addends; the result is rounded to bf16 anyway).
+        __half2 teacher[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) teacher[i] = __floats2half2_rn(0.f, 0.f);
+
+        int hh = 0, chunk = chunk0, rb = 0;   // head, chunk and row-list buffer of the current tile
+        for (int t = 0; t < ntiles; ++t) {
+            const bool is_proxy = hh == P.mpp;
+            const bool has_next = t + 1 < ntiles;
+            // the next two tiles, without divisions
+            int hh1 = hh + 1, chunk_1 = chunk, rb1 = rb;
+            if (hh1 == hpc) {
+                hh1 = 0;
+                ++chunk_1;
+                rb1 = (rb == 2) ? 0 : rb + 1;
+            }
+            int hh2 = hh1 + 1, chunk_2 = chunk_1, rb2 = rb1;
+            if (hh2 == hpc) {
+                hh2 = 0;
+                ++chunk_2;
+                rb2 = (rb1 == 2) ? 0 : rb1 + 1;
+            }
+            const bool next_proxy = has_next && (hh1 == P.mpp);
+            const uint32_t qbuf = tile_q0 + (t & 1) * kTileBytes;
+            const int nrows = min(kBlock, n - chunk * kBlock);
+            const int64_t slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
+
+            // ---- A: issuer: S (unless issued ahead) and dP;  workers: fetch the next tile's Q rows ----
+            if (issuer) {
+                tc_fence_after_sync();
+                if (is_proxy) {
+                    umma_tile_128<false, false>(t_s, qbuf, tile_do, false, elect);              // Sp = Qp_g Kp_j^T
+                } else {
+                    if (!s_issued) umma_tile_128<false, false>(t_s, qbuf, tile_k, false, elect);   // S  = Q_g K_j^T
+                    umma_tile_128<false, false>(t_dp, tile_do, tile_v, false, elect);           // dP = dO_g V_j^T
+                }
+                umma_commit(bar_a, elect);
+            }
+            if (worker) {
+                // per-row statistics: only the loads are issued here; they are consumed after the waits below
+                float raw_lse = INFINITY, row_delta = 0.f;   // +inf: exp2(-inf) = 0, a dead row contributes nothing
+                int limit = 127;
+                {
+                    const int qid = sm->rows[rb][row];
+                    if (qid >= 0) {
+                        if ((qid >> 7) == j) limit = qid & 127;
+                        if (is_proxy) {
+                            raw_lse = P.lse_proxy[bp * P.S + qid];
+                        } else {
+                            const int64_t at = (static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + qid;
+                            raw_lse = P.lse[at];
+                            row_delta = P.delta[at];
                         }
                     }
-                    sm->rows[chunk & 1][tid] = qid;
                 }
-            };
-            auto issue_gather = [&](int t) {
-                const int chunk = t / hpc, hh = t % hpc;
-                if (hh < P.mpp) {
-                    const int h = p * P.mpp + hh;
-                    gather_tile_async<kBwdThreads>(tile_q, q_b + static_cast<int64_t>(h) * P.q_sh, P.q_ss, sm->rows[chunk & 1], tid);
-                    gather_tile_async<kBwdThreads>(tile_do, do_b + static_cast<int64_t>(h) * P.do_sh, P.do_ss, sm->rows[chunk & 1], tid);
-                } else {
-                    gather_tile_async<kBwdThreads>(tile_q, qp_bp, P.qp_ss, sm->rows[chunk & 1], tid);
-                    load_tile_async<kBwdThreads>(tile_do, kp_blk, P.kp_ss, tid);
+                if (dk_pending) {          // dK^T of the previous tile still reads the other Q buffer
+                    if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
+                    ph_dk ^= 1;
                 }
+                if (has_next) gather_q(hh1, rb1, (t + 1) & 1);
                 cp_async_commit();
-            };
-
-            stage_rows(0);
-            __syncthreads();
-            issue_gather(0);
-
-            float teacher[64];
-#pragma unroll
-            for (int i = 0; i < 64; ++i) teacher[i] = 0.f;
-
-            for (int t = 0; t < ntiles; ++t) {
-                const int chunk = t / hpc, hh = t % hpc;
-                const bool is_proxy = hh == P.mpp;
-                const int qid = sm->rows[chunk & 1][row];
-                const bool live = qid >= 0;
-                const int limit = (live && (qid >> 7) == j) ? (qid & 127) : 127;
-                // per-row statistics: issue the loads before waiting on anything
-                float row_lse = 0.f, row_delta = 0.f;
-                if (live) {
-                    if (is_proxy) {
-                        row_lse = P.lse_proxy[bp * P.S + qid];
-                    } else {
-                        const int64_t at = (static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + qid;
-                        row_lse = P.lse[at];
-                        row_delta = P.delta[at];
-                    }
-                }
-                cp_async_wait<0>();
-                fence_async_smem();
-                __syncthreads();
-                if (tid == 0) {
-                    if (!kv_ready) bad |= !mbar_wait(bar_kv, ph_kv);
-                    tc_fence_after_sync();
-                    if (is_proxy) {
-                        umma_tile_128<false, false>(t_s, tile_q, tile_do, false);           // Sp = Qp_g Kp_j^T
-                    } else {
-                        umma_tile_128<false, false>(t_s, tile_q, tile_k, false);            // S  = Q_g K_j^T
-                        umma_tile_128<false, false>(t_dp, tile_do, tile_v, false);          // dP = dO_g V_j^T
-                    }
-                    umma_commit(bar_a);
-                }
-                if (!kv_ready) {
-                    kv_ready = true;
-                    ph_kv ^= 1;
-                }
-                bad |= !mbar_wait(bar_a, ph_a);
+                if (!bad) bad = !mbar_wait(bar_a, ph_a);
                 ph_a ^= 1;
-                if (__syncthreads_or(bad)) {
-                    bad = true;
-                    goto abort;
-                }
                 tc_fence_after_sync();
+                if (t + 2 < ntiles && chunk_2 != chunk_1) stage_rows(chunk_2, rb2);
 
-                const float neg_lse = -row_lse * kLog2e;
-                if (!is_proxy) {
+                // ---- B: P, dS (or dSp) for this thread's (row, 32 columns) ----
+                // Only the first chunk of a reverse-index row can hold rows of the key block itself
+                // (they are the smallest query positions), so only there the causal mask is needed.
+                const bool masked = (chunk == 0);
+                const float neg_lse = -raw_lse * kLog2e;
 #pragma unroll
-                    for (int c = 0; c < 64; c += 32) {
-                        uint32_t sv[32], dv[32];
-                        tmem_ld32(tmem_addr(t_s, quarter, c0 + c), sv);
-                        tmem_ld32(tmem_addr(t_dp, quarter, c0 + c), dv);
-                        tmem_ld_wait();
-                        uint32_t pk[16], dk[16];
+                for (int c = 0; c < 32; c += 16) {
+                    uint32_t sv[16], dv[16];
+                    tmem_ld16(tmem_addr(t_s, quarter, c0 + c), sv);
+                    if (!is_proxy) tmem_ld16(tmem_addr(t_dp, quarter, c0 + c), dv);
+                    tmem_ld_wait();
+                    uint32_t pk[8], dk[8];
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float p0 = fast_exp2(fmaf(__uint_as_float(sv[i]), P.scale_log2e, neg_lse));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), P.scale_log2e, neg_lse));
-                            p0 = (live && c0 + c + i <= limit) ? p0 : 0.f;
-                            p1 = (live && c0 + c + i + 1 <= limit) ? p1 : 0.f;
+                    for (int i = 0; i < 16; i += 2) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(sv[i]), P.scale_log2e, neg_lse));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), P.scale_log2e, neg_lse));
+                        if (masked) {
+                            p0 = (c0 + c + i <= limit) ? p0 : 0.f;
+                            p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
+                        }
+                        if (!is_proxy) {
                             const float d0 = p0 * (__uint_as_float(dv[i]) - row_delta);
                             const float d1 = p1 * (__uint_as_float(dv[i + 1]) - row_delta);
-                            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                            pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+                            pk[i >> 1] = pack_bf16(p0, p1);
                             dk[i >> 1] = pack_bf16(d0, d1);
-                            if (P.with_kl) {
-                                teacher[c + i] += __low2float(pb);
-                                teacher[c + i + 1] += __high2float(pb);
-                            }
-                        }
-#pragma unroll
-                        for (int k8 = 0; k8 < 4; ++k8) {
-                            const uint32_t off = swz_offset(row, ((c0 + c) >> 3) + k8);
-                            st_shared_v4(tile_p + off, pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
-                            st_shared_v4(tile_ds + off, dk[4 * k8], dk[4 * k8 + 1], dk[4 * k8 + 2], dk[4 * k8 + 3]);
+                            teacher[(c + i) >> 1] = __hadd2(teacher[(c + i) >> 1], __floats2half2_rn(p0, p1));
+                        } else {
+                            const float2 tt = __half22float2(teacher[(c + i) >> 1]);
+                            dk[i >> 1] = pack_bf16(p0 - tt.x * inv_mpp, p1 - tt.y * inv_mpp);
+                            teacher[(c + i) >> 1] = __floats2half2_rn(0.f, 0.f);
                         }
                     }
-                } else {
 #pragma unroll
-                    for (int c = 0; c < 64; c += 32) {
-                        uint32_t sv[32];
-                        tmem_ld32(tmem_addr(t_s, quarter, c0 + c), sv);
-                        tmem_ld_wait();
-                        uint32_t dk[16];
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float p0 = fast_exp2(fmaf(__uint_as_float(sv[i]), P.scale_log2e, neg_lse));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), P.scale_log2e, neg_lse));
-                            p0 = (live && c0 + c + i <= limit) ? p0 : 0.f;
-                            p1 = (live && c0 + c + i + 1 <= limit) ? p1 : 0.f;
-                            dk[i >> 1] = pack_bf16(p0 - teacher[c + i] * inv_mpp, p1 - teacher[c + i + 1] * inv_mpp);
-                            teacher[c + i] = 0.f;
-                            teacher[c + i + 1] = 0.f;
-                        }
-#pragma unroll
-                        for (int k8 = 0; k8 < 4; ++k8)
-                            st_shared_v4(tile_ds + swz_offset(row, ((c0 + c) >> 3) + k8), dk[4 * k8], dk[4 * k8 + 1],
-                                         dk[4 * k8 + 2], dk[4 * k8 + 3]);
+                    for (int k8 = 0; k8 < 2; ++k8) {
+                        const uint32_t off = swz_offset(row, ((c0 + c) >> 3) + k8);
+                        if (!is_proxy) st_shared_v4(tile_p + off, pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
+                        st_shared_v4(tile_ds + off, dk[4 * k8], dk[4 * k8 + 1], dk[4 * k8 + 2], dk[4 * k8 + 3]);
                     }
                 }
+                cp_async_wait<0>();      // Q rows of the next tile have landed
                 fence_async_smem();
-                tc_fence_before_sync();
-                __syncthreads();
-                if (tid == 0) {
-                    tc_fence_after_sync();
-                    if (is_proxy) {
-                        umma_tile_128<false, true>(t_s, tile_ds, tile_do, false);    // dQp = dSp Kp_j
-                        umma_tile_128<true, true>(t_dp, tile_ds, tile_q, false);     // dKp = dSp^T Qp_g
-                    } else {
-                        umma_tile_128<true, true>(t_dv, tile_p, tile_do, kv_acc);    // dV += P^T dO_g
-                        umma_tile_128<true, true>(t_dk, tile_ds, tile_q, kv_acc);    // dK += dS^T Q_g
-                        umma_tile_128<false, true>(t_s, tile_ds, tile_k, false);     // dQ  = dS K_j
-                    }
-                    umma_commit(bar_b);
-                }
-                if (!is_proxy) kv_acc = true;
-                bad |= !mbar_wait(bar_b, ph_b);
-                ph_b ^= 1;
-                if (__syncthreads_or(bad)) {
-                    bad = true;
-                    goto abort;
-                }
-                tc_fence_after_sync();
-                // the operand tiles are free again: start fetching the next tile
-                if (t + 1 < ntiles) {
-                    const int nchunk = (t + 1) / hpc;
-                    if (nchunk != chunk) {
-                        stage_rows(nchunk);
-                        __syncthreads();
-                    }
-                    issue_gather(t + 1);
-                }
-                // epilogue: reduce dQ (or dQp and dKp) into the fp32 buffers
-                {
-                    const float osc = is_proxy ? P.kl_out_scale : P.scale;
-                    float* dst = nullptr;
-                    if (live) {
-                        dst = is_proxy ? P.dqp_acc + (bp * P.S + qid) * kHeadDim
-                                       : P.dq_acc + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + qid) * kHeadDim;
-                    }
-#pragma unroll 1
-                    for (int c = 0; c < 64; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(t_s, quarter, c0 + c), v);
-                        tmem_ld_wait();
-                        if (live) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4)
-                                red_add_v4(dst + c0 + c + i, __uint_as_float(v[i]) * osc, __uint_as_float(v[i + 1]) * osc,
-                                           __uint_as_float(v[i + 2]) * osc, __uint_as_float(v[i + 3]) * osc);
-                        }
-                    }
-                    if (is_proxy) {
-                        float* kdst = P.dkp_acc + ((static_cast<int64_t>(b) * P.Hpkv + kph) * P.S + j * kBlock + row) * kHeadDim;
-#pragma unroll 1
-                        for (int c = 0; c < 64; c += 32) {
-                            uint32_t v[32];
-                            tmem_ld32(tmem_addr(t_dp, quarter, c0 + c), v);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4)
-                                red_add_v4(kdst + c0 + c + i, __uint_as_float(v[i]) * osc, __uint_as_float(v[i + 1]) * osc,
-                                           __uint_as_float(v[i + 2]) * osc, __uint_as_float(v[i + 3]) * osc);
-                        }
-                    }
-                }
                 tc_fence_before_sync();
             }
             __syncthreads();
-        }
-        if (!kv_ready) {
-            if (tid == 0) bad |= !mbar_wait(bar_kv, ph_kv);
-            ph_kv ^= 1;
-            if (__syncthreads_or(bad)) {
-                bad = true;
-                goto abort;
+
+            // ---- C: issuer: dQ^T first (so its store overlaps the rest), dV^T, dK^T, S of the next main tile ----
+            const bool s_ahead = has_next && !next_proxy && !is_proxy;
+            if (issuer) {
+                tc_fence_after_sync();
+                if (is_proxy) {
+                    umma_tile_128<true, false>(t_dp, tile_do, tile_ds, false, elect);   // dQp^T = Kp_j^T dSp^T
+                    umma_commit(bar_dq, elect);
+                    umma_commit(bar_dv, elect);
+                    umma_tile_128<true, true>(t_s, qbuf, tile_ds, false, elect);        // dKp^T = Qp_g^T dSp
+                    umma_commit(bar_dk, elect);
+                } else {
+                    umma_tile_128<true, false>(t_dp, tile_k, tile_ds, false, elect);    // dQ^T  = K_j^T dS^T
+                    umma_commit(bar_dq, elect);
+                    umma_tile_128<true, true>(t_dv, tile_do, tile_p, kv_acc, elect);    // dV^T += dO_g^T P
+                    umma_commit(bar_dv, elect);
+                    umma_tile_128<true, true>(t_dk, qbuf, tile_ds, kv_acc, elect);      // dK^T += Q_g^T dS
+                    umma_commit(bar_dk, elect);
+                    if (s_ahead) umma_tile_128<false, false>(t_s, tile_q0 + ((t + 1) & 1) * kTileBytes, tile_k, false, elect);
+                }
             }
+            if (!is_proxy) kv_acc = true;
+            s_issued = s_ahead;
+            dk_pending = true;
+
+            // ---- D: workers: store dQ^T, refill the dO buffer, reduce dKp^T ----
+            if (worker) {
+                if (!bad) bad = !mbar_wait(bar_dq, ph_dq);
+                ph_dq ^= 1;
+                tc_fence_after_sync();
+                {
+                    // this thread: head-dimension index `row`, output rows = tile rows c0 .. c0+31.
+                    // The factor (scale, or scale/(B*Hp*S) for the proxy) is applied by the combine kernel.
+                    __nv_bfloat16* dst = is_proxy ? P.dqp_part + (slot0 + c0) * kHeadDim + row
+                                                  : P.dq_part + ((slot0 + c0) * P.mpp + hh) * kHeadDim + row;
+                    const int64_t rstride = is_proxy ? kHeadDim : static_cast<int64_t>(P.mpp) * kHeadDim;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(tmem_addr(t_dp, quarter, c0 + c), v);
+                        tmem_ld_wait();
+                        store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, nrows);
+                    }
+                }
+                if (!bad) bad = !mbar_wait(bar_dv, ph_dv);
+                ph_dv ^= 1;
+                if (has_next) gather_do(hh1, rb1);
+                cp_async_commit();
+                if (is_proxy) {
+                    if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
+                    ph_dk ^= 1;
+                    tc_fence_after_sync();
+                    float* kbase = P.dkp_acc + ((static_cast<int64_t>(b) * P.Hpkv + kph) * P.S + j * kBlock + c0) * kHeadDim + row;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(tmem_addr(t_s, quarter, c0 + c), v);
+                        tmem_ld_wait();
+#pragma unroll
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) atomicAdd(kbase + (c + i) * kHeadDim, __uint_as_float(v[i]));
+                    }
+                }
+                cp_async_wait<0>();      // dO rows (or Kp_j) of the next tile have landed
+                fence_async_smem();
+                tc_fence_before_sync();
+            }
+            if (is_proxy) dk_pending = false;
+            __syncthreads();
+            hh = hh1;
+            chunk = chunk_1;
+            rb = rb1;
         }
-        // unit epilogue: the unit owns dK_j and dV_j
-        {
+        // ---- sub-unit epilogue: add this sub-unit's share of dK_j and dV_j ----
+        if (worker) {
+            if (dk_pending) {
+                if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
+                ph_dk ^= 1;
+            }
             tc_fence_after_sync();
-            const int64_t at = ((static_cast<int64_t>(b) * P.Hkv + kvh) * P.S + j * kBlock + row) * kHeadDim + c0;
+            // accumulators are transposed: lane = head-dimension index, column = key row of the block
+            const int64_t at = ((static_cast<int64_t>(b) * P.Hkv + kvh) * P.S + j * kBlock) * kHeadDim + row;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
-                __nv_bfloat16* dst = (which == 0 ? P.dv : P.dk) + at;
-                const float osc = which == 0 ? 1.f : P.scale;
-#pragma unroll 1
-                for (int c = 0; c < 64; c += 32) {
-                    uint32_t v[32];
+                float* dst = (which == 0 ? P.dv_acc : P.dk_acc) + at;
+#pragma unroll
+                for (int c = 0; c < 32; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_addr(which == 0 ? t_dv : t_dk, quarter, c0 + c), v);
+                    tmem_ld_wait();
                     if (kv_acc) {
-                        tmem_ld32(tmem_addr(which == 0 ? t_dv : t_dk, quarter, c0 + c), v);
-                        tmem_ld_wait();
-                    } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = 0u;
-                    }
-#pragma unroll
-                    for (int k8 = 0; k8 < 4; ++k8) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(v[8 * k8 + 0]) * osc, __uint_as_float(v[8 * k8 + 1]) * osc);
-                        w.y = pack_bf16(__uint_as_float(v[8 * k8 + 2]) * osc, __uint_as_float(v[8 * k8 + 3]) * osc);
-                        w.z = pack_bf16(__uint_as_float(v[8 * k8 + 4]) * osc, __uint_as_float(v[8 * k8 + 5]) * osc);
-                        w.w = pack_bf16(__uint_as_float(v[8 * k8 + 6]) * osc, __uint_as_float(v[8 * k8 + 7]) * osc);
-                        *reinterpret_cast<uint4*>(dst + c + 8 * k8) = w;
+                        for (int i = 0; i < 16; ++i)
+                            atomicAdd(dst + static_cast<int64_t>(c0 + c + i) * kHeadDim, __uint_as_float(v[i]));
                     }
                 }
             }
             tc_fence_before_sync();
-            __syncthreads();
         }
+        __syncthreads();
     }
-abort:
     cp_async_wait<0>();
-    if (bad && tid == 0) atomicMax(P.status, kStatusWaitTimeout);
+    if (bad) atomicMax(P.status, kStatusWaitTimeout);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// -------------------------------------------------------------------------------------------
+// dq[b,h,q,:] = sum over the row's edges of dq_part;  dq_proxy likewise, times the upstream
+// gradient of kl_loss (a device scalar).  One warp per (batch*proxy head, query row).
+// -------------------------------------------------------------------------------------------
+struct BwdCombineParams {
+    const __nv_bfloat16* dq_part;
+    const __nv_bfloat16* dqp_part;
+    const int32_t* edge_pos;   // sparse: [B*Hp, S, Kb]
+    const int32_t* row_ptr;
+    __nv_bfloat16* dq;         // [B,Hq,S,128]
+    __nv_bfloat16* dqp;        // [B,Hp,S,128] or null
+    const float* grad_kl;      // device scalar or null (= 1)
+    float scale, kl_out_scale; // factors the backward kernel left out of its partial rows
+    int S, NB, Hq, Hp, mpp, ppk, Kb;
+    int g_begin, G, dense;
+};
+
+__global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams P) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;
+    if (w >= static_cast<int64_t>(P.G) * P.ppk * P.S) return;
+    const int64_t bp = bp0 + w / P.S;
+    const int q = static_cast<int>(w % P.S);
+    const int b = static_cast<int>(bp / P.Hp), p = static_cast<int>(bp % P.Hp);
+    const int64_t edge_base = P.dense ? dense_edge_base(bp0, P.S, P.NB) : static_cast<int64_t>(P.row_ptr[bp0 * P.NB]);
+    const int nslots = P.dense ? (q >> 7) + 1 : P.Kb;
+    const int32_t* erow = P.dense ? nullptr : P.edge_pos + (bp * P.S + q) * P.Kb;
+    auto slot_of = [&](int s) -> int64_t {
+        if (s >= nslots) return -1;
+        if (P.dense) return dense_edge_base(bp, P.S, P.NB) + dense_row_offset(s, P.S) + (q - s * kBlock) - edge_base;
+        const int e = erow[s];
+        return e < 0 ? -1 : static_cast<int64_t>(e) - edge_base;
+    };
+    const float gk = ((P.dqp && P.grad_kl) ? *P.grad_kl : 1.f) * P.kl_out_scale;
+    const int nheads = P.mpp + (P.dqp ? 1 : 0);
+    for (int hh = 0; hh < nheads; ++hh) {
+        const bool proxy = hh == P.mpp;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int s0 = 0; s0 < nslots; s0 += 32) {
+            const int64_t sl = slot_of(s0 + lane);
+            const int cnt = min(32, nslots - s0);
+#pragma unroll 4
+            for (int i = 0; i < cnt; ++i) {
+                const int64_t si = __shfl_sync(0xffffffffu, sl, i);
+                if (si < 0) continue;
+                const __nv_bfloat16* src = proxy ? P.dqp_part + si * kHeadDim : P.dq_part + (si * P.mpp + hh) * kHeadDim;
+                const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
+                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                a0 += __low2float(lo);
+                a1 += __high2float(lo);
+                a2 += __low2float(hi);
+                a3 += __high2float(hi);
+            }
+        }
+        uint2 o;
+        if (proxy) {
+            o.x = pack_bf16(a0 * gk, a1 * gk);
+            o.y = pack_bf16(a2 * gk, a3 * gk);
+            *reinterpret_cast<uint2*>(P.dqp + (bp * P.S + q) * kHeadDim + lane * 4) = o;
+        } else {
+            o.x = pack_bf16(a0 * P.scale, a1 * P.scale);
+            o.y = pack_bf16(a2 * P.scale, a3 * P.scale);
+            *reinterpret_cast<uint2*>(P.dq + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q) * kHeadDim + lane * 4) = o;
+        }
+    }
+}
+
+// Wide variant for Hq/Hp <= 8: one sweep over the contiguous mpp*256-byte record of each edge.
+constexpr int kWideMaxHeads = 8;
+__global__ void __launch_bounds__(256) bwd_combine_wide_kernel(const BwdCombineParams P) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;
+    if (w >= static_cast<int64_t>(P.G) * P.ppk * P.S) return;
+    const int64_t bp = bp0 + w / P.S;
+    const int q = static_cast<int>(w % P.S);
+    const int b = static_cast<int>(bp / P.Hp), p = static_cast<int>(bp % P.Hp);
+    const int64_t edge_base = P.dense ? dense_edge_base(bp0, P.S, P.NB) : static_cast<int64_t>(P.row_ptr[bp0 * P.NB]);
+    const int nslots = P.dense ? (q >> 7) + 1 : P.Kb;
+    const int32_t* erow = P.dense ? nullptr : P.edge_pos + (bp * P.S + q) * P.Kb;
+    auto slot_of = [&](int s) -> int64_t {
+        if (s >= nslots) return -1;
+        if (P.dense) return dense_edge_base(bp, P.S, P.NB) + dense_row_offset(s, P.S) + (q - s * kBlock) - edge_base;
+        const int e = erow[s];
+        return e < 0 ? -1 : static_cast<int64_t>(e) - edge_base;
+    };
+    const int nchunk = P.mpp * 16;
+    float acc[4][8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
+    float pa0 = 0.f, pa1 = 0.f, pa2 = 0.f, pa3 = 0.f;   // proxy row: lane owns columns 4*lane..+3
+    for (int s0 = 0; s0 < nslots; s0 += 32) {
+        const int64_t sl = slot_of(s0 + lane);
+        const int cnt = min(32, nslots - s0);
+#pragma unroll 2
+        for (int i = 0; i < cnt; ++i) {
+            const int64_t si = __shfl_sync(0xffffffffu, sl, i);
+            if (si < 0) continue;
+            const __nv_bfloat16* rec = P.dq_part + si * P.mpp * kHeadDim;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int ck = k * 32 + lane;
+                if (ck < nchunk) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
+                    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&u[e]);
+                        acc[k][2 * e] += __low2float(v2);
+                        acc[k][2 * e + 1] += __high2float(v2);
+                    }
+                }
+            }
+            if (P.dqp) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(P.dqp_part + si * kHeadDim + lane * 4);
+                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                pa0 += __low2float(lo);
+                pa1 += __high2float(lo);
+                pa2 += __low2float(hi);
+                pa3 += __high2float(hi);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int ck = k * 32 + lane;
+        if (ck < nchunk) {
+            const int hh = ck >> 4, col = (ck & 15) * 8;
+            uint4 o;
+            o.x = pack_bf16(acc[k][0] * P.scale, acc[k][1] * P.scale);
+            o.y = pack_bf16(acc[k][2] * P.scale, acc[k][3] * P.scale);
+            o.z = pack_bf16(acc[k][4] * P.scale, acc[k][5] * P.scale);
+            o.w = pack_bf16(acc[k][6] * P.scale, acc[k][7] * P.scale);
+            *reinterpret_cast<uint4*>(P.dq + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q) * kHeadDim + col) = o;
+        }
+    }
+    if (P.dqp) {
+        const float gk = (P.grad_kl ? *P.grad_kl : 1.f) * P.kl_out_scale;
+        uint2 o;
+        o.x = pack_bf16(pa0 * gk, pa1 * gk);
+        o.y = pack_bf16(pa2 * gk, pa3 * gk);
+        *reinterpret_cast<uint2*>(P.dqp + (bp * P.S + q) * kHeadDim + lane * 4) = o;
+    }
 }
 
 // -------------------------------------------------------------------------------------------
@@ -409,11 +609,11 @@ __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restr
     if (lane == 0) delta[(static_cast<int64_t>(b) * Hq + h) * S + q] = s;
 }
 
-// dst = bf16(src * factor), factor = *scale_ptr when given (the upstream kl gradient lives on the
+// dst = bf16(src * const_scale * factor), factor = *scale_ptr when given (the upstream kl gradient lives on the
 // device: flash_msa/flash_msa.py:122-125) else 1.
 __global__ void __launch_bounds__(256) cast_scaled_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n4,
-                                                          const float* __restrict__ scale_ptr) {
-    const float f = scale_ptr ? *scale_ptr : 1.f;
+                                                          const float* __restrict__ scale_ptr, float const_scale) {
+    const float f = (scale_ptr ? *scale_ptr : 1.f) * const_scale;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 v = reinterpret_cast<const float4*>(src)[i];
@@ -442,7 +642,8 @@ extern "C" int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* 
     return check_launch();
 }
 
-extern "C" int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, void* stream) {
+extern "C" int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale,
+                                void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(src && dst && n >= 0 && n % 4 == 0);
     FMSA_REQUIRE(aligned16(src) && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0);
@@ -451,22 +652,26 @@ extern "C" int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const fl
     int64_t grid = (n4 + 255) / 256;
     if (grid > 148 * 16) grid = 148 * 16;
     cast_scaled_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        src, static_cast<__nv_bfloat16*>(dst), n4, scale_ptr);
+        src, static_cast<__nv_bfloat16*>(dst), n4, scale_ptr, const_scale);
     return check_launch();
 }
 
 extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
                                const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out,
                                const float* lse, const float* lse_proxy, const float* delta, const int32_t* row_ptr,
-                               const int32_t* col_q, float* dq_acc, float* dqp_acc, float* dkp_acc, void* dk, void* dv,
-                               int32_t with_kl, int32_t dense, int32_t* counter, int32_t* status, void* stream) {
+                               const int32_t* col_q, void* dq_part, void* dqp_part, int64_t part_slots, float* dkp_acc,
+                               float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
+                               int32_t dense, int32_t* counter, int32_t* status, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(problem_ok(pb));
     FMSA_REQUIRE(q && k && v && d_out && q->ptr && k->ptr && v->ptr && d_out->ptr);
-    FMSA_REQUIRE(lse && delta && dq_acc && dk && dv && counter && status);
+    FMSA_REQUIRE(lse && delta && dq_part && dk_acc && dv_acc && counter && status);
     FMSA_REQUIRE(dense || (row_ptr && col_q));
-    FMSA_REQUIRE(!with_kl || (q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && lse_proxy && dqp_acc && dkp_acc));
+    FMSA_REQUIRE(!with_kl || (q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && lse_proxy && dqp_part && dkp_acc));
+    FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
+    FMSA_REQUIRE(dense || (pb->top_k_blocks >= 1 && pb->top_k_blocks <= pb->S / kBlock));
     FMSA_REQUIRE(pb->scale > 0.f);
+    if (part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
     FMSA_REQUIRE(tma_compatible(k->ptr, k->stride_b, k->stride_h, k->stride_s));
     FMSA_REQUIRE(tma_compatible(v->ptr, v->stride_b, v->stride_h, v->stride_s));
     FMSA_REQUIRE(tma_compatible(q->ptr, q->stride_b, q->stride_h, q->stride_s));
@@ -475,7 +680,8 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
         FMSA_REQUIRE(tma_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
         FMSA_REQUIRE(tma_compatible(k_proxy->ptr, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s));
     }
-    FMSA_REQUIRE(aligned16(dq_acc) && aligned16(dk) && aligned16(dv) && (!with_kl || (aligned16(dqp_acc) && aligned16(dkp_acc))));
+    FMSA_REQUIRE(aligned16(dq_part) && aligned16(dk_acc) && aligned16(dv_acc) &&
+                 (!with_kl || (aligned16(dqp_part) && aligned16(dkp_acc))));
     CUtensorMap tk, tv;
     if (!make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
         !make_tmap_bhsd(&tv, v->ptr, pb->B, pb->Hkv, pb->S, v->stride_b, v->stride_h, v->stride_s, 128))
@@ -497,12 +703,12 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     }
     P.lse = lse; P.lse_proxy = lse_proxy; P.delta = delta;
     P.row_ptr = row_ptr; P.col_q = col_q;
-    P.dq_acc = dq_acc; P.dqp_acc = dqp_acc; P.dkp_acc = dkp_acc;
-    P.dk = static_cast<__nv_bfloat16*>(dk); P.dv = static_cast<__nv_bfloat16*>(dv);
+    P.dq_part = static_cast<__nv_bfloat16*>(dq_part); P.dqp_part = static_cast<__nv_bfloat16*>(dqp_part);
+    P.dkp_acc = dkp_acc; P.dk_acc = dk_acc; P.dv_acc = dv_acc;
     P.counter = counter; P.status = status;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hkv = pb->Hkv; P.Hp = pb->Hp; P.Hpkv = pb->Hpkv;
     P.mpp = pb->Hq / pb->Hp; P.ppk = pb->Hp / pb->Hkv; P.pg = pb->Hp / pb->Hpkv;
-    P.units_g = pb->B * pb->Hkv;
+    P.g_begin = g_begin; P.G = g_count;
     P.with_kl = with_kl ? 1 : 0; P.dense = dense ? 1 : 0;
     P.scale = pb->scale; P.scale_log2e = pb->scale * kLog2e;
     P.kl_out_scale = pb->scale / (static_cast<float>(pb->B) * pb->Hp * pb->S);
@@ -515,8 +721,37 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
         cudaSuccess)
         return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
-    const int64_t units = static_cast<int64_t>(P.units_g) * P.NB;
-    const int grid = static_cast<int>(units < sms ? units : sms);
+    P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
+    FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
+    const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
     sparse_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tk, tv, P);
+    return check_launch();
+}
+
+extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part,
+                                       const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
+                                       const float* grad_kl, int32_t g_begin, int32_t g_count, int32_t dense,
+                                       void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(problem_ok(pb));
+    FMSA_REQUIRE(dq_part && dq);
+    FMSA_REQUIRE(dense || (edge_pos && row_ptr));
+    FMSA_REQUIRE(!dq_proxy || dqp_part);
+    FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
+    BwdCombineParams P;
+    P.dq_part = static_cast<const __nv_bfloat16*>(dq_part); P.dqp_part = static_cast<const __nv_bfloat16*>(dqp_part);
+    P.edge_pos = edge_pos; P.row_ptr = row_ptr;
+    P.dq = static_cast<__nv_bfloat16*>(dq); P.dqp = static_cast<__nv_bfloat16*>(dq_proxy); P.grad_kl = grad_kl;
+    P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hp = pb->Hp; P.mpp = pb->Hq / pb->Hp; P.ppk = pb->Hp / pb->Hkv;
+    P.Kb = pb->top_k_blocks; P.g_begin = g_begin; P.G = g_count; P.dense = dense ? 1 : 0;
+    P.scale = pb->scale;
+    P.kl_out_scale = pb->scale / (static_cast<float>(pb->B) * pb->Hp * pb->S);
+    const int64_t rows = static_cast<int64_t>(g_count) * P.ppk * P.S;
+    const int64_t grid = (rows + 7) / 8;
+    FMSA_REQUIRE(grid <= 0x7fffffffLL);
+    if (P.mpp <= kWideMaxHeads)
+        bwd_combine_wide_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    else
+        bwd_combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return check_launch();
 }

@@ -40,24 +40,29 @@ struct FwdParams {
     const int32_t* row_ptr;
     const int32_t* col_q;
     __nv_bfloat16* o_part;   // [(edge - edge_base) * mpp + head][128]
-    float* lse_part;         // [(edge - edge_base) * (mpp + 1) + head], head == mpp is the proxy head
+    float* stat_part;        // [(edge - edge_base) * (mpp + 1) + head][2] = (row max in the log2 domain, row sum);
+                             // head == mpp is the proxy head
     int32_t* counter;
     int32_t* status;
     int S, NB, Hq, Hkv, Hp, mpp, ppk, pg;
     int g_begin, G;
     int with_proxy, dense;
+    int64_t n_subunits;
     float scale_log2e;
 };
 
 struct FwdSmem {
-    uint64_t bar_kv, bar_kp, bar_s, bar_o[2];
+    uint64_t bar_kv, bar_kp, bar_s[2], bar_o[2];
     uint32_t tmem_slot;
     int32_t unit;
-    int32_t rows[2][128];
-    float inv_l[2][128];
+    int32_t rows[4][128];
+    float rmax[2][4][128];   // per tile parity: partial row maxima of the four column groups
+    float lsum[2][4][128];   // partial row sums
+    float mrow[2][128];      // row maximum (scaled, log2 domain)
 };
 
-constexpr int kFwdThreads = 256;
+constexpr int kFwdWorkers = 512;                // 16 worker warps
+constexpr int kFwdThreads = kFwdWorkers + 32;   // + one warp whose lane 0 only issues tcgen05.mma
 constexpr size_t kFwdSmemBytes = 6 * kTileBytes + 1024 + sizeof(FwdSmem);
 
 struct TileMeta {   // what the epilogue of a finished main tile needs
@@ -65,8 +70,20 @@ struct TileMeta {   // what the epilogue of a finished main tile needs
     int nrows;
     int head;       // head inside the proxy group
     int obuf;
+    uint32_t parity;
 };
 
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Thread layout: 16 worker warps; worker warp w reads TMEM lanes 32*(w%4)..+31 (tile rows) and owns
+// the 32 columns starting at 32*(w/4).  Warp 16 is the MMA issuer: a thread that issues tcgen05.mma
+// is held while the tensor core's queue is full, so it carries no other work.  Shared memory: K_j, V_j, Kp_j (resident for the sub-unit), two Q
+// buffers (rows gathered two tiles ahead), one P buffer (P*V of a tile is issued before S of the
+// next one, so it has finished reading P by the time the next softmax may write).  TMEM: two S and two O accumulators, so
+// the elected thread can issue P*V of this tile and S of the next one back to back while the
+// other threads store the previous tile's output.
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
                                                                     const __grid_constant__ CUtensorMap tmap_kp,
@@ -78,15 +95,21 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     FwdSmem* sm = reinterpret_cast<FwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 6 * kTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quarter = warp & 3, row = quarter * 32 + lane;
-    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_kp = smem_u32(&sm->bar_kp), bar_s = smem_u32(&sm->bar_s);
+    const bool worker = warp < 16;
+    const bool issuer = (warp == 16);            // the whole warp runs the issue sequence ...
+    const uint32_t elect = (lane == 0) ? 1u : 0u;   // ... and only this lane's instructions take effect
+    const int quarter = warp & 3, cg = (warp >> 2) & 3;
+    const int row = quarter * 32 + lane, c0 = cg * 32;
+    const GatherLane glane = make_gather_lane(tid & 511);
+    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_kp = smem_u32(&sm->bar_kp);
 
     if (tid == 0) {
         mbar_init(bar_kv, 1);
         mbar_init(bar_kp, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(smem_u32(&sm->bar_o[0]), 1);
-        mbar_init(smem_u32(&sm->bar_o[1]), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&sm->bar_s[i]), 1);
+            mbar_init(smem_u32(&sm->bar_o[i]), 1);
+        }
         fence_mbar_init();
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
@@ -100,264 +123,248 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm->tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o0 = tmem + 128;
+    const uint32_t tmem_s0 = tmem, tmem_o0 = tmem + 256;
 
     const int hpc = P.mpp + (P.with_proxy ? 1 : 0);   // tiles per chunk
     const int lse_stride = P.mpp + 1;
     const int64_t edge_base = P.dense ? dense_edge_base(static_cast<int64_t>(P.g_begin) * P.ppk, P.S, P.NB)
                                       : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
-    uint32_t ph_kv = 0, ph_kp = 0, ph_s = 0;
-    uint32_t mt = 0;   // main tiles issued so far (selects the O accumulator and its barrier phase)
-    bool bad = false;
+    uint32_t ph_kv = 0, ph_kp = 0;
+    uint32_t gt = 0;   // tiles processed so far by this CTA: selects the S, Q, P and statistics buffers
+    uint32_t mt = 0;   // main tiles so far: selects the O accumulator
+    bool bad = false;  // a bounded wait gave up: later waits are skipped, the status word is set at the end
 
     for (;;) {
         if (tid == 0) sm->unit = atomicAdd(P.counter, 1);
         __syncthreads();
         const int u = sm->unit;
         __syncthreads();
-        if (u >= P.G * P.NB) break;
-        const int j = u / P.G;
-        const int g = P.g_begin + u % P.G;
+        if (u >= P.n_subunits) break;
+        const SubUnit su = decode_subunit(u, P.NB, P.ppk);
+        const int j = su.j;
+        const int g = P.g_begin + su.g;
         const int b = g / P.Hkv, kvh = g % P.Hkv;
+        const int p = kvh * P.ppk + su.pp;
+        const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
+        int64_t e0;
+        int n;
+        if (P.dense) {
+            e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(j, P.S);
+            n = P.S - j * kBlock;
+        } else {
+            e0 = P.row_ptr[bp * P.NB + j];
+            n = P.row_ptr[bp * P.NB + j + 1] - static_cast<int>(e0);
+        }
+        const int chunk0 = su.chunk0;
+        const int chunk1 = min((n + kBlock - 1) / kBlock, chunk0 + kChunksPerSubUnit);
+        if (chunk1 <= chunk0) continue;   // this sub-unit lies beyond the end of the row
         if (tid == 0) {
             mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
             tma_load_tile(tile_k, &tmap_k, j * kBlock, kvh, b, bar_kv);
             tma_load_tile(tile_v, &tmap_v, j * kBlock, kvh, b, bar_kv);
-        }
-        bool kv_ready = false;
-
-        for (int pp = 0; pp < P.ppk; ++pp) {
-            const int p = kvh * P.ppk + pp;
-            const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
-            int64_t e0;
-            int n;
-            if (P.dense) {
-                e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(j, P.S);
-                n = P.S - j * kBlock;
-            } else {
-                e0 = P.row_ptr[bp * P.NB + j];
-                n = P.row_ptr[bp * P.NB + j + 1] - static_cast<int>(e0);
-            }
-            if (n <= 0) continue;
-            bool kp_ready = false;
-            if (P.with_proxy && tid == 0) {
+            if (P.with_proxy) {
                 mbar_arrive_expect_tx(bar_kp, kTileBytes);
                 tma_load_tile(tile_kp, &tmap_kp, j * kBlock, p / P.pg, b, bar_kp);
             }
-            const int nchunks = (n + kBlock - 1) / kBlock;
-            const int ntiles = nchunks * hpc;
-            const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
-            const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
+        }
+        const int ntiles = (chunk1 - chunk0) * hpc;
+        const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
+        const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
 
-            auto stage_rows = [&](int chunk) {
-                if (tid < kBlock) {
-                    const int at = chunk * kBlock + tid;
-                    int qid = -1;
-                    if (at < n) {
-                        qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
-                        if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
-                            atomicMax(P.status, kStatusBadIndex);
-                            qid = -1;
-                        }
+        auto stage_rows = [&](int chunk, int rb) {
+            if (tid < kBlock) {
+                const int at = chunk * kBlock + tid;
+                int qid = -1;
+                if (at < n) {
+                    qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
+                    if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
+                        atomicMax(P.status, kStatusBadIndex);
+                        qid = -1;
                     }
-                    sm->rows[chunk & 1][tid] = qid;
                 }
-            };
-            auto issue_gather = [&](int t) {
-                const int chunk = t / hpc, hh = t % hpc;
-                const uint32_t dst = tile_q0 + (t & 1) * kTileBytes;
-                if (hh < P.mpp)
-                    gather_tile_async<kFwdThreads>(dst, q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh, P.q_ss,
-                                                   sm->rows[chunk & 1], tid);
-                else
-                    gather_tile_async<kFwdThreads>(dst, qp_bp, P.qp_ss, sm->rows[chunk & 1], tid);
+                sm->rows[rb][tid] = qid;
+            }
+        };
+        // rows of a tile (main head hh or the proxy head) into the Q buffer selected by the global tile count
+        auto gather_q = [&](int hh, int rb, uint32_t gtile) {
+            const uint32_t dst = tile_q0 + (gtile & 1) * kTileBytes;
+            if (hh < P.mpp)
+                gather_tile_512(dst, q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh, P.q_ss, sm->rows[rb], glane);
+            else
+                gather_tile_512(dst, qp_bp, P.qp_ss, sm->rows[rb], glane);
+        };
+        auto issue_s = [&](bool proxy, uint32_t gtile) {   // issuer warp
+            umma_tile_128<false, false>(tmem_s0 + (gtile & 1) * 128, tile_q0 + (gtile & 1) * kTileBytes,
+                                        proxy ? tile_kp : tile_k, false, elect);
+            umma_commit(smem_u32(&sm->bar_s[gtile & 1]), elect);
+        };
+        // The output product is issued transposed (O^T = V_j^T P^T: TMEM lane = head-dimension index,
+        // column = tile row), so the 32 lanes of a warp store 32 consecutive elements of ONE partial
+        // row per instruction instead of touching 32 different rows.  The rows are stored
+        // unnormalised; the combine kernel divides by the row sums kept in stat_part.
+        auto epilogue = [&](const TileMeta& m) {
+            if (!bad) bad = !mbar_wait(smem_u32(&sm->bar_o[m.obuf]), m.parity);
+            tc_fence_after_sync();
+            __nv_bfloat16* dst = P.o_part + ((m.slot0 + c0) * P.mpp + m.head) * kHeadDim + row;
+            const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
+#pragma unroll
+            for (int c = 0; c < 32; c += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_addr(tmem_o0 + m.obuf * 128, quarter, c0 + c), v);
+                tmem_ld_wait();
+                store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, m.nrows);
+            }
+            tc_fence_before_sync();
+        };
+
+        // ---- prologue: rows, the first two Q tiles, S of tile 0 ----
+        // (chunk, head, row-list buffer) of local tiles 0, 1, 2 without divisions
+        int hh = 0, chunk = chunk0, rb = 0;
+        int hh1 = 1, chunk_1 = chunk0, rb1 = 0;
+        if (hh1 == hpc) { hh1 = 0; ++chunk_1; rb1 = 1; }
+        int hh2 = hh1 + 1, chunk_2 = chunk_1, rb2 = rb1;
+        if (hh2 == hpc) { hh2 = 0; ++chunk_2; rb2 = (rb1 + 1) & 3; }
+        stage_rows(chunk0, 0);
+        if (ntiles > 1 && chunk_1 != chunk0) stage_rows(chunk_1, rb1);
+        if (ntiles > 2 && chunk_2 != chunk_1) stage_rows(chunk_2, rb2);
+        __syncthreads();
+        if (worker) {
+            gather_q(0, 0, gt);
+            cp_async_commit();
+            if (ntiles > 1) gather_q(hh1, rb1, gt + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+            fence_async_smem();
+        }
+        __syncthreads();
+        if (issuer) {
+            if (!bad) bad = !mbar_wait(bar_kv, ph_kv);
+            tc_fence_after_sync();
+            issue_s(false, gt);
+        }
+        ph_kv ^= 1;
+        bool kp_ready = false;
+        TileMeta prev{};
+        bool have_prev = false;
+
+        for (int t = 0; t < ntiles; ++t, ++gt) {
+            const bool is_proxy = hh == P.mpp;
+            const int sb = gt & 1;
+            int hh3 = hh2 + 1, chunk_3 = chunk_2, rb3 = rb2;
+            if (hh3 == hpc) { hh3 = 0; ++chunk_3; rb3 = (rb2 + 1) & 3; }
+            const int nrows = min(kBlock, n - chunk * kBlock);
+            const int64_t slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
+            bool live = false;
+            if (worker) {
+                const int qid = sm->rows[rb][row];
+                live = qid >= 0;
+                // only the first chunk of a reverse-index row can hold rows of the key block itself
+                const bool masked = (chunk == 0);
+                const int limit = (masked && live && (qid >> 7) == j) ? (qid & 127) : 127;
+
+                if (!bad) bad = !mbar_wait(smem_u32(&sm->bar_s[sb]), (gt >> 1) & 1);
+                tc_fence_after_sync();
+                // rows needed three tiles ahead, then the gather of tile t+2 into the Q buffer S(t) just released
+                if (t + 3 < ntiles && chunk_3 != chunk_2) stage_rows(chunk_3, rb3);
+                if (t + 2 < ntiles) gather_q(hh2, rb2, gt + 2);
                 cp_async_commit();
-            };
 
-            stage_rows(0);
-            __syncthreads();
-            issue_gather(0);
-
-            TileMeta prev{};
-            bool pv_pending = false;
-
-            for (int t = 0; t < ntiles; ++t) {
-                const int chunk = t / hpc, hh = t % hpc;
-                const bool is_proxy = hh == P.mpp;
-                const uint32_t qbuf = tile_q0 + (t & 1) * kTileBytes;
-                cp_async_wait<0>();
+                // ---- softmax of this thread's (row, 32 columns): pass 1 maximum, pass 2 exponentials ----
+                float mloc = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 32; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_addr(tmem_s0 + sb * 128, quarter, c0 + c), v);
+                    tmem_ld_wait();
+                    if (masked) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) mloc = (c0 + c + i <= limit) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) mloc = fmaxf(mloc, __uint_as_float(v[i]));
+                    }
+                }
+                sm->rmax[sb][cg][row] = mloc;      // raw logits: scale > 0, so the maximum commutes with it
+                named_barrier_sync(1 + quarter, 128);
+                const float m = fmaxf(fmaxf(sm->rmax[sb][0][row], sm->rmax[sb][1][row]),
+                                      fmaxf(sm->rmax[sb][2][row], sm->rmax[sb][3][row])) * P.scale_log2e;
+                float l = 0.f;
+#pragma unroll
+                for (int c = 0; c < 32; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_addr(tmem_s0 + sb * 128, quarter, c0 + c), v);
+                    tmem_ld_wait();
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), P.scale_log2e, -m));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), P.scale_log2e, -m));
+                        if (masked) {
+                            p0 = (c0 + c + i <= limit) ? p0 : 0.f;
+                            p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
+                        }
+                        l += p0 + p1;
+                        pk[i >> 1] = pack_bf16(p0, p1);
+                    }
+                    if (!is_proxy) {
+#pragma unroll
+                        for (int k8 = 0; k8 < 2; ++k8)
+                            st_shared_v4(tile_p + swz_offset(row, ((c0 + c) >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1],
+                                         pk[4 * k8 + 2], pk[4 * k8 + 3]);
+                    }
+                }
+                sm->lsum[sb][cg][row] = l;
+                if (cg == 0) sm->mrow[sb][row] = m;
+                cp_async_wait<1>();      // Q rows of tile t+1 have landed (tile t+2 may still be in flight)
                 fence_async_smem();
-                __syncthreads();
-                if (tid == 0) {
-                    if (!kv_ready) bad |= !mbar_wait(bar_kv, ph_kv);
-                    if (is_proxy && !kp_ready) bad |= !mbar_wait(bar_kp, ph_kp);
-                    tc_fence_after_sync();
-                    umma_tile_128<false, false>(tmem_s, qbuf, is_proxy ? tile_kp : tile_k, false);
-                    umma_commit(bar_s);
-                }
-                if (!kv_ready) {
-                    kv_ready = true;
-                    ph_kv ^= 1;
-                }
-                if (is_proxy && !kp_ready) {
-                    kp_ready = true;
-                    ph_kp ^= 1;
-                }
-                // prefetch the next tile's rows while the tensor core works
-                if (t + 1 < ntiles) {
-                    const int nchunk = (t + 1) / hpc;
-                    if (nchunk != chunk) {
-                        stage_rows(nchunk);
-                        __syncthreads();
-                    }
-                    issue_gather(t + 1);
-                }
-                bad |= !mbar_wait(bar_s, ph_s);
-                ph_s ^= 1;
-                if (__syncthreads_or(bad)) {
-                    bad = true;
-                    goto abort;
-                }
-                tc_fence_after_sync();
+                tc_fence_before_sync();
+            }
+            __syncthreads();
 
-                const int nrows = min(kBlock, n - chunk * kBlock);
-                if (warp < 4) {
-                    // ---------------- softmax of tile t: one row per thread ----------------
-                    const int qid = sm->rows[chunk & 1][row];
-                    const int limit = (qid >= 0 && (qid >> 7) == j) ? (qid & 127) : 127;
-                    float m = -INFINITY;
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(tmem_s, quarter, c), v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float x = __uint_as_float(v[i]) * P.scale_log2e;
-                            m = (c + i <= limit) ? fmaxf(m, x) : m;
-                        }
-                    }
-                    if (pv_pending && !is_proxy)   // P buffer is still being read by the previous P*V
-                        bad |= !mbar_wait(smem_u32(&sm->bar_o[prev.obuf]), ((mt - 1) >> 1) & 1);
-                    float l = 0.f;
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(tmem_s, quarter, c), v);
-                        tmem_ld_wait();
-                        uint32_t pk[16];
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float p0 = fast_exp2(__uint_as_float(v[i]) * P.scale_log2e - m);
-                            float p1 = fast_exp2(__uint_as_float(v[i + 1]) * P.scale_log2e - m);
-                            p0 = (c + i <= limit) ? p0 : 0.f;
-                            p1 = (c + i + 1 <= limit) ? p1 : 0.f;
-                            l += p0 + p1;
-                            pk[i >> 1] = pack_bf16(p0, p1);
-                        }
-                        if (!is_proxy) {
-#pragma unroll
-                            for (int k8 = 0; k8 < 4; ++k8)
-                                st_shared_v4(tile_p + swz_offset(row, (c >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1],
-                                             pk[4 * k8 + 2], pk[4 * k8 + 3]);
-                        }
-                    }
-                    if (row < nrows && qid >= 0) {
-                        const int64_t slot = e0 - edge_base + chunk * kBlock + row;
-                        P.lse_part[slot * lse_stride + hh] = (m + __log2f(l)) * kLn2;
-                    }
-                    if (!is_proxy) sm->inv_l[mt & 1][row] = 1.f / l;
-                    fence_async_smem();
-                } else if (pv_pending) {
-                    // ---------------- epilogue of the previous main tile ----------------
-                    bad |= !mbar_wait(smem_u32(&sm->bar_o[prev.obuf]), ((mt - 1) >> 1) & 1);
-                    tc_fence_after_sync();
-                    const float il = sm->inv_l[prev.obuf][row];
-                    const bool live = row < prev.nrows;
-                    __nv_bfloat16* dst = P.o_part + ((prev.slot0 + row) * P.mpp + prev.head) * kHeadDim;
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(tmem_o0 + prev.obuf * 128, quarter, c), v);
-                        tmem_ld_wait();
-                        if (live) {
-#pragma unroll
-                            for (int k8 = 0; k8 < 4; ++k8) {
-                                uint4 w;
-                                w.x = pack_bf16(__uint_as_float(v[8 * k8 + 0]) * il, __uint_as_float(v[8 * k8 + 1]) * il);
-                                w.y = pack_bf16(__uint_as_float(v[8 * k8 + 2]) * il, __uint_as_float(v[8 * k8 + 3]) * il);
-                                w.z = pack_bf16(__uint_as_float(v[8 * k8 + 4]) * il, __uint_as_float(v[8 * k8 + 5]) * il);
-                                w.w = pack_bf16(__uint_as_float(v[8 * k8 + 6]) * il, __uint_as_float(v[8 * k8 + 7]) * il);
-                                *reinterpret_cast<uint4*>(dst + c + 8 * k8) = w;
-                            }
-                        }
-                    }
-                }
-                tc_fence_before_sync();
-                if (__syncthreads_or(bad)) {
-                    bad = true;
-                    goto abort;
-                }
-                pv_pending = false;
-                if (!is_proxy) {
-                    if (tid == 0) {
-                        tc_fence_after_sync();
-                        umma_tile_128<false, true>(tmem_o0 + (mt & 1) * 128, tile_p, tile_v, false);
-                        umma_commit(smem_u32(&sm->bar_o[mt & 1]));
-                    }
-                    prev.slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
-                    prev.nrows = nrows;
-                    prev.head = hh;
-                    prev.obuf = mt & 1;
-                    ++mt;
-                    pv_pending = true;
-                }
-            }
-            // drain: the last main tile of this (unit, proxy head)
-            if (pv_pending) {
-                bad |= !mbar_wait(smem_u32(&sm->bar_o[prev.obuf]), ((mt - 1) >> 1) & 1);
+            // ---- P*V of this tile and S of the next one ----
+            const bool next_proxy = (t + 1 < ntiles) && (hh1 == P.mpp);
+            if (issuer) {
                 tc_fence_after_sync();
-                if (warp >= 4 && !bad) {
-                    const float il = sm->inv_l[prev.obuf][row];
-                    const bool live = row < prev.nrows;
-                    __nv_bfloat16* dst = P.o_part + ((prev.slot0 + row) * P.mpp + prev.head) * kHeadDim;
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(tmem_o0 + prev.obuf * 128, quarter, c), v);
-                        tmem_ld_wait();
-                        if (live) {
-#pragma unroll
-                            for (int k8 = 0; k8 < 4; ++k8) {
-                                uint4 w;
-                                w.x = pack_bf16(__uint_as_float(v[8 * k8 + 0]) * il, __uint_as_float(v[8 * k8 + 1]) * il);
-                                w.y = pack_bf16(__uint_as_float(v[8 * k8 + 2]) * il, __uint_as_float(v[8 * k8 + 3]) * il);
-                                w.z = pack_bf16(__uint_as_float(v[8 * k8 + 4]) * il, __uint_as_float(v[8 * k8 + 5]) * il);
-                                w.w = pack_bf16(__uint_as_float(v[8 * k8 + 6]) * il, __uint_as_float(v[8 * k8 + 7]) * il);
-                                *reinterpret_cast<uint4*>(dst + c + 8 * k8) = w;
-                            }
-                        }
-                    }
+                if (!is_proxy) {
+                    umma_tile_128<true, false>(tmem_o0 + (mt & 1) * 128, tile_v, tile_p, false, elect);   // O^T = V_j^T P^T
+                    umma_commit(smem_u32(&sm->bar_o[mt & 1]), elect);
                 }
-                tc_fence_before_sync();
-                if (__syncthreads_or(bad)) {
-                    bad = true;
-                    goto abort;
+                if (t + 1 < ntiles) {
+                    if (next_proxy && !kp_ready && !bad) bad = !mbar_wait(bar_kp, ph_kp);
+                    issue_s(next_proxy, gt + 1);
                 }
             }
-        }
-        if (!kv_ready) {   // no proxy head of this unit had any edge: still consume the K/V load
-            if (tid == 0) bad |= !mbar_wait(bar_kv, ph_kv);
-            ph_kv ^= 1;
-            if (__syncthreads_or(bad)) {
-                bad = true;
-                goto abort;
+            if (next_proxy) kp_ready = true;
+            // ---- row statistics of this tile (one thread per row): maximum (log2 domain) and sum ----
+            if (worker && cg == 0 && row < nrows && live) {
+                const float lt = sm->lsum[sb][0][row] + sm->lsum[sb][1][row] + sm->lsum[sb][2][row] + sm->lsum[sb][3][row];
+                float2* st = reinterpret_cast<float2*>(P.stat_part) + (slot0 + row) * lse_stride + hh;
+                *st = make_float2(sm->mrow[sb][row], lt);
             }
+            // ---- output rows of the previous main tile, while the tensor core works ----
+            if (have_prev && worker) epilogue(prev);
+            have_prev = false;
+            if (!is_proxy) {
+                prev.slot0 = slot0;
+                prev.nrows = nrows;
+                prev.head = hh;
+                prev.obuf = mt & 1;
+                prev.parity = (mt >> 1) & 1;
+                ++mt;
+                have_prev = true;
+            }
+            hh = hh1; chunk = chunk_1; rb = rb1;
+            hh1 = hh2; chunk_1 = chunk_2; rb1 = rb2;
+            hh2 = hh3; chunk_2 = chunk_3; rb2 = rb3;
         }
+        if (P.with_proxy) ph_kp ^= 1;
+        // drain: the last main tile of the sub-unit
+        __syncthreads();
+        if (have_prev && worker) epilogue(prev);
+        __syncthreads();
     }
-abort:
     cp_async_wait<0>();
-    if (bad && tid == 0) atomicMax(P.status, kStatusWaitTimeout);
+    if (bad) atomicMax(P.status, kStatusWaitTimeout);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -399,16 +406,17 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
         return e < 0 ? -1 : static_cast<int64_t>(e) - edge_base;
     };
 
+    const float2* stats = reinterpret_cast<const float2*>(P.lse_part);
     const int nheads = P.mpp + (P.lse_proxy ? 1 : 0);
     for (int hh = 0; hh < nheads; ++hh) {
-        // pass A: log-sum-exp over the slots
+        // pass A: every partial carries (row max m in the log2 domain, row sum l); merge them
         float m = -INFINITY, sum = 0.f;
         for (int s0 = 0; s0 < nslots; s0 += 32) {
             const int64_t sl = slot_of(s0 + lane);
             if (sl >= 0) {
-                const float x = P.lse_part[sl * lse_stride + hh];
-                const float mn = fmaxf(m, x);
-                sum = sum * __expf(m - mn) + __expf(x - mn);
+                const float2 st = stats[sl * lse_stride + hh];
+                const float mn = fmaxf(m, st.x);
+                sum = sum * fast_exp2(m - mn) + st.y * fast_exp2(st.x - mn);
                 m = mn;
             }
         }
@@ -417,24 +425,26 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
             const float mo = __shfl_xor_sync(0xffffffffu, m, off);
             const float so = __shfl_xor_sync(0xffffffffu, sum, off);
             const float mn = fmaxf(m, mo);
-            const float a = (m == -INFINITY) ? 0.f : sum * __expf(m - mn);
-            const float c = (mo == -INFINITY) ? 0.f : so * __expf(mo - mn);
+            const float a = (m == -INFINITY) ? 0.f : sum * fast_exp2(m - mn);
+            const float c = (mo == -INFINITY) ? 0.f : so * fast_exp2(mo - mn);
             sum = a + c;
             m = mn;
         }
-        const float total = m + __logf(sum);
+        const float total = (m + __log2f(sum)) * kLn2;   // natural-log LSE of the whole row
         if (hh == P.mpp) {
             if (lane == 0) P.lse_proxy[bp * P.S + q] = total;
             continue;
         }
         const int h = p * P.mpp + hh;
         if (lane == 0) P.lse[(static_cast<int64_t>(b) * P.Hq + h) * P.S + q] = total;
-        // pass B: weighted sum of the partial outputs; lane owns columns 4*lane..4*lane+3
+        // pass B: weighted sum of the unnormalised partial outputs; lane owns columns 4*lane..4*lane+3
+        const float inv = 1.f / sum;
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         for (int s0 = 0; s0 < nslots; s0 += 32) {
             const int64_t sl = slot_of(s0 + lane);
-            const float wgt = sl >= 0 ? __expf(P.lse_part[sl * lse_stride + hh] - total) : 0.f;
+            const float wgt = sl >= 0 ? fast_exp2(stats[sl * lse_stride + hh].x - m) * inv : 0.f;
             const int cnt = min(32, nslots - s0);
+#pragma unroll 4
             for (int i = 0; i < cnt; ++i) {
                 const int64_t si = __shfl_sync(0xffffffffu, sl, i);
                 const float wi = __shfl_sync(0xffffffffu, wgt, i);
@@ -453,6 +463,124 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
         o.y = pack_bf16(a2, a3);
         *reinterpret_cast<uint2*>(P.out + (static_cast<int64_t>(b) * P.S + q) * (static_cast<int64_t>(P.Hq) * kHeadDim) +
                                   static_cast<int64_t>(h) * kHeadDim + lane * 4) = o;
+    }
+}
+
+// Wide variant for Hq/Hp <= 8: the partial rows of all main heads of one edge are contiguous
+// (mpp * 256 bytes), so a warp reads them with 16-byte loads per lane in one sweep instead of one
+// 256-byte row at a time; weights go through shared memory.
+constexpr int kWideMaxHeads = 8;
+__global__ void __launch_bounds__(256) combine_wide_kernel(const CombineParams P) {
+    __shared__ float wsm[8][32][kWideMaxHeads + 1];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + wib;
+    const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;
+    if (w >= static_cast<int64_t>(P.G) * P.ppk * P.S) return;
+    const int64_t bp = bp0 + w / P.S;
+    const int q = static_cast<int>(w % P.S);
+    const int b = static_cast<int>(bp / P.Hp), p = static_cast<int>(bp % P.Hp);
+    const int64_t edge_base = P.dense ? dense_edge_base(bp0, P.S, P.NB) : static_cast<int64_t>(P.row_ptr[bp0 * P.NB]);
+    const int nslots = P.dense ? (q >> 7) + 1 : P.Kb;
+    const int lse_stride = P.mpp + 1;
+    const int32_t* erow = P.dense ? nullptr : P.edge_pos + (bp * P.S + q) * P.Kb;
+    auto slot_of = [&](int s) -> int64_t {
+        if (s >= nslots) return -1;
+        if (P.dense) return dense_edge_base(bp, P.S, P.NB) + dense_row_offset(s, P.S) + (q - s * kBlock) - edge_base;
+        const int e = erow[s];
+        return e < 0 ? -1 : static_cast<int64_t>(e) - edge_base;
+    };
+    const float2* stats = reinterpret_cast<const float2*>(P.lse_part);
+    const int nheads = P.mpp + (P.lse_proxy ? 1 : 0);
+
+    // pass A: merged (max, sum) of every head over all slots
+    float hm[kWideMaxHeads + 1], hs[kWideMaxHeads + 1];
+#pragma unroll
+    for (int hh = 0; hh <= kWideMaxHeads; ++hh) {
+        hm[hh] = -INFINITY;
+        hs[hh] = 0.f;
+    }
+    for (int s0 = 0; s0 < nslots; s0 += 32) {
+        const int64_t sl = slot_of(s0 + lane);
+#pragma unroll
+        for (int hh = 0; hh <= kWideMaxHeads; ++hh) {
+            if (hh < nheads && sl >= 0) {
+                const float2 st = stats[sl * lse_stride + hh];
+                const float mn = fmaxf(hm[hh], st.x);
+                hs[hh] = hs[hh] * fast_exp2(hm[hh] - mn) + st.y * fast_exp2(st.x - mn);
+                hm[hh] = mn;
+            }
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh <= kWideMaxHeads; ++hh) {
+        if (hh < nheads) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float mo = __shfl_xor_sync(0xffffffffu, hm[hh], off);
+                const float so = __shfl_xor_sync(0xffffffffu, hs[hh], off);
+                const float mn = fmaxf(hm[hh], mo);
+                const float a = (hm[hh] == -INFINITY) ? 0.f : hs[hh] * fast_exp2(hm[hh] - mn);
+                const float c = (mo == -INFINITY) ? 0.f : so * fast_exp2(mo - mn);
+                hs[hh] = a + c;
+                hm[hh] = mn;
+            }
+            const float total = (hm[hh] + __log2f(hs[hh])) * kLn2;
+            if (lane == 0) {
+                if (hh == P.mpp) P.lse_proxy[bp * P.S + q] = total;
+                else P.lse[(static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q] = total;
+            }
+        }
+    }
+    // pass B: lane owns 16-byte chunks ck = k*32 + lane of the mpp*128-element edge record
+    const int nchunk = P.mpp * 16;
+    float acc[4][8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
+    for (int s0 = 0; s0 < nslots; s0 += 32) {
+        const int64_t sl = slot_of(s0 + lane);
+        __syncwarp();
+#pragma unroll
+        for (int hh = 0; hh < kWideMaxHeads; ++hh)
+            if (hh < P.mpp) wsm[wib][lane][hh] = sl >= 0 ? fast_exp2(stats[sl * lse_stride + hh].x - hm[hh]) / hs[hh] : 0.f;
+        __syncwarp();
+        const int cnt = min(32, nslots - s0);
+#pragma unroll 2
+        for (int i = 0; i < cnt; ++i) {
+            const int64_t si = __shfl_sync(0xffffffffu, sl, i);
+            if (si < 0) continue;
+            const __nv_bfloat16* rec = P.o_part + si * P.mpp * kHeadDim;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int ck = k * 32 + lane;
+                if (ck < nchunk) {
+                    const float wgt = wsm[wib][i][ck >> 4];
+                    const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
+                    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&u[e]);
+                        acc[k][2 * e] += wgt * __low2float(v2);
+                        acc[k][2 * e + 1] += wgt * __high2float(v2);
+                    }
+                }
+            }
+        }
+    }
+    __nv_bfloat16* orow = P.out + (static_cast<int64_t>(b) * P.S + q) * (static_cast<int64_t>(P.Hq) * kHeadDim) +
+                          static_cast<int64_t>(p) * P.mpp * kHeadDim;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int ck = k * 32 + lane;
+        if (ck < nchunk) {
+            uint4 o;
+            o.x = pack_bf16(acc[k][0], acc[k][1]);
+            o.y = pack_bf16(acc[k][2], acc[k][3]);
+            o.z = pack_bf16(acc[k][4], acc[k][5]);
+            o.w = pack_bf16(acc[k][6], acc[k][7]);
+            *reinterpret_cast<uint4*>(orow + ck * 8) = o;
+        }
     }
 }
 
@@ -502,7 +630,7 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.qp_sb = with_proxy ? q_proxy->stride_b : 0; P.qp_sh = with_proxy ? q_proxy->stride_h : 0;
     P.qp_ss = with_proxy ? q_proxy->stride_s : 0;
     P.row_ptr = row_ptr; P.col_q = col_q;
-    P.o_part = static_cast<__nv_bfloat16*>(o_part); P.lse_part = lse_part;
+    P.o_part = static_cast<__nv_bfloat16*>(o_part); P.stat_part = lse_part;
     P.counter = counter; P.status = status;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hkv = pb->Hkv; P.Hp = pb->Hp;
     P.mpp = pb->Hq / pb->Hp; P.ppk = pb->Hp / pb->Hkv; P.pg = pb->Hp / pb->Hpkv;
@@ -517,8 +645,9 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
         cudaSuccess)
         return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
-    const int64_t units = static_cast<int64_t>(g_count) * P.NB;
-    const int grid = static_cast<int>(units < sms ? units : sms);
+    P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
+    FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
+    const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
     sparse_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tk, tv, tkp, P);
     return check_launch();
 }
@@ -539,6 +668,9 @@ extern "C" int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_par
     const int64_t rows = static_cast<int64_t>(g_count) * P.ppk * P.S;
     const int64_t grid = (rows + 7) / 8;
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
-    combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    if (P.mpp <= kWideMaxHeads)
+        combine_wide_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    else
+        combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return check_launch();
 }

@@ -240,11 +240,11 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
     counter = torch.empty(1, dtype=torch.int32, device=dev)
     groups = b * hkv
     per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
-    bytes_per_slot = mpp * d * 2 + (mpp + 1) * 4
+    bytes_per_slot = mpp * d * 2 + (mpp + 1) * 8
     gstep = max(1, min(groups, MAX_PARTIAL_BYTES // max(1, per_group * bytes_per_slot)))
     slots = per_group * gstep
     o_part = torch.empty(slots * mpp * d, dtype=q.dtype, device=dev)
-    lse_part = torch.empty(slots * (mpp + 1), dtype=torch.float32, device=dev)
+    lse_part = torch.empty(slots * (mpp + 1) * 2, dtype=torch.float32, device=dev)
     row_ptr = 0 if dense else rix.row_ptr.data_ptr()
     col_q = 0 if dense else rix.col_q.data_ptr()
     edge_pos = 0 if dense else rix.edge_pos.data_ptr()
@@ -274,6 +274,7 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
     b, hq, s, d = q.shape
     hkv, hp, hpkv = k.shape[1], qp.shape[1], kp.shape[1]
+    mpp = hq // hp
     dev = q.device
     st = _stream(dev)
     pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale)
@@ -291,33 +292,47 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     with _Timed("bwd_delta", dev):
         _launch("fmsa_bwd_delta", 1, lib.fmsa_bwd_delta(out.data_ptr(), _tensor_arg(go), delta.data_ptr(), b, s, hq, st), dev)
 
-    dq_acc = torch.zeros(b, hq, s, d, dtype=torch.float32, device=dev)
-    dk = torch.empty(b, hkv, s, d, dtype=q.dtype, device=dev)
-    dv = torch.empty(b, hkv, s, d, dtype=q.dtype, device=dev)
-    if with_kl:
-        dqp_acc = torch.zeros(b, hp, s, d, dtype=torch.float32, device=dev)
-        dkp_acc = torch.zeros(b, hpkv, s, d, dtype=torch.float32, device=dev)
-    with _Timed("attn_bwd", dev):
-        _launch("fmsa_sparse_bwd", 1, lib.fmsa_sparse_bwd(
-            ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
-            _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(),
-            0 if dense else rix.row_ptr.data_ptr(), 0 if dense else rix.col_q.data_ptr(),
-            dq_acc.data_ptr(), dqp_acc.data_ptr() if with_kl else 0, dkp_acc.data_ptr() if with_kl else 0,
-            dk.data_ptr(), dv.data_ptr(), int(with_kl), int(dense), counter.data_ptr(), status.data_ptr(), st), dev)
-
     dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
-    with _Timed("cast", dev):
-        _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dq_acc.data_ptr(), dq.data_ptr(), dq_acc.numel(), 0, st), dev)
+    dkv_acc = torch.zeros(2, b, hkv, s, d, dtype=torch.float32, device=dev)
     if with_kl:
         gk = grad_kl.detach().to(device=dev, dtype=torch.float32).reshape(1)
         dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
-        dkp = torch.empty(b, hpkv, s, d, dtype=q.dtype, device=dev)
-        with _Timed("cast", dev):
-            _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dqp_acc.data_ptr(), dqp.data_ptr(), dqp_acc.numel(),
-                                                              gk.data_ptr(), st), dev)
-            _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dkp_acc.data_ptr(), dkp.data_ptr(), dkp_acc.numel(),
-                                                              gk.data_ptr(), st), dev)
+        dkp_acc = torch.zeros(b, hpkv, s, d, dtype=torch.float32, device=dev)
     else:
         dqp = torch.zeros(b, hp, s, d, dtype=q.dtype, device=dev)
         dkp = torch.zeros(b, hpkv, s, d, dtype=q.dtype, device=dev)
-    return dqp, dkp, dq, dk, dv
+
+    groups = b * hkv
+    per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
+    bytes_per_slot = (mpp + (1 if with_kl else 0)) * d * 2
+    gstep = max(1, min(groups, MAX_PARTIAL_BYTES // max(1, per_group * bytes_per_slot)))
+    slots = per_group * gstep
+    dq_part = torch.empty(slots * mpp * d, dtype=q.dtype, device=dev)
+    dqp_part = torch.empty(slots * d, dtype=q.dtype, device=dev) if with_kl else None
+    row_ptr = 0 if dense else rix.row_ptr.data_ptr()
+    col_q = 0 if dense else rix.col_q.data_ptr()
+    edge_pos = 0 if dense else rix.edge_pos.data_ptr()
+    for g0 in range(0, groups, gstep):
+        gc = min(gstep, groups - g0)
+        with _Timed("attn_bwd", dev):
+            _launch("fmsa_sparse_bwd", 1, lib.fmsa_sparse_bwd(
+                ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
+                _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(), row_ptr, col_q,
+                dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, dkp_acc.data_ptr() if with_kl else 0,
+                dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), g0, gc, int(with_kl), int(dense), counter.data_ptr(),
+                status.data_ptr(), st), dev)
+        with _Timed("bwd_combine", dev):
+            _launch("fmsa_sparse_bwd_combine", 1, lib.fmsa_sparse_bwd_combine(
+                ctypes_byref(pb), dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, edge_pos, row_ptr,
+                dq.data_ptr(), dqp.data_ptr() if with_kl else 0, gk.data_ptr() if with_kl else 0, g0, gc, int(dense), st), dev)
+
+    dkv = torch.empty(2, b, hkv, s, d, dtype=q.dtype, device=dev)
+    n_kv = dkv_acc[0].numel()
+    with _Timed("cast", dev):
+        _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dkv_acc[0].data_ptr(), dkv[0].data_ptr(), n_kv, 0, float(scale), st), dev)
+        _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dkv_acc[1].data_ptr(), dkv[1].data_ptr(), n_kv, 0, 1.0, st), dev)
+        if with_kl:
+            dkp = torch.empty(b, hpkv, s, d, dtype=q.dtype, device=dev)
+            _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(dkp_acc.data_ptr(), dkp.data_ptr(), dkp_acc.numel(),
+                                                              gk.data_ptr(), float(scale) / float(b * hp * s), st), dev)
+    return dqp, dkp, dq, dkv[0], dkv[1]

@@ -119,7 +119,8 @@ int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, f
  * Work is restricted to the (batch, KV head) groups g_begin .. g_begin+g_count-1 (g = b*Hkv + kvh)
  * so that the partial buffers can be bounded: fmsa_fwd_partial_slots() gives the number of edge
  * slots the pass needs;
- *   o_part   bf16 [slots, Hq/Hp, 128]       lse_part fp32 [slots, Hq/Hp + 1]
+ *   o_part   bf16 [slots, Hq/Hp, 128]   unnormalised partial rows (sum over the block of exp(s - max) * V)
+ *   lse_part fp32 [slots, Hq/Hp + 1, 2] per partial row: (row max in the log2 domain, row sum)
  * dense = 1 ignores row_ptr/col_q and runs every causal (query block, key block) pair: the warmup
  * forward (flash_msa/warmup/msa_forward_cutedsl_warmup.py:22-67).
  * counter: int32[1] scratch (reset by the call);  status: int32[1]. */
@@ -145,24 +146,40 @@ int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int3
 /* Fused backward over the selected edges (dense = 1: over every causal block pair, the warmup
  * backward).  Replaces run_fused_backward (flash_msa/msa_backward_cutedsl.py:944-1114) and
  * run_warmup_backward (flash_msa/warmup/msa_backward_cutedsl_warmup.py:117-191).
+ * Restricted, like fmsa_sparse_fwd, to the (batch, KV head) groups g_begin .. g_begin+g_count-1.
  *   d_out      (B,Hq,S,128) view of the upstream gradient
  *   lse, delta fp32 [B,Hq,S];  lse_proxy fp32 [B,Hp,S]
- *   dq_acc fp32 [B,Hq,S,128], dqp_acc fp32 [B,Hp,S,128], dkp_acc fp32 [B,Hpkv,S,128]: ZEROED by the
- *              caller, accumulated with red.add; dqp/dkp already carry scale/(B*Hp*S)
- *   dk, dv     bf16 [B,Hkv,S,128], written exactly once per element
+ *   dq_part    bf16 [slots, Hq/Hp, 128], dqp_part bf16 [slots, 128]: per-edge contributions to dQ and
+ *              dQp (slots >= fmsa_fwd_partial_slots); fmsa_sparse_bwd_combine sums them per row.
+ *              Both are unscaled; the combine applies scale and scale/(B*Hp*S).
+ *   dkp_acc fp32 [B,Hpkv,S,128], dk_acc, dv_acc fp32 [B,Hkv,S,128]: ZEROED by the caller,
+ *              accumulated with atomics (long reverse-index rows are split over several CTAs),
+ *              unscaled; cast to the activation dtype with fmsa_cast_scaled (which applies the factors).
  * with_kl = 0 skips the proxy work (the reference does the same when no gradient reaches kl_loss,
- * flash_msa/flash_msa.py:104-106) and ignores q_proxy, k_proxy, lse_proxy, dqp_acc, dkp_acc.
+ * flash_msa/flash_msa.py:104-106) and ignores q_proxy, k_proxy, lse_proxy, dqp_part, dkp_acc.
  * counter: int32[1] scratch;  status: int32[1]. */
 int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
                     const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out, const float* lse,
                     const float* lse_proxy, const float* delta, const int32_t* row_ptr, const int32_t* col_q,
-                    float* dq_acc, float* dqp_acc, float* dkp_acc, void* dk, void* dv, int32_t with_kl, int32_t dense,
-                    int32_t* counter, int32_t* status, void* stream);
+                    void* dq_part, void* dqp_part, int64_t part_slots, float* dkp_acc, float* dk_acc, float* dv_acc,
+                    int32_t g_begin, int32_t g_count, int32_t with_kl, int32_t dense, int32_t* counter,
+                    int32_t* status, void* stream);
 
-/* dst[i] = bf16(src[i] * f), f = *scale_ptr (a device scalar, e.g. the upstream gradient of
- * kl_loss: flash_msa/flash_msa.py:122-125) or 1 when scale_ptr is NULL.  n % 4 == 0.
- * Replaces the fp32 -> input-dtype casts at flash_msa/msa_backward_cutedsl.py:1075-1081. */
-int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, void* stream);
+/* Sums the per-edge contributions of every query row:
+ *   dq bf16 [B,Hq,S,128];  dq_proxy bf16 [B,Hp,S,128] (or NULL), multiplied by *grad_kl (device
+ *   scalar, the upstream gradient of kl_loss: flash_msa/flash_msa.py:122-125; NULL = 1).
+ * Takes the place of the reference's fp32 atomic accumulation + cast
+ * (flash_msa/msa_backward_cutedsl.py:738-836, 1075-1081). */
+int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part,
+                            const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
+                            const float* grad_kl, int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
+
+/* dst[i] = bf16(src[i] * const_scale * f), f = *scale_ptr (a device scalar, e.g. the upstream
+ * gradient of kl_loss: flash_msa/flash_msa.py:122-125) or 1 when scale_ptr is NULL.  n % 4 == 0.
+ * Replaces the fp32 -> input-dtype casts at flash_msa/msa_backward_cutedsl.py:1075-1081.
+ * fmsa_sparse_bwd leaves these factors to the cast: dv_acc needs 1, dk_acc needs scale, dkp_acc
+ * needs scale/(B*Hp*S) times the upstream kl gradient. */
+int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale, void* stream);
 
 #ifdef __cplusplus
 }
