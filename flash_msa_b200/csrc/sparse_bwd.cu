@@ -505,8 +505,8 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams
 }
 
 // Wide variant for Hq/Hp <= 8: one sweep over the contiguous mpp*256-byte record of each edge.
-constexpr int kWideMaxHeads = 8;
-__global__ void __launch_bounds__(256) bwd_combine_wide_kernel(const BwdCombineParams P) {
+template <int KITER>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (latency bound)
+__global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_kernel(const BwdCombineParams P) {
     const int lane = threadIdx.x & 31;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;
@@ -524,22 +524,22 @@ __global__ void __launch_bounds__(256) bwd_combine_wide_kernel(const BwdCombineP
         return e < 0 ? -1 : static_cast<int64_t>(e) - edge_base;
     };
     const int nchunk = P.mpp * 16;
-    float acc[4][8];
+    float acc[KITER][8];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int k = 0; k < KITER; ++k)
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
     float pa0 = 0.f, pa1 = 0.f, pa2 = 0.f, pa3 = 0.f;   // proxy row: lane owns columns 4*lane..+3
     for (int s0 = 0; s0 < nslots; s0 += 32) {
         const int64_t sl = slot_of(s0 + lane);
         const int cnt = min(32, nslots - s0);
-#pragma unroll 2
+#pragma unroll 4
         for (int i = 0; i < cnt; ++i) {
             const int64_t si = __shfl_sync(0xffffffffu, sl, i);
             if (si < 0) continue;
             const __nv_bfloat16* rec = P.dq_part + si * P.mpp * kHeadDim;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < KITER; ++k) {
                 const int ck = k * 32 + lane;
                 if (ck < nchunk) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
@@ -564,7 +564,7 @@ __global__ void __launch_bounds__(256) bwd_combine_wide_kernel(const BwdCombineP
         }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < KITER; ++k) {
         const int ck = k * 32 + lane;
         if (ck < nchunk) {
             const int hh = ck >> 4, col = (ck & 15) * 8;
@@ -749,8 +749,16 @@ extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_pa
     const int64_t rows = static_cast<int64_t>(g_count) * P.ppk * P.S;
     const int64_t grid = (rows + 7) / 8;
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
-    if (P.mpp <= kWideMaxHeads)
-        bwd_combine_wide_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    const dim3 cg(static_cast<unsigned>(grid));
+    cudaStream_t cst = static_cast<cudaStream_t>(stream);
+    if (P.mpp <= 2)
+        bwd_combine_wide_kernel<1><<<cg, 256, 0, cst>>>(P);
+    else if (P.mpp <= 4)
+        bwd_combine_wide_kernel<2><<<cg, 256, 0, cst>>>(P);
+    else if (P.mpp <= 6)
+        bwd_combine_wide_kernel<3><<<cg, 256, 0, cst>>>(P);
+    else if (P.mpp <= 8)
+        bwd_combine_wide_kernel<4><<<cg, 256, 0, cst>>>(P);
     else
         bwd_combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return check_launch();

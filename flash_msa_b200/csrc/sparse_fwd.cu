@@ -469,8 +469,13 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
 // Wide variant for Hq/Hp <= 8: the partial rows of all main heads of one edge are contiguous
 // (mpp * 256 bytes), so a warp reads them with 16-byte loads per lane in one sweep instead of one
 // 256-byte row at a time; weights go through shared memory.
+// KITER = number of 512-byte sweeps per edge record: Hq/Hp <= 2*KITER.  Templated so that the common
+// small head ratios keep few accumulators in registers and reach a high occupancy (the kernel is
+// bound by memory latency).
 constexpr int kWideMaxHeads = 8;
-__global__ void __launch_bounds__(256) combine_wide_kernel(const CombineParams P) {
+template <int KITER>
+__global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel(const CombineParams P) {
+    constexpr int kWideMaxHeads = 2 * KITER;
     __shared__ float wsm[8][32][kWideMaxHeads + 1];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + wib;
@@ -533,9 +538,9 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const CombineParams P
     }
     // pass B: lane owns 16-byte chunks ck = k*32 + lane of the mpp*128-element edge record
     const int nchunk = P.mpp * 16;
-    float acc[4][8];
+    float acc[KITER][8];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int k = 0; k < KITER; ++k)
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
     for (int s0 = 0; s0 < nslots; s0 += 32) {
@@ -546,13 +551,13 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const CombineParams P
             if (hh < P.mpp) wsm[wib][lane][hh] = sl >= 0 ? fast_exp2(stats[sl * lse_stride + hh].x - hm[hh]) / hs[hh] : 0.f;
         __syncwarp();
         const int cnt = min(32, nslots - s0);
-#pragma unroll 2
+#pragma unroll 4
         for (int i = 0; i < cnt; ++i) {
             const int64_t si = __shfl_sync(0xffffffffu, sl, i);
             if (si < 0) continue;
             const __nv_bfloat16* rec = P.o_part + si * P.mpp * kHeadDim;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < KITER; ++k) {
                 const int ck = k * 32 + lane;
                 if (ck < nchunk) {
                     const float wgt = wsm[wib][i][ck >> 4];
@@ -571,7 +576,7 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const CombineParams P
     __nv_bfloat16* orow = P.out + (static_cast<int64_t>(b) * P.S + q) * (static_cast<int64_t>(P.Hq) * kHeadDim) +
                           static_cast<int64_t>(p) * P.mpp * kHeadDim;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < KITER; ++k) {
         const int ck = k * 32 + lane;
         if (ck < nchunk) {
             uint4 o;
@@ -668,8 +673,16 @@ extern "C" int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_par
     const int64_t rows = static_cast<int64_t>(g_count) * P.ppk * P.S;
     const int64_t grid = (rows + 7) / 8;
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
-    if (P.mpp <= kWideMaxHeads)
-        combine_wide_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    const dim3 cg(static_cast<unsigned>(grid));
+    cudaStream_t cst = static_cast<cudaStream_t>(stream);
+    if (P.mpp <= 2)
+        combine_wide_kernel<1><<<cg, 256, 0, cst>>>(P);
+    else if (P.mpp <= 4)
+        combine_wide_kernel<2><<<cg, 256, 0, cst>>>(P);
+    else if (P.mpp <= 6)
+        combine_wide_kernel<3><<<cg, 256, 0, cst>>>(P);
+    else if (P.mpp <= 8)
+        combine_wide_kernel<4><<<cg, 256, 0, cst>>>(P);
     else
         combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return check_launch();
