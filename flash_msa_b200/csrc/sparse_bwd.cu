@@ -82,6 +82,8 @@ constexpr size_t kBwdSmemBytes = 7 * kTileBytes + 1024 + sizeof(BwdSmem);
 // bwd_combine_kernel): fp32 atomics for them would move ~6 GB through the L2 atomic units per step.
 __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
+                                                                    const __grid_constant__ CUtensorMap tmap_dq,
+                                                                    const __grid_constant__ CUtensorMap tmap_dqp,
                                                                     const BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -109,6 +111,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         fence_mbar_init();
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
+        prefetch_tmap(&tmap_dq);
+        if (P.with_kl) prefetch_tmap(&tmap_dqp);
     }
     if (warp == 0) {
         tmem_alloc(smem_u32(&sm->tmem_slot), 512);
@@ -328,7 +332,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
             }
             __syncthreads();
 
-            // ---- C: issuer: dQ^T first (so its store overlaps the rest), dV^T, dK^T, S of the next main tile ----
+            // ---- C: issuer: dV^T (frees the dO and P buffers), dQ^T, dK^T, S of the next main tile ----
             const bool s_ahead = has_next && !next_proxy && !is_proxy;
             if (issuer) {
                 tc_fence_after_sync();
@@ -339,10 +343,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     umma_tile_128<true, true>(t_s, qbuf, tile_ds, false, elect);        // dKp^T = Qp_g^T dSp
                     umma_commit(bar_dk, elect);
                 } else {
+                    umma_tile_128<true, true>(t_dv, tile_do, tile_p, kv_acc, elect);    // dV^T += dO_g^T P  (frees dO and P)
+                    umma_commit(bar_dv, elect);
                     umma_tile_128<true, false>(t_dp, tile_k, tile_ds, false, elect);    // dQ^T  = K_j^T dS^T
                     umma_commit(bar_dq, elect);
-                    umma_tile_128<true, true>(t_dv, tile_do, tile_p, kv_acc, elect);    // dV^T += dO_g^T P
-                    umma_commit(bar_dv, elect);
                     umma_tile_128<true, true>(t_dk, qbuf, tile_ds, kv_acc, elect);      // dK^T += Q_g^T dS
                     umma_commit(bar_dk, elect);
                     if (s_ahead) umma_tile_128<false, false>(t_s, tile_q0 + ((t + 1) & 1) * kTileBytes, tile_k, false, elect);
@@ -352,14 +356,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
             s_issued = s_ahead;
             dk_pending = true;
 
-            // ---- D: workers: store dQ^T, refill the dO buffer, reduce dKp^T ----
+            // ---- D: workers: refill the dO buffer, write dQ^T out, reduce dKp^T ----
             if (worker) {
+                if (!bad) bad = !mbar_wait(bar_dv, ph_dv);
+                ph_dv ^= 1;
+                if (has_next) gather_do(hh1, rb1);
+                cp_async_commit();
                 if (!bad) bad = !mbar_wait(bar_dq, ph_dq);
                 ph_dq ^= 1;
                 tc_fence_after_sync();
                 {
-                    // this thread: head-dimension index `row`, output rows = tile rows c0 .. c0+31.
-                    // The factor (scale, or scale/(B*Hp*S) for the proxy) is applied by the combine kernel.
+                    // This thread holds head-dimension index `row` of the output rows c0 .. c0+31 (the
+                    // factor scale, or scale/(B*Hp*S) for the proxy, is applied by the combine kernel).
+                    // A full chunk is transposed through the P buffer (free since dV^T) into dense
+                    // [row][d] order and leaves with ONE TMA tile store; the partial last chunk of a
+                    // reverse-index row is written directly.
+                    const bool full = (nrows == kBlock);
                     __nv_bfloat16* dst = is_proxy ? P.dqp_part + (slot0 + c0) * kHeadDim + row
                                                   : P.dq_part + ((slot0 + c0) * P.mpp + hh) * kHeadDim + row;
                     const int64_t rstride = is_proxy ? kHeadDim : static_cast<int64_t>(P.mpp) * kHeadDim;
@@ -368,13 +380,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                         uint32_t v[16];
                         tmem_ld16(tmem_addr(t_dp, quarter, c0 + c), v);
                         tmem_ld_wait();
-                        store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, nrows);
+                        if (full) {
+                            const uint32_t sbase = tile_p + static_cast<uint32_t>((c0 + c) * 256 + row * 2);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const __nv_bfloat16 hv = __float2bfloat16_rn(__uint_as_float(v[i]));
+                                asm volatile("st.shared.b16 [%0], %1;" ::"r"(sbase + i * 256), "h"(*reinterpret_cast<const uint16_t*>(&hv)) : "memory");
+                            }
+                        } else {
+                            store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, nrows);
+                        }
+                    }
+                    if (full) {
+                        fence_async_smem();
+                        named_barrier_sync(5, kBwdWorkers);
+                        if (tid == 0) {
+                            if (is_proxy) tma_store_3d(&tmap_dqp, tile_p, 0, 0, static_cast<int>(slot0));
+                            else tma_store_3d(&tmap_dq, tile_p, 0, hh, static_cast<int>(slot0));
+                            tma_store_commit();
+                        }
                     }
                 }
-                if (!bad) bad = !mbar_wait(bar_dv, ph_dv);
-                ph_dv ^= 1;
-                if (has_next) gather_do(hh1, rb1);
-                cp_async_commit();
                 if (is_proxy) {
                     if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
                     ph_dk ^= 1;
@@ -391,6 +417,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     }
                 }
                 cp_async_wait<0>();      // dO rows (or Kp_j) of the next tile have landed
+                if (tid == 0) tma_store_wait_read();   // the P buffer may be overwritten by the next tile
                 fence_async_smem();
                 tc_fence_before_sync();
             }
@@ -429,6 +456,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         __syncthreads();
     }
     cp_async_wait<0>();
+    if (tid == 0) tma_store_wait_all();
     if (bad) atomicMax(P.status, kStatusWaitTimeout);
     tc_fence_before_sync();
     __syncthreads();
@@ -682,9 +710,11 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     }
     FMSA_REQUIRE(aligned16(dq_part) && aligned16(dk_acc) && aligned16(dv_acc) &&
                  (!with_kl || (aligned16(dqp_part) && aligned16(dkp_acc))));
-    CUtensorMap tk, tv;
+    CUtensorMap tk, tv, tdq, tdqp;
     if (!make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
-        !make_tmap_bhsd(&tv, v->ptr, pb->B, pb->Hkv, pb->S, v->stride_b, v->stride_h, v->stride_s, 128))
+        !make_tmap_bhsd(&tv, v->ptr, pb->B, pb->Hkv, pb->S, v->stride_b, v->stride_h, v->stride_s, 128) ||
+        !make_tmap_partials(&tdq, dq_part, part_slots, pb->Hq / pb->Hp) ||
+        !make_tmap_partials(&tdqp, with_kl ? dqp_part : dq_part, part_slots, 1))
         return FMSA_ERR_CUDA;
 
     BwdParams P;
@@ -724,7 +754,7 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    sparse_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tk, tv, P);
+    sparse_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tk, tv, tdq, tdqp, P);
     return check_launch();
 }
 

@@ -73,10 +73,6 @@ struct TileMeta {   // what the epilogue of a finished main tile needs
     uint32_t parity;
 };
 
-__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
 // Thread layout: 16 worker warps; worker warp w reads TMEM lanes 32*(w%4)..+31 (tile rows) and owns
 // the 32 columns starting at 32*(w/4).  Warp 16 is the MMA issuer: a thread that issues tcgen05.mma
 // is held while the tensor core's queue is full, so it carries no other work.  Shared memory: K_j, V_j, Kp_j (resident for the sub-unit), two Q

@@ -55,6 +55,20 @@ inline bool make_tmap_bhsd(CUtensorMap* map, const void* base, uint64_t B, uint6
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Partial-row buffer [slots][heads][128] bf16 (heads = 1 gives the 2-D case) for tile STORES of
+// 128 slots x one head x 128 elements from a dense row-major shared-memory tile (no swizzle).
+inline bool make_tmap_partials(CUtensorMap* map, const void* base, uint64_t slots, uint64_t heads) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {128, heads, slots};
+    const cuuint64_t strides[2] = {256, 256 * heads};
+    const cuuint32_t box[3] = {128, 1, 128};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // A TMA-loadable activation: last dimension contiguous, every stride a multiple of 8 elements
 // (16 bytes), base 16-byte aligned.
 inline bool tma_compatible(const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
