@@ -48,9 +48,10 @@ WORKLOADS = {
                desc="long-context sparse MSA, B=1 S=65536 Hq=64 Hkv=8 Hp=16 Hpkv=8 top_k=32 blocks, sharded by KV group"),
 }
 SCALE = 128 ** -0.5
-# DRAM bytes per launch of the dominant kernel (sparse backward at c2) from the ncu capture
-# summarised in profiles/; None until a capture exists.
-BWD_TRAFFIC_BYTES_C2 = None
+# DRAM bytes per launch of the dominant kernel (sparse backward at c2): dram__bytes_read.sum +
+# dram__bytes_write.sum of the ncu capture summarised in profiles/sparse_bwd_kernel_c2q.md (a quarter-size
+# case), scaled by 4 to the full launch.
+BWD_TRAFFIC_BYTES_C2 = 4 * (260.143104e6 + 614.321664e6)
 
 
 def measured_peaks():
@@ -329,13 +330,16 @@ def main():
 
     # dominant kernel: the fused backward.  Algorithmic FLOPs per launch = 5 products over the
     # selected pairs of this rank's problem.
-    bwd_ms = statistics.mean(per_kernel.get("attn_bwd", [float("nan")]))
+    bwd_times = per_kernel.get("attn_bwd", [float("nan")])
+    bwd_ms_step = sum(bwd_times) / args.steps            # all launches of one step (large problems run in passes)
+    bwd_launches = len(bwd_times) / args.steps
     bwd_flops = flops(local) * 5.0 / 7.0
-    achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
+    achieved = bwd_flops / (bwd_ms_step * 1e-3) / 1e12
+    traffic = BWD_TRAFFIC_BYTES_C2 if (args.workload == "c2" and bwd_launches == 1) else None
     roofline = {"kernel": "sparse_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
-                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                "traffic": BWD_TRAFFIC_BYTES_C2 if args.workload == "c2" else None,
-                "peak_source": f"{peaks['source']} (burst cuBLAS bf16)", "ms_per_launch": bwd_ms}
+                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": traffic,
+                "peak_source": f"{peaks['source']} (burst cuBLAS bf16)", "ms_per_launch": bwd_ms_step / bwd_launches,
+                "launches_per_step": bwd_launches}
     step_total = sum(sum(v) for v in per_kernel.values()) / args.steps
     breakdown = {n: {"ms_per_step": sum(v) / args.steps, "share": (sum(v) / args.steps) / step_total if step_total else None}
                  for n, v in sorted(per_kernel.items())}
