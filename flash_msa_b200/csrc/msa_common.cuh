@@ -29,23 +29,20 @@ __host__ __device__ __forceinline__ int64_t dense_row_offset(int j, int S) {
 // on the device, so the sub-units are enumerated for the worst case (NB - j chunks) and a CTA that
 // draws a sub-unit beyond the real end of its row simply skips it.
 //
-// Order: (batch, KV head) group major, then key block ascending (long rows first), then sub-unit,
-// then proxy head of the group.  Group-major order keeps the rows that the active CTAs gather from
-// and reduce into (a few heads of Q, dO, dQ) resident in L2.
+// Order: (batch, KV head) group major, then sub-unit index s (chunks 8s .. 8s+7 of a row), then key
+// block ascending, then proxy head of the group.  Group-major order keeps the rows that the active
+// CTAs gather from and reduce into (a few heads of Q, dO) resident in L2.  Inside a group, putting s
+// outermost makes neighbouring sub-units alike in size (for a given s the rows of neighbouring key
+// blocks are about equally long, and the sub-units that lie beyond the end of their row cluster
+// together), so both a dynamic work counter and a static round-robin deal stay balanced.
 // -------------------------------------------------------------------------------------------
 constexpr int kChunksPerSubUnit = 8;
 
-// sum_{R=1..n} ceil(R / C)
-__host__ __device__ __forceinline__ int64_t ceil_sum(int n, int C) {
-    const int64_t a = n / C, b = n % C;
-    return C * (a * (a + 1) / 2) + (a + 1) * b;
-}
-// sub-units of key blocks 0..j-1 of one (group, proxy head): sum_{j'<j} ceil((NB-j')/C)
-__host__ __device__ __forceinline__ int64_t subunits_before(int j, int NB, int C) {
-    return ceil_sum(NB, C) - ceil_sum(NB - j, C);
-}
+// Key blocks j that can have a sub-unit s: NB - j > C*s, i.e. j < NB - C*s.
 __host__ __device__ __forceinline__ int64_t subunits_per_group(int NB, int ppk, int C) {
-    return ceil_sum(NB, C) * ppk;
+    int64_t total = 0;
+    for (int s = 0; s * C < NB; ++s) total += NB - s * C;
+    return total * ppk;
 }
 
 struct SubUnit {
@@ -58,14 +55,14 @@ __device__ __forceinline__ SubUnit decode_subunit(int64_t u, int NB, int ppk) {
     su.g = static_cast<int>(u / per_group);
     const int64_t r = u % per_group;
     su.pp = static_cast<int>(r % ppk);
-    const int64_t x = r / ppk;
-    int lo = 0, hi = NB - 1;   // largest j with subunits_before(j) <= x
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (subunits_before(mid, NB, C) <= x) lo = mid; else hi = mid - 1;
+    int64_t x = r / ppk;
+    int s = 0;
+    while (x >= NB - s * C) {   // at most NB/C iterations
+        x -= NB - s * C;
+        ++s;
     }
-    su.j = lo;
-    su.chunk0 = static_cast<int>(x - subunits_before(lo, NB, C)) * C;
+    su.j = static_cast<int>(x);
+    su.chunk0 = s * C;
     return su;
 }
 

@@ -52,34 +52,37 @@ struct FwdParams {
 };
 
 struct FwdSmem {
-    uint64_t bar_kv, bar_kp, bar_s[2], bar_o[2];
+    uint64_t bar_kv, bar_kp, bar_done;
+    uint64_t q_full[2];              // Q rows of a tile have landed (arrivals: the store group)
+    uint64_t s_full[2], s_empty[2];  // S accumulator written by the tensor core / read by the softmax group
+    uint64_t p_full;                 // P written to shared memory (arrivals: the softmax group)
+    uint64_t o_full[2], o_empty[2];  // O accumulator written by the tensor core / read by the store group
+    uint64_t unit_full[4];           // a sub-unit index has been published in unit_ring
+    int32_t unit_ring[4];
     uint32_t tmem_slot;
-    int32_t unit;
-    int32_t rows[4][128];
-    float rmax[2][4][128];   // per tile parity: partial row maxima of the four column groups
-    float lsum[2][4][128];   // partial row sums
-    float mrow[2][128];      // row maximum (scaled, log2 domain)
+    int32_t rows[8][128];            // query positions of the chunks in flight (ring)
+    float rmax[4][128];              // row maxima of the four column groups
+    float lsum[4][128];              // row sums of the four column groups
 };
 
-constexpr int kFwdWorkers = 512;                // 16 worker warps
-constexpr int kFwdThreads = kFwdWorkers + 32;   // + one warp whose lane 0 only issues tcgen05.mma
+constexpr int kFwdSoftmax = 512;                              // 16 warps: thread = (tile row, 32 columns)
+constexpr int kFwdStore = 256;                                // 8 warps: thread = (head-dim lane, 64 tile rows)
+constexpr int kFwdThreads = kFwdSoftmax + kFwdStore + 32;     // + one warp that issues tcgen05.mma
 constexpr size_t kFwdSmemBytes = 6 * kTileBytes + 1024 + sizeof(FwdSmem);
 
-struct TileMeta {   // what the epilogue of a finished main tile needs
-    int64_t slot0;  // (edge - edge_base) of tile row 0
-    int nrows;
-    int head;       // head inside the proxy group
-    int obuf;
-    uint32_t parity;
-};
-
-// Thread layout: 16 worker warps; worker warp w reads TMEM lanes 32*(w%4)..+31 (tile rows) and owns
-// the 32 columns starting at 32*(w/4).  Warp 16 is the MMA issuer: a thread that issues tcgen05.mma
-// is held while the tensor core's queue is full, so it carries no other work.  Shared memory: K_j, V_j, Kp_j (resident for the sub-unit), two Q
-// buffers (rows gathered two tiles ahead), one P buffer (P*V of a tile is issued before S of the
-// next one, so it has finished reading P by the time the next softmax may write).  TMEM: two S and two O accumulators, so
-// the elected thread can issue P*V of this tile and S of the next one back to back while the
-// other threads store the previous tile's output.
+// Warp-specialised forward.  Three roles run decoupled and meet only through mbarriers:
+//   warps 0-15  softmax group : thread = (tile row, 32-column group); reads S from TMEM, writes P (bf16)
+//                               to shared memory and the per-row (max, sum) to global memory;
+//   warps 16-23 store group   : gathers the Q rows two tiles ahead (cp.async) and writes the finished
+//                               O^T accumulators out as unnormalised bf16 partial rows;
+//   warp 24     issuer        : loads K_j, V_j, Kp_j by TMA and issues S(t+1) = Q K^T, then
+//                               O^T(t) = V^T P^T(t), so the softmax of one tile overlaps the products of
+//                               its neighbours and the store of the tile before.  All its lanes run the
+//                               same code; only lane 0's tcgen05 instructions take effect (a lone
+//                               diverged lane is scheduled late).
+// Work is drawn from a global counter by one thread of the store group and published to the other
+// roles through a four-entry ring, so every role walks the same sequence of sub-units.
+// TMEM: S[2] at columns 0 and 128, O^T[2] at 256 and 384.
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
                                                                     const __grid_constant__ CUtensorMap tmap_kp,
@@ -91,21 +94,27 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     FwdSmem* sm = reinterpret_cast<FwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 6 * kTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool worker = warp < 16;
-    const bool issuer = (warp == 16);            // the whole warp runs the issue sequence ...
-    const uint32_t elect = (lane == 0) ? 1u : 0u;   // ... and only this lane's instructions take effect
-    const int quarter = warp & 3, cg = (warp >> 2) & 3;
-    const int row = quarter * 32 + lane, c0 = cg * 32;
-    const GatherLane glane = make_gather_lane(tid & 511);
-    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_kp = smem_u32(&sm->bar_kp);
+    const int role = warp < 16 ? 0 : (warp < 24 ? 1 : 2);   // 0 softmax group, 1 store group, 2 issuer
+    const int quarter = warp & 3;                            // TMEM lane quarter this warp may read
+    const int row = quarter * 32 + lane;                     // softmax: tile row; store: head-dimension index
+    const uint32_t elect = (lane == 0) ? 1u : 0u;
+    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_kp = smem_u32(&sm->bar_kp), bar_done = smem_u32(&sm->bar_done);
+    const uint32_t p_full = smem_u32(&sm->p_full);
+    auto B2 = [&](uint64_t* arr, uint32_t i) { return smem_u32(&arr[i & 1]); };
 
     if (tid == 0) {
         mbar_init(bar_kv, 1);
         mbar_init(bar_kp, 1);
+        mbar_init(bar_done, 1);
+        mbar_init(p_full, kFwdSoftmax / 32);   // one arrival per warp: hundreds of arrivals on one barrier serialise
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&sm->bar_s[i]), 1);
-            mbar_init(smem_u32(&sm->bar_o[i]), 1);
+            mbar_init(smem_u32(&sm->q_full[i]), kFwdStore / 32);
+            mbar_init(smem_u32(&sm->s_full[i]), 1);
+            mbar_init(smem_u32(&sm->s_empty[i]), kFwdSoftmax / 32);
+            mbar_init(smem_u32(&sm->o_full[i]), 1);
+            mbar_init(smem_u32(&sm->o_empty[i]), kFwdStore / 32);
         }
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sm->unit_full[i]), 1);
         fence_mbar_init();
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
@@ -125,16 +134,27 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     const int lse_stride = P.mpp + 1;
     const int64_t edge_base = P.dense ? dense_edge_base(static_cast<int64_t>(P.g_begin) * P.ppk, P.S, P.NB)
                                       : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
-    uint32_t ph_kv = 0, ph_kp = 0;
-    uint32_t gt = 0;   // tiles processed so far by this CTA: selects the S, Q, P and statistics buffers
-    uint32_t mt = 0;   // main tiles so far: selects the O accumulator
-    bool bad = false;  // a bounded wait gave up: later waits are skipped, the status word is set at the end
+    uint32_t gt = 0;    // tiles seen so far by this CTA (every role counts the same sequence)
+    uint32_t mt = 0;    // main-head tiles seen so far
+    uint32_t nsub = 0;  // sub-units with work seen so far
+    bool bad = false;   // a bounded wait gave up: later waits are skipped, the status word is set at the end
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        if (!bad) bad = !mbar_wait(bar, parity);
+    };
+    auto warp_arrive = [&](uint32_t bar) {   // every lane has finished (and fenced) its part; one arrival per warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+    };
 
-    for (;;) {
-        if (tid == 0) sm->unit = atomicAdd(P.counter, 1);
-        __syncthreads();
-        const int u = sm->unit;
-        __syncthreads();
+    for (uint32_t draw = 0;; ++draw) {
+        // The drawing thread cannot get more than three sub-units ahead of the slowest role (its own
+        // group needs the other roles' results to finish a sub-unit), so a ring of four is enough.
+        if (tid == kFwdSoftmax) {
+            sm->unit_ring[draw & 3] = atomicAdd(P.counter, 1);
+            mbar_arrive(smem_u32(&sm->unit_full[draw & 3]));
+        }
+        wait(smem_u32(&sm->unit_full[draw & 3]), (draw >> 2) & 1);
+        const int64_t u = sm->unit_ring[draw & 3];
         if (u >= P.n_subunits) break;
         const SubUnit su = decode_subunit(u, P.NB, P.ppk);
         const int j = su.j;
@@ -154,123 +174,78 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         const int chunk0 = su.chunk0;
         const int chunk1 = min((n + kBlock - 1) / kBlock, chunk0 + kChunksPerSubUnit);
         if (chunk1 <= chunk0) continue;   // this sub-unit lies beyond the end of the row
-        if (tid == 0) {
-            mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-            tma_load_tile(tile_k, &tmap_k, j * kBlock, kvh, b, bar_kv);
-            tma_load_tile(tile_v, &tmap_v, j * kBlock, kvh, b, bar_kv);
-            if (P.with_proxy) {
-                mbar_arrive_expect_tx(bar_kp, kTileBytes);
-                tma_load_tile(tile_kp, &tmap_kp, j * kBlock, p / P.pg, b, bar_kp);
-            }
-        }
         const int ntiles = (chunk1 - chunk0) * hpc;
-        const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
-        const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
 
-        auto stage_rows = [&](int chunk, int rb) {
-            if (tid < kBlock) {
-                const int at = chunk * kBlock + tid;
-                int qid = -1;
-                if (at < n) {
-                    qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
-                    if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
-                        atomicMax(P.status, kStatusBadIndex);
-                        qid = -1;
-                    }
+        if (role == 2) {
+            // =========================== issuer ===========================
+            if (nsub > 0) wait(bar_done, (nsub - 1) & 1);   // every product of the previous sub-unit has finished
+            if (elect) {
+                mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
+                tma_load_tile(tile_k, &tmap_k, j * kBlock, kvh, b, bar_kv);
+                tma_load_tile(tile_v, &tmap_v, j * kBlock, kvh, b, bar_kv);
+                if (P.with_proxy) {
+                    mbar_arrive_expect_tx(bar_kp, kTileBytes);
+                    tma_load_tile(tile_kp, &tmap_kp, j * kBlock, p / P.pg, b, bar_kp);
                 }
-                sm->rows[rb][tid] = qid;
             }
-        };
-        // rows of a tile (main head hh or the proxy head) into the Q buffer selected by the global tile count
-        auto gather_q = [&](int hh, int rb, uint32_t gtile) {
-            const uint32_t dst = tile_q0 + (gtile & 1) * kTileBytes;
-            if (hh < P.mpp)
-                gather_tile_512(dst, q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh, P.q_ss, sm->rows[rb], glane);
-            else
-                gather_tile_512(dst, qp_bp, P.qp_ss, sm->rows[rb], glane);
-        };
-        auto issue_s = [&](bool proxy, uint32_t gtile) {   // issuer warp
-            umma_tile_128<false, false>(tmem_s0 + (gtile & 1) * 128, tile_q0 + (gtile & 1) * kTileBytes,
-                                        proxy ? tile_kp : tile_k, false, elect);
-            umma_commit(smem_u32(&sm->bar_s[gtile & 1]), elect);
-        };
-        // The output product is issued transposed (O^T = V_j^T P^T: TMEM lane = head-dimension index,
-        // column = tile row), so the 32 lanes of a warp store 32 consecutive elements of ONE partial
-        // row per instruction instead of touching 32 different rows.  The rows are stored
-        // unnormalised; the combine kernel divides by the row sums kept in stat_part.
-        auto epilogue = [&](const TileMeta& m) {
-            if (!bad) bad = !mbar_wait(smem_u32(&sm->bar_o[m.obuf]), m.parity);
-            tc_fence_after_sync();
-            __nv_bfloat16* dst = P.o_part + ((m.slot0 + c0) * P.mpp + m.head) * kHeadDim + row;
-            const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
-#pragma unroll
-            for (int c = 0; c < 32; c += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_addr(tmem_o0 + m.obuf * 128, quarter, c0 + c), v);
-                tmem_ld_wait();
-                store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, m.nrows);
-            }
-            tc_fence_before_sync();
-        };
-
-        // ---- prologue: rows, the first two Q tiles, S of tile 0 ----
-        // (chunk, head, row-list buffer) of local tiles 0, 1, 2 without divisions
-        int hh = 0, chunk = chunk0, rb = 0;
-        int hh1 = 1, chunk_1 = chunk0, rb1 = 0;
-        if (hh1 == hpc) { hh1 = 0; ++chunk_1; rb1 = 1; }
-        int hh2 = hh1 + 1, chunk_2 = chunk_1, rb2 = rb1;
-        if (hh2 == hpc) { hh2 = 0; ++chunk_2; rb2 = (rb1 + 1) & 3; }
-        stage_rows(chunk0, 0);
-        if (ntiles > 1 && chunk_1 != chunk0) stage_rows(chunk_1, rb1);
-        if (ntiles > 2 && chunk_2 != chunk_1) stage_rows(chunk_2, rb2);
-        __syncthreads();
-        if (worker) {
-            gather_q(0, 0, gt);
-            cp_async_commit();
-            if (ntiles > 1) gather_q(hh1, rb1, gt + 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-            fence_async_smem();
-        }
-        __syncthreads();
-        if (issuer) {
-            if (!bad) bad = !mbar_wait(bar_kv, ph_kv);
-            tc_fence_after_sync();
+            __syncwarp();
+            wait(bar_kv, nsub & 1);
+            bool kp_ready = false;
+            auto issue_s = [&](bool proxy, uint32_t gtile) {
+                if (proxy && !kp_ready) {
+                    wait(bar_kp, nsub & 1);
+                    kp_ready = true;
+                }
+                wait(B2(sm->q_full, gtile), (gtile >> 1) & 1);
+                if (gtile >= 2) wait(B2(sm->s_empty, gtile), ((gtile >> 1) - 1) & 1);
+                tc_fence_after_sync();
+                umma_tile_128<false, false>(tmem_s0 + (gtile & 1) * 128, tile_q0 + (gtile & 1) * kTileBytes,
+                                            proxy ? tile_kp : tile_k, false, elect);
+                umma_commit(B2(sm->s_full, gtile), elect);
+            };
             issue_s(false, gt);
-        }
-        ph_kv ^= 1;
-        bool kp_ready = false;
-        TileMeta prev{};
-        bool have_prev = false;
-
-        for (int t = 0; t < ntiles; ++t, ++gt) {
-            const bool is_proxy = hh == P.mpp;
-            const int sb = gt & 1;
-            int hh3 = hh2 + 1, chunk_3 = chunk_2, rb3 = rb2;
-            if (hh3 == hpc) { hh3 = 0; ++chunk_3; rb3 = (rb2 + 1) & 3; }
-            const int nrows = min(kBlock, n - chunk * kBlock);
-            const int64_t slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
-            bool live = false;
-            if (worker) {
-                const int qid = sm->rows[rb][row];
-                live = qid >= 0;
+            int hh = 0;
+            for (int t = 0; t < ntiles; ++t, ++gt) {
+                const bool is_proxy = hh == P.mpp;
+                int hh1 = hh + 1;
+                if (hh1 == hpc) hh1 = 0;
+                if (t + 1 < ntiles) issue_s(hh1 == P.mpp, gt + 1);     // S of the next tile first: the softmax group never starves
+                if (!is_proxy) {
+                    wait(p_full, mt & 1);
+                    if (mt >= 2) wait(B2(sm->o_empty, mt), ((mt >> 1) - 1) & 1);
+                    tc_fence_after_sync();
+                    umma_tile_128<true, false>(tmem_o0 + (mt & 1) * 128, tile_v, tile_p, false, elect);   // O^T = V_j^T P^T
+                    umma_commit(B2(sm->o_full, mt), elect);
+                    ++mt;
+                }
+                hh = hh1;
+            }
+            umma_commit(bar_done, elect);
+            if (P.with_proxy && !kp_ready) wait(bar_kp, nsub & 1);   // (every chunk has a proxy tile, so this never waits)
+        } else if (role == 0) {
+            // =========================== softmax group ===========================
+            const int cg = warp >> 2, c0 = cg * 32;
+            int hh = 0, chunk = chunk0;
+            bool prev_main = false;
+            uint32_t prev_mt = 0;
+            for (int t = 0; t < ntiles; ++t, ++gt) {
+                const bool is_proxy = hh == P.mpp;
+                const int sb = gt & 1;
+                const int nrows = min(kBlock, n - chunk * kBlock);
+                wait(B2(sm->s_full, gt), (gt >> 1) & 1);
+                tc_fence_after_sync();
+                // (the row list was published by the store group before it released the Q rows S was computed from)
+                const int qid = sm->rows[(chunk - chunk0) & 7][row];
+                const bool live = qid >= 0;
                 // only the first chunk of a reverse-index row can hold rows of the key block itself
                 const bool masked = (chunk == 0);
                 const int limit = (masked && live && (qid >> 7) == j) ? (qid & 127) : 127;
-
-                if (!bad) bad = !mbar_wait(smem_u32(&sm->bar_s[sb]), (gt >> 1) & 1);
-                tc_fence_after_sync();
-                // rows needed three tiles ahead, then the gather of tile t+2 into the Q buffer S(t) just released
-                if (t + 3 < ntiles && chunk_3 != chunk_2) stage_rows(chunk_3, rb3);
-                if (t + 2 < ntiles) gather_q(hh2, rb2, gt + 2);
-                cp_async_commit();
-
-                // ---- softmax of this thread's (row, 32 columns): pass 1 maximum, pass 2 exponentials ----
+                const uint32_t ts = tmem_s0 + sb * 128;
                 float mloc = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 32; c += 16) {
                     uint32_t v[16];
-                    tmem_ld16(tmem_addr(tmem_s0 + sb * 128, quarter, c0 + c), v);
+                    tmem_ld16(tmem_addr(ts, quarter, c0 + c), v);
                     tmem_ld_wait();
                     if (masked) {
 #pragma unroll
@@ -280,15 +255,16 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         for (int i = 0; i < 16; ++i) mloc = fmaxf(mloc, __uint_as_float(v[i]));
                     }
                 }
-                sm->rmax[sb][cg][row] = mloc;      // raw logits: scale > 0, so the maximum commutes with it
-                named_barrier_sync(1 + quarter, 128);
-                const float m = fmaxf(fmaxf(sm->rmax[sb][0][row], sm->rmax[sb][1][row]),
-                                      fmaxf(sm->rmax[sb][2][row], sm->rmax[sb][3][row])) * P.scale_log2e;
+                sm->rmax[cg][row] = mloc;               // raw logits: scale > 0, so the maximum commutes with it
+                named_barrier_sync(1 + quarter, 128);   // the four warps that share these 32 rows
+                const float m = fmaxf(fmaxf(sm->rmax[0][row], sm->rmax[1][row]), fmaxf(sm->rmax[2][row], sm->rmax[3][row])) *
+                                P.scale_log2e;
+                if (!is_proxy && prev_main) wait(B2(sm->o_full, prev_mt), (prev_mt >> 1) & 1);   // P*V of the previous tile has read P
                 float l = 0.f;
 #pragma unroll
                 for (int c = 0; c < 32; c += 16) {
                     uint32_t v[16];
-                    tmem_ld16(tmem_addr(tmem_s0 + sb * 128, quarter, c0 + c), v);
+                    tmem_ld16(tmem_addr(ts, quarter, c0 + c), v);
                     tmem_ld_wait();
                     uint32_t pk[8];
 #pragma unroll
@@ -309,57 +285,140 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                                          pk[4 * k8 + 2], pk[4 * k8 + 3]);
                     }
                 }
-                sm->lsum[sb][cg][row] = l;
-                if (cg == 0) sm->mrow[sb][row] = m;
-                cp_async_wait<1>();      // Q rows of tile t+1 have landed (tile t+2 may still be in flight)
-                fence_async_smem();
                 tc_fence_before_sync();
-            }
-            __syncthreads();
-
-            // ---- P*V of this tile and S of the next one ----
-            const bool next_proxy = (t + 1 < ntiles) && (hh1 == P.mpp);
-            if (issuer) {
-                tc_fence_after_sync();
+                warp_arrive(B2(sm->s_empty, gt));
                 if (!is_proxy) {
-                    umma_tile_128<true, false>(tmem_o0 + (mt & 1) * 128, tile_v, tile_p, false, elect);   // O^T = V_j^T P^T
-                    umma_commit(smem_u32(&sm->bar_o[mt & 1]), elect);
+                    fence_async_smem();
+                    warp_arrive(p_full);
+                    prev_main = true;
+                    prev_mt = mt;
+                    ++mt;
                 }
+                sm->lsum[cg][row] = l;
+                named_barrier_sync(1 + quarter, 128);
+                if (cg == 0 && live && row < nrows) {
+                    const int64_t slot = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock + row;
+                    float2* st = reinterpret_cast<float2*>(P.stat_part) + slot * lse_stride + hh;
+                    *st = make_float2(m, sm->lsum[0][row] + sm->lsum[1][row] + sm->lsum[2][row] + sm->lsum[3][row]);
+                }
+                if (++hh == hpc) {
+                    hh = 0;
+                    ++chunk;
+                }
+            }
+        } else {
+            // =========================== store group ===========================
+            const int etid = tid - kFwdSoftmax;
+            const int c0 = ((warp - 16) >> 2) * 64;   // this thread's 64 tile rows of the transposed accumulator
+            const GatherLane glane = make_gather_lane(etid);
+            const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
+            const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
+            auto stage_rows = [&](int chunk) {
+                if (etid < kBlock) {
+                    const int at = chunk * kBlock + etid;
+                    int qid = -1;
+                    if (at < n) {
+                        qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
+                        if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
+                            atomicMax(P.status, kStatusBadIndex);
+                            qid = -1;
+                        }
+                    }
+                    sm->rows[(chunk - chunk0) & 7][etid] = qid;
+                }
+            };
+            // 256 threads move a 128-row tile: thread (r0 = etid/16, 16-byte chunk etid%16) covers rows r0 + 16k
+            auto gather_q = [&](int hh, int chunk, uint32_t gtile) {
+                const uint32_t dst = tile_q0 + (gtile & 1) * kTileBytes;
+                const int* rows = sm->rows[(chunk - chunk0) & 7];
+                const __nv_bfloat16* base = (hh < P.mpp) ? q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh : qp_bp;
+                const int64_t stride = (hh < P.mpp) ? P.q_ss : P.qp_ss;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int rowid = rows[glane.r0 + 16 * k];
+                    const bool ok = rowid >= 0;
+                    cp_async_16(dst + glane.dst_off + k * 2048, base + static_cast<int64_t>(ok ? rowid : 0) * stride + glane.col, ok);
+                }
+            };
+            struct Meta { int64_t slot0; int nrows; int head; uint32_t mt; };
+            auto epilogue = [&](const Meta& m) {
+                const int ob = m.mt & 1;
+                wait(B2(sm->o_full, m.mt), (m.mt >> 1) & 1);
+                tc_fence_after_sync();
+                // O^T: TMEM lane = head-dimension index, column = tile row: 32 lanes store 64 contiguous
+                // bytes of ONE partial row per instruction
+                __nv_bfloat16* dst = P.o_part + ((m.slot0 + c0) * P.mpp + m.head) * kHeadDim + row;
+                const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
+#pragma unroll
+                for (int c = 0; c < 64; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_addr(tmem_o0 + ob * 128, quarter, c0 + c), v);
+                    tmem_ld_wait();
+                    store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, m.nrows);
+                }
+                tc_fence_before_sync();
+                warp_arrive(B2(sm->o_empty, m.mt));
+            };
+
+            // tile walk (head, chunk) for tiles t, t+1, t+2, t+3 without divisions
+            int hh = 0, chunk = chunk0;
+            int hh1 = 1, chunk_1 = chunk0;
+            if (hh1 == hpc) { hh1 = 0; ++chunk_1; }
+            int hh2 = hh1 + 1, chunk_2 = chunk_1;
+            if (hh2 == hpc) { hh2 = 0; ++chunk_2; }
+            // prologue: row lists of the first three tiles, Q rows of the first two
+            stage_rows(chunk0);
+            if (ntiles > 1 && chunk_1 != chunk0) stage_rows(chunk_1);
+            if (ntiles > 2 && chunk_2 != chunk_1) stage_rows(chunk_2);
+            named_barrier_sync(5, kFwdStore);
+            if (gt >= 2) wait(B2(sm->s_full, gt), ((gt >> 1) - 1) & 1);        // the Q buffers' last readers are done
+            if (gt >= 1) wait(B2(sm->s_full, gt + 1), (((gt + 1) >> 1) - 1) & 1);
+            gather_q(0, chunk0, gt);
+            cp_async_commit();
+            if (ntiles > 1) gather_q(hh1, chunk_1, gt + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+            fence_async_smem();
+            warp_arrive(B2(sm->q_full, gt));
+            Meta prev{};
+            bool have_prev = false;
+            for (int t = 0; t < ntiles; ++t, ++gt) {
+                const bool is_proxy = hh == P.mpp;
+                int hh3 = hh2 + 1, chunk_3 = chunk_2;
+                if (hh3 == hpc) { hh3 = 0; ++chunk_3; }
+                // Q rows of tile t+2 go into the buffer S(t) has finished reading
+                if (t + 2 < ntiles) {
+                    wait(B2(sm->s_full, gt), (gt >> 1) & 1);
+                    gather_q(hh2, chunk_2, gt + 2);
+                }
+                cp_async_commit();
+                if (t + 3 < ntiles && chunk_3 != chunk_2) stage_rows(chunk_3);
                 if (t + 1 < ntiles) {
-                    if (next_proxy && !kp_ready && !bad) bad = !mbar_wait(bar_kp, ph_kp);
-                    issue_s(next_proxy, gt + 1);
+                    cp_async_wait<1>();     // tile t+1 has landed (t+2 may still be in flight)
+                    fence_async_smem();
+                    warp_arrive(B2(sm->q_full, gt + 1));
                 }
+                named_barrier_sync(5, kFwdStore);   // row list of tile t+3 visible to the whole group before its gather
+                if (have_prev) epilogue(prev);
+                have_prev = false;
+                if (!is_proxy) {
+                    prev.slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
+                    prev.nrows = min(kBlock, n - chunk * kBlock);
+                    prev.head = hh;
+                    prev.mt = mt;
+                    ++mt;
+                    have_prev = true;
+                }
+                hh = hh1; chunk = chunk_1;
+                hh1 = hh2; chunk_1 = chunk_2;
+                hh2 = hh3; chunk_2 = chunk_3;
             }
-            if (next_proxy) kp_ready = true;
-            // ---- row statistics of this tile (one thread per row): maximum (log2 domain) and sum ----
-            if (worker && cg == 0 && row < nrows && live) {
-                const float lt = sm->lsum[sb][0][row] + sm->lsum[sb][1][row] + sm->lsum[sb][2][row] + sm->lsum[sb][3][row];
-                float2* st = reinterpret_cast<float2*>(P.stat_part) + (slot0 + row) * lse_stride + hh;
-                *st = make_float2(sm->mrow[sb][row], lt);
-            }
-            // ---- output rows of the previous main tile, while the tensor core works ----
-            if (have_prev && worker) epilogue(prev);
-            have_prev = false;
-            if (!is_proxy) {
-                prev.slot0 = slot0;
-                prev.nrows = nrows;
-                prev.head = hh;
-                prev.obuf = mt & 1;
-                prev.parity = (mt >> 1) & 1;
-                ++mt;
-                have_prev = true;
-            }
-            hh = hh1; chunk = chunk_1; rb = rb1;
-            hh1 = hh2; chunk_1 = chunk_2; rb1 = rb2;
-            hh2 = hh3; chunk_2 = chunk_3; rb2 = rb3;
+            if (have_prev) epilogue(prev);
         }
-        if (P.with_proxy) ph_kp ^= 1;
-        // drain: the last main tile of the sub-unit
-        __syncthreads();
-        if (have_prev && worker) epilogue(prev);
-        __syncthreads();
+        ++nsub;
     }
     cp_async_wait<0>();
+    if (role == 2 && nsub > 0) wait(bar_done, (nsub - 1) & 1);
     if (bad) atomicMax(P.status, kStatusWaitTimeout);
     tc_fence_before_sync();
     __syncthreads();
