@@ -292,6 +292,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                 // (they are the smallest query positions), so only there the causal mask is needed.
                 const bool masked = (chunk == 0);
                 const float neg_lse = -raw_lse * kLog2e;
+                const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e), nl2 = f2_pack(neg_lse, neg_lse);
+                const uint64_t nd2 = f2_pack(-row_delta, -row_delta);
 #pragma unroll
                 for (int c = 0; c < 32; c += 16) {
                     uint32_t sv[16], dv[16];
@@ -301,15 +303,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     uint32_t pk[8], dk[8];
 #pragma unroll
                     for (int i = 0; i < 16; i += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(sv[i]), P.scale_log2e, neg_lse));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), P.scale_log2e, neg_lse));
+                        float p0, p1;
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl2), p0, p1);
+                        p0 = fast_exp2(p0);
+                        p1 = fast_exp2(p1);
                         if (masked) {
                             p0 = (c0 + c + i <= limit) ? p0 : 0.f;
                             p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
                         }
                         if (!is_proxy) {
-                            const float d0 = p0 * (__uint_as_float(dv[i]) - row_delta);
-                            const float d1 = p1 * (__uint_as_float(dv[i + 1]) - row_delta);
+                            const uint64_t pp = f2_pack(p0, p1);
+                            float d0, d1;   // dS = P o (dP - delta)
+                            f2_unpack(f2_mul(pp, f2_add(f2_pack(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), nd2)), d0, d1);
                             pk[i >> 1] = pack_bf16(p0, p1);
                             dk[i >> 1] = pack_bf16(d0, d1);
                             teacher[(c + i) >> 1] = __hadd2(teacher[(c + i) >> 1], __floats2half2_rn(p0, p1));

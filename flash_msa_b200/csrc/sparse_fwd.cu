@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         for (int i = 0; i < 16; ++i) mloc = (c0 + c + i <= limit) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) mloc = fmaxf(mloc, __uint_as_float(v[i]));
+                        for (int i = 0; i < 16; i += 2) mloc = fmax3(mloc, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
                     }
                 }
                 sm->rmax[cg][row] = mloc;               // raw logits: scale > 0, so the maximum commutes with it
@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 const float m = fmaxf(fmaxf(sm->rmax[0][row], sm->rmax[1][row]), fmaxf(sm->rmax[2][row], sm->rmax[3][row])) *
                                 P.scale_log2e;
                 if (!is_proxy && prev_main) wait(B2(sm->o_full, prev_mt), (prev_mt >> 1) & 1);   // P*V of the previous tile has read P
-                float l = 0.f;
+                uint64_t l2 = f2_pack(0.f, 0.f);
+                const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e), nm2 = f2_pack(-m, -m);
 #pragma unroll
                 for (int c = 0; c < 32; c += 16) {
                     uint32_t v[16];
@@ -269,13 +270,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     uint32_t pk[8];
 #pragma unroll
                     for (int i = 0; i < 16; i += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), P.scale_log2e, -m));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), P.scale_log2e, -m));
+                        float p0, p1;
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2), p0, p1);
+                        p0 = fast_exp2(p0);
+                        p1 = fast_exp2(p1);
                         if (masked) {
                             p0 = (c0 + c + i <= limit) ? p0 : 0.f;
                             p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
                         }
-                        l += p0 + p1;
+                        l2 = f2_add(l2, f2_pack(p0, p1));
                         pk[i >> 1] = pack_bf16(p0, p1);
                     }
                     if (!is_proxy) {
@@ -285,6 +288,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                                          pk[4 * k8 + 2], pk[4 * k8 + 3]);
                     }
                 }
+                float l, l_hi;
+                f2_unpack(l2, l, l_hi);
+                l += l_hi;
                 tc_fence_before_sync();
                 warp_arrive(B2(sm->s_empty, gt));
                 if (!is_proxy) {
