@@ -187,6 +187,46 @@ def reference_arm(args, cfg):
 
 
 # --------------------------------------------------------------------------------------------
+# bandwidth kernels at long-context size (they are launch-latency dominated at c2)
+# --------------------------------------------------------------------------------------------
+def micro_select(args):
+    """Achieved GB/s of the top-k pick and of the reverse index on materialised scores of the
+    config-5 size (B*Hp = 16, S = 65536, NB = 512, top_k = 32 blocks).  Algorithmic bytes:
+    top-k reads the causal half of the fp32 scores and writes Kb int32 per row; the reverse index
+    reads block_indices twice and writes col_q, edge_pos and row_ptr."""
+    from flash_msa_b200 import ops
+    dev = torch.device("cuda", 0)
+    rows_bh, s, kb = 16, 65536, 32
+    nb = s // 128
+    peaks = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    scores = torch.randn(1, rows_bh, s, nb, device=dev, generator=gen)
+    idx = ops.select_topk(scores, kb)
+    rix = ops.build_reverse_index(idx)
+    torch.cuda.synchronize()
+    edges = int(rix.row_ptr[-1].item())
+    bytes_topk = rows_bh * sum((q // 128 + 1) for q in range(0, s, 128)) * 128 * 4 + rows_bh * s * kb * 4
+    bytes_rix = 2 * rows_bh * s * kb * 4 + edges * 4 + rows_bh * s * kb * 4 + (rows_bh * nb + 1) * 4
+    out = {}
+    for name, fn, nbytes in (("select_topk", lambda: ops.select_topk(scores, kb), bytes_topk),
+                             ("reverse_index", lambda: ops.build_reverse_index(idx), bytes_rix)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in ev:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        ms = statistics.median(a.elapsed_time(b) for a, b in ev)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "algorithmic_bytes": nbytes, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                     "peak_GB/s": peaks["hbm_gbs"], "peak_source": peaks["source"]}
+    print(json.dumps({"micro": "select kernels at B*Hp=16 S=65536 top_k=32 blocks", "edges": edges, **out}))
+
+
+# --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
 def main():
@@ -198,7 +238,11 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--micro-select", action="store_true", help="time the top-k and reverse-index kernels at config-5 size")
     args = ap.parse_args()
+    if args.micro_select:
+        micro_select(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
     cfg = dict(WORKLOADS[args.workload])
 
