@@ -173,19 +173,40 @@ __device__ __forceinline__ void umma_commit(uint32_t bar, uint32_t elect = 1u) {
 // 32 bytes inside a panel and jump to the second panel after four steps; MN-major steps advance
 // by 16 rows = 2048 bytes.  Adding the encoded step to the low word keeps the issue loop at a few
 // instructions per MMA, which matters because a single thread feeds the tensor core.
+__host__ __device__ constexpr uint32_t umma_kstep(bool mn_major, int ks) {
+    return mn_major ? static_cast<uint32_t>(ks) * (2048u >> 4)
+                    : static_cast<uint32_t>(ks >> 2) * (kPanelBytes >> 4) + static_cast<uint32_t>(ks & 3) * 2u;
+}
+// The eight instructions sit in ONE asm block (two predicate set-ups and two 64-bit adds per step with
+// immediate step sizes), so the issuing warp spends as few issue slots per MMA as possible.
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ void umma_tile_128(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, bool accumulate,
                                               uint32_t elect = 1u) {
     constexpr uint32_t idesc = umma_idesc(128, A_MN, B_MN);
     const uint64_t a0 = A_MN ? desc_mnmajor(a_tile, 0) : desc_kmajor(a_tile, 0);
     const uint64_t b0 = B_MN ? desc_mnmajor(b_tile, 0) : desc_kmajor(b_tile, 0);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-        constexpr uint32_t kPanel = kPanelBytes >> 4;
-        const uint32_t astep = A_MN ? ks * (2048u >> 4) : ((ks >> 2) * kPanel + (ks & 3) * 2u);
-        const uint32_t bstep = B_MN ? ks * (2048u >> 4) : ((ks >> 2) * kPanel + (ks & 3) * 2u);
-        umma_bf16(d_tmem, a0 + astep, b0 + bstep, idesc, (accumulate || ks > 0) ? 1u : 0u, elect);
-    }
+#define FMSA_UMMA_STEP(AI, BI)                                                  \
+    "add.s64 a, %1, " #AI ";\n"                                                 \
+    "add.s64 b, %2, " #BI ";\n"                                                 \
+    "@q tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n"
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q, t;\n"
+        ".reg .b64 a, b;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "setp.ne.b32 q, %5, 0;\n"
+        "setp.eq.b32 t, %5, %5;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        FMSA_UMMA_STEP(%6, %13) FMSA_UMMA_STEP(%7, %14) FMSA_UMMA_STEP(%8, %15) FMSA_UMMA_STEP(%9, %16)
+        FMSA_UMMA_STEP(%10, %17) FMSA_UMMA_STEP(%11, %18) FMSA_UMMA_STEP(%12, %19)
+        "}\n" ::"r"(d_tmem),
+        "l"(a0), "l"(b0), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(elect),
+        "n"(umma_kstep(A_MN, 1)), "n"(umma_kstep(A_MN, 2)), "n"(umma_kstep(A_MN, 3)), "n"(umma_kstep(A_MN, 4)),
+        "n"(umma_kstep(A_MN, 5)), "n"(umma_kstep(A_MN, 6)), "n"(umma_kstep(A_MN, 7)),
+        "n"(umma_kstep(B_MN, 1)), "n"(umma_kstep(B_MN, 2)), "n"(umma_kstep(B_MN, 3)), "n"(umma_kstep(B_MN, 4)),
+        "n"(umma_kstep(B_MN, 5)), "n"(umma_kstep(B_MN, 6)), "n"(umma_kstep(B_MN, 7))
+        : "memory");
+#undef FMSA_UMMA_STEP
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -212,6 +233,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -147,10 +147,27 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     };
 
     for (uint32_t draw = 0;; ++draw) {
-        // The drawing thread cannot get more than three sub-units ahead of the slowest role (its own
-        // group needs the other roles' results to finish a sub-unit), so a ring of four is enough.
+        // One thread draws the work and publishes it in a ring.  It passes over sub-units that lie
+        // beyond the end of their row, so every published entry has work (or is the end marker) and
+        // the drawing thread, whose own role needs the other roles' results to finish a sub-unit,
+        // cannot get more than three entries ahead of the slowest role: a ring of four is enough.
         if (tid == kFwdSoftmax) {
-            sm->unit_ring[draw & 3] = atomicAdd(P.counter, 1);
+            int64_t u;
+            for (;;) {
+                u = atomicAdd(P.counter, 1);
+                if (u >= P.n_subunits) break;
+                const SubUnit su = decode_subunit(u, P.NB, P.ppk);
+                int n;
+                if (P.dense) {
+                    n = P.S - su.j * kBlock;
+                } else {
+                    const int g = P.g_begin + su.g;
+                    const int64_t r = (static_cast<int64_t>(g / P.Hkv) * P.Hp + (g % P.Hkv) * P.ppk + su.pp) * P.NB + su.j;
+                    n = P.row_ptr[r + 1] - P.row_ptr[r];
+                }
+                if (su.chunk0 * kBlock < n) break;
+            }
+            sm->unit_ring[draw & 3] = static_cast<int32_t>(u < P.n_subunits ? u : P.n_subunits);
             mbar_arrive(smem_u32(&sm->unit_full[draw & 3]));
         }
         wait(smem_u32(&sm->unit_full[draw & 3]), (draw >> 2) & 1);
