@@ -35,7 +35,9 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
     const uint32_t tile_q = tiles, tile_k0 = tiles + kTileBytes;
     ScoreSmem* sm = reinterpret_cast<ScoreSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 3 * kTileBytes);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // The warp index goes through a shuffle so that the compiler knows it, and every branch on the warp's
+    // role, to be uniform across the warp: the issuer's descriptor arithmetic can then use the uniform datapath.
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const int qt = NB - 1 - static_cast<int>(blockIdx.x);   // longest tiles first
     const int bp = blockIdx.y;
     const int b = bp / Hp, p = bp % Hp, kph = p / pg;
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = sm->tmem_slot;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, sm->tmem_slot, 0);
     bool ok = true;
 
     if (warp == 0) {

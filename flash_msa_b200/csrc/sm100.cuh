@@ -73,8 +73,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: gives up after about two seconds of wall time and returns false.  Callers vote
 // on the result with a block-wide barrier so that the whole CTA leaves together.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The polling loop is kept out of line: the warp-specialised kernels have dozens of wait sites, and
+// their code has to stay small enough for the instruction cache (several roles run different code
+// at the same time, and a kernel much above 100 KB was measured to run several times slower).
+static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
@@ -84,6 +86,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         }
         if (global_timer_ns() - t0 > 2000000000ull) return false;
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_poll(bar, parity);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -233,12 +239,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

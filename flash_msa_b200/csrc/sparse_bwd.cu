@@ -92,7 +92,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     const uint32_t tile_p = tiles + 5 * kTileBytes, tile_ds = tiles + 6 * kTileBytes;
     BwdSmem* sm = reinterpret_cast<BwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 7 * kTileBytes);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // The warp index goes through a shuffle so that the compiler knows it, and every branch on the warp's
+    // role, to be uniform across the warp: the issuer's descriptor arithmetic can then use the uniform datapath.
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const bool worker = warp < 16;
     const bool issuer = (warp == 16);            // the whole warp runs the issue sequence ...
     const uint32_t elect = (lane == 0) ? 1u : 0u;   // ... and only this lane's instructions take effect
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = sm->tmem_slot;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, sm->tmem_slot, 0);
     const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 384;
 
     const int hpc = P.mpp + (P.with_kl ? 1 : 0);
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     for (;;) {
         if (tid == 0) sm->unit = atomicAdd(P.counter, 1);
         __syncthreads();
-        const int u = sm->unit;
+        const int u = __shfl_sync(0xffffffffu, sm->unit, 0);   // (uniform anyway; tells the compiler so)
         __syncthreads();
         if (u >= P.n_subunits) break;
         const SubUnit su = decode_subunit(u, P.NB, P.ppk);
