@@ -51,7 +51,7 @@ SCALE = 128 ** -0.5
 # DRAM bytes per launch of the dominant kernel (sparse backward at c2): dram__bytes_read.sum +
 # dram__bytes_write.sum of the ncu capture summarised in profiles/sparse_bwd_kernel_c2q.md (a quarter-size
 # case), scaled by 4 to the full launch.
-BWD_TRAFFIC_BYTES_C2 = 4 * (260.143104e6 + 614.321664e6)
+BWD_TRAFFIC_BYTES_C2 = 4 * (285.179904e6 + 618.938624e6)
 
 
 def measured_peaks():
