@@ -59,6 +59,34 @@ def _require_cuda(q):
         raise RuntimeError("flash_msa_b200 requires CUDA tensors (there is no CPU path)")
 
 
+# The reference returns a zero placeholder as kl_loss and users cannot watch the distillation loss
+# (flash_msa/msa_forward_cutedsl.py:69).  With COMPUTE_KL_VALUE = True every backward that receives a
+# gradient for kl_loss also computes the loss value inside the backward kernel (the teacher and the proxy
+# probabilities are in registers there anyway); ``last_kl_value()`` returns it.
+COMPUTE_KL_VALUE = False
+_last_kl_value = None
+
+
+def last_kl_value():
+    """0-dim fp32 CUDA tensor: the KL loss of the most recent backward that ran with
+    ``COMPUTE_KL_VALUE = True`` (mean over batch, proxy heads and rows of KL(teacher || proxy), the
+    value of the reference's eager model, flash_msa/tests/testing_model.py:158-167).  None before the
+    first such backward.  Reading it does not synchronise; ``.item()`` does."""
+    return _last_kl_value
+
+
+def _kl_buffer(grad_kl, device):
+    if COMPUTE_KL_VALUE and grad_kl is not None:
+        return torch.zeros(1, dtype=torch.float32, device=device)
+    return None
+
+
+def _publish_kl(buf):
+    global _last_kl_value
+    if buf is not None:
+        _last_kl_value = buf.reshape(())
+
+
 def _maybe_check(status, what):
     if DEBUG_CHECK_STATUS:
         ops.check_status(status, what)
@@ -80,6 +108,9 @@ class _SparseAttentionFunction(torch.autograd.Function):
         # (reference: flash_msa/msa_forward_cutedsl.py:69)
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
         ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy, rix.row_ptr, rix.col_q, rix.edge_pos)
+        # an output that does not feed the loss arrives as None in backward (not as zeros): no gradient for
+        # kl_loss then really skips the proxy work, as the reference intends (flash_msa/flash_msa.py:104-106)
+        ctx.set_materialize_grads(False)
         ctx.scale = float(scale)
         ctx.top_k_blocks = top_k_blocks
         ctx.block_indices = block_indices      # kept for inspection by tests (not a saved tensor)
@@ -93,8 +124,10 @@ class _SparseAttentionFunction(torch.autograd.Function):
             grad_out = torch.zeros_like(out)
         rix = ops.ReverseIndex(row_ptr, col_q, edge_pos, b, q_proxy.shape[1], s, ctx.top_k_blocks)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        klv = _kl_buffer(grad_kl, q.device)
         dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
-                                                      ctx.scale, rix, grad_kl, status=status)
+                                                      ctx.scale, rix, grad_kl, status=status, kl_value=klv)
+        _publish_kl(klv)
         _maybe_check(status, "flash_msa_func backward")
         return dqp, dkp, dq, dk, dv, None, None
 
@@ -112,6 +145,7 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
         _maybe_check(status, "flash_msa_warmup_func forward")
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
         ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy)
+        ctx.set_materialize_grads(False)
         ctx.scale = float(scale)
         return out, kl_loss
 
@@ -121,8 +155,10 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
         if grad_out is None:
             grad_out = torch.zeros_like(out)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        klv = _kl_buffer(grad_kl, q.device)
         dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
-                                                      ctx.scale, None, grad_kl, dense=True, status=status)
+                                                      ctx.scale, None, grad_kl, dense=True, status=status, kl_value=klv)
+        _publish_kl(klv)
         _maybe_check(status, "flash_msa_warmup_func backward")
         return dqp, dkp, dq, dk, dv, None, None
 

@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
 }  // namespace
 }  // namespace fmsa
 
-extern "C" int fmsa_abi_version(void) { return 1; }
+extern "C" int fmsa_abi_version(void) { return 2; }
 
 extern "C" int fmsa_umma_selftest(const void* a, const void* b, float* d, int a_mn, int b_mn, int use_tma, int* status,
                                   void* stream) {

@@ -385,6 +385,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float fast_log2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 // Packed fp32 pairs (sm_100 executes fma/add/mul on two floats per instruction) and 3-input max:
 // they halve the instruction count of the element-wise softmax / dS arithmetic, which is issue bound.
 __device__ __forceinline__ uint64_t f2_pack(float a, float b) {

@@ -50,6 +50,8 @@ struct BwdParams {
     int64_t n_subunits;
     int with_kl, dense;
     float scale, scale_log2e, kl_out_scale;   // kl_out_scale = scale / (B*Hp*S)
+    float* kl_value;    // optional: += KL(teacher || proxy) summed over this launch's rows, / (B*Hp*S)
+    float kl_value_scale;   // ln(2) / (B*Hp*S)
 };
 
 struct BwdSmem {
@@ -132,6 +134,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                                       : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
     uint32_t ph_kv = 0, ph_a = 0, ph_dq = 0, ph_dv = 0, ph_dk = 0;
     bool bad = false;   // a bounded wait gave up: later waits are skipped, the status word is set at the end
+    float kl_acc = 0.f;   // this thread's share of sum t * (log2 t - log2 p_proxy), when the KL value is asked for
 
     for (;;) {
         if (tid == 0) sm->unit = atomicAdd(P.counter, 1);
@@ -305,10 +308,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     uint32_t pk[8], dk[8];
 #pragma unroll
                     for (int i = 0; i < 16; i += 2) {
-                        float p0, p1;
-                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl2), p0, p1);
-                        p0 = fast_exp2(p0);
-                        p1 = fast_exp2(p1);
+                        float a0, a1;   // log2 of the probability
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl2), a0, a1);
+                        float p0 = fast_exp2(a0);
+                        float p1 = fast_exp2(a1);
                         if (masked) {
                             p0 = (c0 + c + i <= limit) ? p0 : 0.f;
                             p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
@@ -322,7 +325,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                             teacher[(c + i) >> 1] = __hadd2(teacher[(c + i) >> 1], __floats2half2_rn(p0, p1));
                         } else {
                             const float2 tt = __half22float2(teacher[(c + i) >> 1]);
-                            dk[i >> 1] = pack_bf16(p0 - tt.x * inv_mpp, p1 - tt.y * inv_mpp);
+                            const float t0 = tt.x * inv_mpp, t1 = tt.y * inv_mpp;
+                            dk[i >> 1] = pack_bf16(p0 - t0, p1 - t1);
+                            if (P.kl_value) {   // KL(teacher || proxy) = sum t (ln t - ln p); t = 0 contributes nothing
+                                kl_acc += (t0 > 0.f) ? t0 * (fast_log2(t0) - a0) : 0.f;
+                                kl_acc += (t1 > 0.f) ? t1 * (fast_log2(t1) - a1) : 0.f;
+                            }
                             teacher[(c + i) >> 1] = __floats2half2_rn(0.f, 0.f);
                         }
                     }
@@ -464,6 +472,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     }
     cp_async_wait<0>();
     if (tid == 0) tma_store_wait_all();
+    if (P.kl_value && worker) {
+        for (int o = 16; o > 0; o >>= 1) kl_acc += __shfl_xor_sync(0xffffffffu, kl_acc, o);
+        if (lane == 0) atomicAdd(P.kl_value, kl_acc * P.kl_value_scale);
+    }
     if (bad) atomicMax(P.status, kStatusWaitTimeout);
     tc_fence_before_sync();
     __syncthreads();
@@ -696,7 +708,7 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
                                const float* lse, const float* lse_proxy, const float* delta, const int32_t* row_ptr,
                                const int32_t* col_q, void* dq_part, void* dqp_part, int64_t part_slots, float* dkp_acc,
                                float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
-                               int32_t dense, int32_t* counter, int32_t* status, void* stream) {
+                               int32_t dense, float* kl_value, int32_t* counter, int32_t* status, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(problem_ok(pb));
     FMSA_REQUIRE(q && k && v && d_out && q->ptr && k->ptr && v->ptr && d_out->ptr);
@@ -749,6 +761,8 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.with_kl = with_kl ? 1 : 0; P.dense = dense ? 1 : 0;
     P.scale = pb->scale; P.scale_log2e = pb->scale * kLog2e;
     P.kl_out_scale = pb->scale / (static_cast<float>(pb->B) * pb->Hp * pb->S);
+    P.kl_value = with_kl ? kl_value : nullptr;
+    P.kl_value_scale = kLn2 / (static_cast<float>(pb->B) * pb->Hp * pb->S);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int dev = 0, sms = 0;

@@ -264,10 +264,13 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
 
 
 def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy, scale, rix, grad_kl, *, dense=False,
-                       status=None):
+                       status=None, kl_value=None):
     """Fused backward.  ``out`` is the [B,S,Hq*D] forward output, ``grad_out`` its upstream gradient,
     ``grad_kl`` the upstream gradient of kl_loss (0-dim tensor) or None.  Returns
-    (dq_proxy, dk_proxy, dq, dk, dv) in the input dtype, shaped like the inputs."""
+    (dq_proxy, dk_proxy, dq, dk, dv) in the input dtype, shaped like the inputs.
+    ``kl_value``: optional zeroed fp32 tensor of one element; the kernel adds the value of the KL loss
+    (what the reference's eager model returns, flash_msa/tests/testing_model.py:158-167) to it.  Only
+    with ``grad_kl`` given: without it the proxy work is skipped altogether."""
     _require_cuda(q, k, v, grad_out)
     lib = _lib.load()
     q, k, v = (_as_kernel_input(t.detach()) for t in (q, k, v))
@@ -319,7 +322,8 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
                 ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
                 _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(), row_ptr, col_q,
                 dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, dkp_acc.data_ptr() if with_kl else 0,
-                dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), g0, gc, int(with_kl), int(dense), counter.data_ptr(),
+                dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), g0, gc, int(with_kl), int(dense),
+                kl_value.data_ptr() if (with_kl and kl_value is not None) else 0, counter.data_ptr(),
                 status.data_ptr(), st), dev)
         with _Timed("bwd_combine", dev):
             _launch("fmsa_sparse_bwd_combine", 1, lib.fmsa_sparse_bwd_combine(

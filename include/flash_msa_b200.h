@@ -156,14 +156,20 @@ int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int3
  *              accumulated with atomics (long reverse-index rows are split over several CTAs),
  *              unscaled; cast to the activation dtype with fmsa_cast_scaled (which applies the factors).
  * with_kl = 0 skips the proxy work (the reference does the same when no gradient reaches kl_loss,
- * flash_msa/flash_msa.py:104-106) and ignores q_proxy, k_proxy, lse_proxy, dqp_part, dkp_acc.
+ * flash_msa/flash_msa.py:104-106) and ignores q_proxy, k_proxy, lse_proxy, dqp_part, dkp_acc, kl_value.
+ * kl_value: NULL, or fp32[1] that the kernel ADDS this launch's share of the KL loss value to:
+ *              sum over the launch's (batch, proxy head, row) of KL(teacher || proxy distribution), divided by
+ *              B*Hp*S -- the number the reference's eager model returns as kl_loss
+ *              (flash_msa/tests/testing_model.py:158-167).  The reference kernels return a zero placeholder
+ *              (flash_msa/msa_forward_cutedsl.py:69); this output has no counterpart there.  The caller zeroes
+ *              it before the first pass.
  * counter: int32[1] scratch;  status: int32[1]. */
 int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
                     const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out, const float* lse,
                     const float* lse_proxy, const float* delta, const int32_t* row_ptr, const int32_t* col_q,
                     void* dq_part, void* dqp_part, int64_t part_slots, float* dkp_acc, float* dk_acc, float* dv_acc,
-                    int32_t g_begin, int32_t g_count, int32_t with_kl, int32_t dense, int32_t* counter,
-                    int32_t* status, void* stream);
+                    int32_t g_begin, int32_t g_count, int32_t with_kl, int32_t dense, float* kl_value,
+                    int32_t* counter, int32_t* status, void* stream);
 
 /* Sums the per-edge contributions of every query row:
  *   dq bf16 [B,Hq,S,128];  dq_proxy bf16 [B,Hp,S,128] (or NULL), multiplied by *grad_kl (device

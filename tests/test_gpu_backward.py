@@ -102,3 +102,29 @@ def test_grad_out_none_and_error_behaviour(fm):
         fm.flash_msa_func(qp.float(), kp.float(), q.float(), k.float(), v.float(), 256, SCALE)
     with pytest.raises(RuntimeError):
         fm.flash_msa_warmup_func(qp.cpu(), kp.cpu(), q.cpu(), k.cpu(), v.cpu(), 256, SCALE)
+
+
+@pytest.mark.parametrize("name", ["tiny", "c1", "mpp6", "pg2"])
+def test_kl_value(fm, name):
+    """Optional KL loss value computed inside the backward kernel, against the oracle's value on the same
+    selection (tolerance 2 % + 1e-4: teacher and probabilities come from bf16 operands and fp16 sums)."""
+    from flash_msa_b200 import api
+    cfg = CFGS[name]
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    api.COMPUTE_KL_VALUE = True
+    try:
+        _, _, node = _run_kernel(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, 1.0)
+        got = fm.last_kl_value()
+        assert got is not None and got.shape == () and got.dtype == torch.float32
+        ref = O.sparse_forward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, block_indices=node.block_indices)["kl"]
+        assert abs(got.item() - ref.item()) <= 2e-2 * abs(ref.item()) + 1e-4, (got.item(), ref.item())
+        _run_kernel(fm.flash_msa_warmup_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, 1.0)
+        got_w = fm.last_kl_value()
+        ref_w = O.warmup_forward(qp, kp, q, k, v, SCALE)["kl"]
+        assert abs(got_w.item() - ref_w.item()) <= 2e-2 * abs(ref_w.item()) + 1e-4, (got_w.item(), ref_w.item())
+        # without a gradient for kl_loss the proxy work is skipped and nothing new is published
+        before = fm.last_kl_value()
+        _run_kernel(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, None)
+        assert fm.last_kl_value() is before
+    finally:
+        api.COMPUTE_KL_VALUE = False
