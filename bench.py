@@ -325,29 +325,26 @@ def main():
     # ---- end to end: host buffers, copies inside the timed region ----
     e2e = None
     if not args.no_e2e:
-        out_h = None
-        grads_h = None
+        # the repo's host-buffer call: pinned host tensors in, pinned host tensors out, copies and kernels
+        # pipelined over (batch, KV-group) chunks on three streams (flash_msa_b200/host.py)
+        from flash_msa_b200.host import HostStep
+        hs = HostStep(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], top_k, SCALE,
+                      dense=cfg["dense"], device=dev)
 
         def e2e_step():
-            nonlocal out_h, grads_h
-            ins = [t.to(dev, non_blocking=True) for t in host]
-            leaves = [t.requires_grad_(True) for t in ins[:5]]
-            out, kl = fn(*leaves, top_k, SCALE)
-            torch.autograd.backward([out, kl], [ins[5], ones])
-            res = [out] + [t.grad for t in leaves]
-            if out_h is None:
-                out_h = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
-            for h, r in zip(out_h, res):
-                h.copy_(r, non_blocking=True)
-            return res
+            return hs.run(*host, grad_kl=1.0)
 
         e2e_step()
+        hs.synchronize()
         sync_all()
         s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         n_e2e = max(2, min(args.steps, 5))
         s2.record()
         for _ in range(n_e2e):
             e2e_step()
+        # the step ends when the last result has reached host memory
+        torch.cuda.current_stream().wait_stream(hs.s_out)
+        torch.cuda.current_stream().wait_stream(hs.s_cmp)
         e2.record()
         sync_all()
         e2e_ms = s2.elapsed_time(e2)
@@ -355,8 +352,7 @@ def main():
             t = torch.tensor([e2e_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
-        h2d = sum(t.numel() * t.element_size() for t in host)
-        d2h = sum(t.numel() * t.element_size() for t in out_h)
+        h2d, d2h = hs.bytes_per_step()
         total_f = flops(cfg) * (world if scaling == "weak" else 1)
         e2e = {"value": total_f * n_e2e / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e}

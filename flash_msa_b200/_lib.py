@@ -81,6 +81,8 @@ def _declare(lib):
     lib.fmsa_sparse_bwd_combine.argtypes = [PB, P, P, P, P, P, P, P, c_int32, c_int32, c_int32, P]
     lib.fmsa_cast_scaled.restype = c_int
     lib.fmsa_cast_scaled.argtypes = [P, P, c_int64, P, c_float, P]
+    lib.fmsa_copy2d_async.restype = c_int
+    lib.fmsa_copy2d_async.argtypes = [P, ctypes.c_size_t, P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, P]
 
 
 class FmsaProblem(ctypes.Structure):

@@ -187,6 +187,14 @@ int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const v
  * needs scale/(B*Hp*S) times the upstream kl gradient. */
 int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale, void* stream);
 
+/* Asynchronous strided copy between pinned host memory and the device (either direction; inferred
+ * from the pointers): `rows` pieces of `width` bytes, source pieces `src_pitch` bytes apart, destination
+ * pieces `dst_pitch` bytes apart.  No counterpart in the reference, whose API takes device tensors only:
+ * it serves the host-buffer pipeline (flash_msa_b200/host.py), which moves one (batch, head range)
+ * chunk of a [B,S,H*128] host tensor at a time while the previous chunk computes. */
+int fmsa_copy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width, size_t rows,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,3 +84,30 @@ def test_config2_full_size_properties(fm):
     # rows see at most the first q+1 keys: the output of row 0 is V[0] exactly
     v0 = v[:, :, 0].float().repeat_interleave(cfg["hq"] // cfg["hkv"], dim=1).reshape(cfg["b"], -1)
     assert max_err(out1[:, 0].float(), v0) <= 1e-2
+
+
+def test_host_step_matches_device_call():
+    """The pipelined host-buffer step (pinned tensors in and out, chunks of (batch, KV group) units on
+    three streams) gives the results of one direct call on device tensors: `out` bit for bit (selection
+    and forward do not depend on the chunking), gradients to bf16 rounding (dK/dV/dKp accumulate with
+    atomics; the KL factor is applied as weight * 1/rows_of_chunk instead of 1/rows)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import flash_msa_b200
+    from flash_msa_b200.host import HostStep
+    from oracle.msa_oracle import make_inputs
+    b, s, hq, hkv, hp, hpkv, kb = 2, 1024, 8, 4, 4, 4, 3
+    host = [t.pin_memory() for t in make_inputs(b, s, hq, hkv, hp, hpkv, seed=5, dtype=torch.bfloat16)]
+    hs = HostStep(b, s, hq, hkv, hp, hpkv, kb * 128, 128 ** -0.5, chunks=4)
+    assert len(hs.chunks) == 4
+    for _ in range(2):                       # the second run reuses the device buffers of the first
+        res = hs.run(*host, grad_kl=0.5)
+        hs.synchronize()
+    dev = [t.cuda() for t in host]
+    leaves = [t.detach().requires_grad_(True) for t in dev[:5]]
+    out, kl = flash_msa_b200.flash_msa_func(*leaves, kb * 128, 128 ** -0.5)
+    torch.autograd.backward([out, kl], [dev[5], torch.full((), 0.5, device="cuda")])
+    assert torch.equal(res[0].cuda(), out)
+    for name, got, ref in zip(["dq_proxy", "dk_proxy", "dq", "dk", "dv"], res[1:], [t.grad for t in leaves]):
+        err = (got.cuda().float() - ref.float()).abs().max().item()
+        assert err <= 2 ** -7 * ref.float().abs().max().item() + 1e-6, (name, err)
