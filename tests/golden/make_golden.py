@@ -25,7 +25,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.environ.get("REFERENCE_ROOT", "/root/reference"))
+if "REFERENCE_ROOT" not in os.environ:
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference project (the directory that holds flash_msa/)")
+sys.path.insert(0, os.environ["REFERENCE_ROOT"])
 
 from flash_msa.tests.testing_model import Model                    # noqa: E402
 from flash_msa.tests.testing_model_warmup import WarmupModel       # noqa: E402
