@@ -35,19 +35,74 @@ __global__ void __launch_bounds__(256) topk_rows_kernel(const float* __restrict_
         lv[k] = -INFINITY;
         li[k] = NB;
     }
-    if (lane == 0) {   // forced local block
-        lv[0] = INFINITY;
-        li[0] = local;
-    }
     const int kt = (Kb - 1) >> 5, lt = (Kb - 1) & 31;   // position of the Kb-th entry
     float tv = -INFINITY;
     int ti = NB;
-    if (Kb == 1) {
-        tv = INFINITY;
-        ti = local;
-    }
 
-    for (int base = 0; base < nvalid; base += 32) {
+    // sorted insertion of (cv, ci) with shift; the last entry of the list falls out
+    auto insert = [&](float cv, int ci) {
+        float inv = cv;
+        int ini = ci;
+        bool placed = false;
+#pragma unroll
+        for (int k = 0; k < KPL; ++k) {
+            const unsigned bm = placed ? 0xffffffffu : __ballot_sync(0xffffffffu, beats(cv, ci, lv[k], li[k]));
+            if (bm != 0) {
+                const int first = __ffs(bm) - 1;
+                const float outv = __shfl_sync(0xffffffffu, lv[k], 31);
+                const int outi = __shfl_sync(0xffffffffu, li[k], 31);
+                const float upv = __shfl_up_sync(0xffffffffu, lv[k], 1);
+                const int upi = __shfl_up_sync(0xffffffffu, li[k], 1);
+                if (lane > first) {
+                    lv[k] = upv;
+                    li[k] = upi;
+                } else if (lane == first) {
+                    lv[k] = inv;
+                    li[k] = ini;
+                }
+                inv = outv;
+                ini = outi;
+                placed = true;
+            }
+        }
+        tv = __shfl_sync(0xffffffffu, lv[kt], lt);
+        ti = __shfl_sync(0xffffffffu, li[kt], lt);
+    };
+
+    int base = 0;
+    if (KPL == 1) {
+        // The first 32 candidates would nearly all be inserted one by one (the list is still empty):
+        // sort them with a bitonic network instead (15 compare-exchange steps).  Same total order, so
+        // the list is the one the insertions would have built.
+        const int j = lane;
+        const bool have = (j < nvalid) && (j != local);
+        const float s = have ? srow[j] : -INFINITY;
+        const bool ok = have && s > -INFINITY;   // a score of -inf (or NaN) never enters the list
+        float v = ok ? s : -INFINITY;
+        int id = ok ? j : NB;
+#pragma unroll
+        for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+            for (int jj = k >> 1; jj > 0; jj >>= 1) {
+                const float pv = __shfl_xor_sync(0xffffffffu, v, jj);
+                const int pi = __shfl_xor_sync(0xffffffffu, id, jj);
+                // descending overall: inside a block of k lanes whose bit k is clear the better entry goes
+                // to the lower lane, in the other blocks to the upper lane (k = 32: one block, bit clear)
+                const bool want_better = ((lane & jj) == 0) == ((lane & k) == 0);
+                const bool partner_better = beats(pv, pi, v, id);
+                if (partner_better == want_better && (pv != v || pi != id)) {
+                    v = pv;
+                    id = pi;
+                }
+            }
+        }
+        lv[0] = v;
+        li[0] = id;
+        base = 32;
+    }
+    insert(INFINITY, local);   // the row's own block is forced first
+
+    for (; base < nvalid; base += 32) {
         const int j = base + lane;
         const bool have = (j < nvalid) && (j != local);
         const float s = have ? srow[j] : -INFINITY;
@@ -59,33 +114,7 @@ __global__ void __launch_bounds__(256) topk_rows_kernel(const float* __restrict_
             const float cv = __shfl_sync(0xffffffffu, s, src);
             const int ci = base + src;
             if (!beats(cv, ci, tv, ti)) continue;
-            // sorted insertion with shift
-            float inv = cv;
-            int ini = ci;
-            bool placed = false;
-#pragma unroll
-            for (int k = 0; k < KPL; ++k) {
-                const unsigned bm = placed ? 0xffffffffu : __ballot_sync(0xffffffffu, beats(cv, ci, lv[k], li[k]));
-                if (bm != 0) {
-                    const int first = __ffs(bm) - 1;
-                    const float outv = __shfl_sync(0xffffffffu, lv[k], 31);
-                    const int outi = __shfl_sync(0xffffffffu, li[k], 31);
-                    const float upv = __shfl_up_sync(0xffffffffu, lv[k], 1);
-                    const int upi = __shfl_up_sync(0xffffffffu, li[k], 1);
-                    if (lane > first) {
-                        lv[k] = upv;
-                        li[k] = upi;
-                    } else if (lane == first) {
-                        lv[k] = inv;
-                        li[k] = ini;
-                    }
-                    inv = outv;
-                    ini = outi;
-                    placed = true;
-                }
-            }
-            tv = __shfl_sync(0xffffffffu, lv[kt], lt);
-            ti = __shfl_sync(0xffffffffu, li[kt], lt);
+            insert(cv, ci);
         }
     }
     int32_t* orow = out + row * Kb;
