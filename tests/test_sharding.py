@@ -94,3 +94,27 @@ def test_two_rank_shards_reproduce_the_full_problem(tmp_path, cfg):
     result = tmp_path / "result.txt"
     mp.spawn(_worker, args=(2, _free_port(), cfg, str(result)), nprocs=2, join=True)
     assert result.read_text() == "ok"
+
+
+def test_host_pipeline_chunks_cover_the_grid():
+    """Chunking of the host-buffer pipeline: every (batch, KV head) unit in exactly one rectangular chunk;
+    a proxy-K head is never needed by two chunks (its gradient would have to be summed across them)."""
+    from flash_msa_b200.host import _chunks
+    from flash_msa_b200.sharding import head_ranges
+    for b, hq, hkv, hp, hpkv, want in [(2, 32, 8, 8, 8, 4), (1, 64, 8, 16, 8, 4), (2, 16, 2, 4, 1, 4), (1, 8, 2, 2, 2, 8),
+                                        (3, 12, 2, 2, 1, 4), (8, 48, 4, 8, 4, 16)]:
+        chunks = _chunks(b, hq, hkv, hp, hpkv, want)
+        seen = set()
+        owners = {}
+        for ci, c in enumerate(chunks):
+            (h0, h1), (kv0, kv1), (p0, p1), (kp0, kp1) = head_ranges(c, hq, hkv, hp, hpkv)
+            assert h1 - h0 == (kv1 - kv0) * (hq // hkv) and p1 - p0 == (kv1 - kv0) * (hp // hkv)
+            for bb in range(c.b0, c.b1):
+                for kv in range(c.kv0, c.kv1):
+                    assert (bb, kv) not in seen
+                    seen.add((bb, kv))
+                for kp in range(kp0, kp1):
+                    owners.setdefault((bb, kp), set()).add(ci)
+        assert len(seen) == b * hkv
+        assert all(len(v) == 1 for v in owners.values())
+        assert 1 <= len(chunks) <= want
