@@ -375,6 +375,63 @@ def eager_forward_backward(fn, tensors, d_out, grad_kl: Optional[float] = 1.0):
     return out.detach(), kl.detach(), grads
 
 
+# --------------------------------------------------------------------------------------------
+# one query position at a time (parity at sequence lengths where the full eager model does not fit)
+# --------------------------------------------------------------------------------------------
+def row_reference(q_proxy, k_proxy, q, k, v, d_out, scale, b, p, qpos, block_row, grad_kl=1.0,
+                  rounded=False):
+    """Forward and the row-local gradients of ONE query position (batch b, proxy head p, position
+    qpos) whose selected key blocks are ``block_row`` (int tensor [Kb]; the sentinel NB marks unused
+    slots).  Same formulas as ``_run`` (testing_model.py:77-167 restricted to one row), fp32.
+    Everything that depends on this row only is returned: out [mpp,D], lse [mpp], lse_proxy, kl (the
+    row's KL term), dq [mpp,D], dq_proxy [D] (dK, dV, dKp are sums over rows and are not row-local),
+    and the row's causally visible proxy block scores [qpos//128+1].
+    ``rounded=True`` rounds P, dS, dSp and the outputs to bf16 at the points where the reference kernels
+    do (flash_msa/msa_backward_cutedsl.py:502-510, 675-679): the error yardstick."""
+    bsz, hq, s, d = q.shape
+    hkv, hp, hpkv = k.shape[1], q_proxy.shape[1], k_proxy.shape[1]
+    mpp, grp, pg = hq // hp, hq // hkv, hp // hpkv
+    nb = s // BLOCK
+    f32 = torch.float32
+    rnd = (lambda t: t.to(torch.bfloat16).to(f32)) if rounded else (lambda t: t)
+    blocks = [int(x) for x in block_row.tolist() if 0 <= int(x) < nb]
+    tok = torch.cat([torch.arange(j * BLOCK, min((j + 1) * BLOCK, qpos + 1), device=q.device) for j in sorted(blocks)])
+    kph = p // pg
+    kp_sel = k_proxy[b, kph, tok].to(f32)
+    sp = (kp_sel @ q_proxy[b, p, qpos].to(f32)) * scale
+    lse_p = torch.logsumexp(sp, 0)
+    p_px = torch.exp(sp - lse_p)
+    outs, lses, dqs, probs = [], [], [], []
+    for i in range(mpp):
+        h = p * mpp + i
+        kvh = h // grp
+        k_sel, v_sel = k[b, kvh, tok].to(f32), v[b, kvh, tok].to(f32)
+        sc = (k_sel @ q[b, h, qpos].to(f32)) * scale
+        lse = torch.logsumexp(sc, 0)
+        pr = torch.exp(sc - lse)
+        o = rnd(pr) @ v_sel
+        do = d_out[b, qpos, h * d:(h + 1) * d].to(f32)
+        dp = v_sel @ do
+        delta = (rnd(o) * do).sum()
+        ds = rnd(pr * (dp - delta))
+        outs.append(rnd(o))
+        lses.append(lse)
+        dqs.append(rnd((ds @ k_sel) * scale))
+        probs.append(pr)
+    teacher = torch.stack(probs).mean(0)
+    kl_row = torch.where(teacher > 0, teacher * (torch.log(teacher.clamp_min(1e-45)) - (sp - lse_p)), torch.zeros_like(teacher)).sum()
+    gk = 0.0 if grad_kl is None else float(grad_kl)
+    dsp = rnd(p_px - teacher) * (gk / float(bsz * hp * s))
+    dqp = rnd((dsp @ kp_sel) * scale)
+    allk = k_proxy[b, kph, : qpos + 1].to(f32)
+    full = (allk @ q_proxy[b, p, qpos].to(f32)) * scale
+    nvis = qpos // BLOCK + 1
+    pad = nvis * BLOCK - full.numel()
+    blk = torch.cat([full, full.new_full((pad,), float("-inf"))]).view(nvis, BLOCK).amax(-1)
+    return {"out": torch.stack(outs), "lse": torch.stack(lses), "lse_proxy": lse_p, "kl": kl_row, "dq": torch.stack(dqs),
+            "dq_proxy": dqp, "block_scores": blk}
+
+
 # ----------------------------------------------------------------------------
 # synthetic workloads (shapes and value distributions of the benchmark configs)
 # ----------------------------------------------------------------------------

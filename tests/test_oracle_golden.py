@@ -124,3 +124,25 @@ def test_reverse_index_is_canonical():
 def test_flop_count_config2():
     assert O.pairs_selected(8192, 16) == 14290944
     assert abs(O.flops_sparse_fwd_bwd(2, 8192, 32, 16) - 1.639e12) < 1e9
+
+
+def test_row_reference_matches_full_oracle():
+    """The one-row restatement (used for parity at sequence lengths where the full eager model does not
+    fit) agrees with the full closed-form oracle, which is pinned against the reference above."""
+    b, s, hq, hkv, hp, hpkv, kb = 2, 512, 8, 2, 4, 2, 2
+    qp, kp, q, k, v, do = O.make_inputs(b, s, hq, hkv, hp, hpkv, seed=3)
+    r = O.sparse_forward_backward(qp, kp, q, k, v, kb * 128, 128 ** -0.5, do, 0.7)
+    idx, mpp = r["block_indices"], hq // hp
+    kl_rows = 0.0
+    for bb, p, qpos in [(0, 0, 0), (1, 3, 200), (0, 2, 511), (1, 1, 128)]:
+        rr = O.row_reference(qp, kp, q, k, v, do, 128 ** -0.5, bb, p, qpos, idx[bb, p, qpos], 0.7)
+        heads = slice(p * mpp, (p + 1) * mpp)
+        assert (r["out"][bb, qpos].view(hq, 128)[heads] - rr["out"]).abs().max() < 2e-6
+        assert (r["lse"][bb, heads, qpos] - rr["lse"]).abs().max() < 2e-6
+        assert (r["lse_proxy"][bb, p, qpos] - rr["lse_proxy"]).abs() < 2e-6
+        assert (r["dq"][bb, heads, qpos] - rr["dq"]).abs().max() < 2e-6
+        assert (r["dq_proxy"][bb, p, qpos] - rr["dq_proxy"]).abs().max() < 1e-6 * r["dq_proxy"].abs().max()
+        sc = O.proxy_block_scores(qp, kp, 128 ** -0.5)[bb, p, qpos, : qpos // 128 + 1]
+        assert (sc - rr["block_scores"]).abs().max() < 2e-6
+        kl_rows += rr["kl"].item()
+    assert kl_rows > 0.0
