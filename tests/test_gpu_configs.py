@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import msa_oracle as O
-from tests.gpu_util import SCALE, bf16_inputs, max_err, yardstick_check
+from tests.gpu_util import SCALE, bf16_inputs, max_err, yardstick_check, yardstick_ratio
 
 pytestmark = pytest.mark.gpu
 NAMES = ["dq_proxy", "dk_proxy", "dq", "dk", "dv"]
@@ -86,21 +86,32 @@ def test_config2_full_size_properties(fm):
     assert max_err(out1[:, 0].float(), v0) <= 1e-2
 
 
-def test_long_context_sampled_rows(fm):
-    """Config 5's sequence length (S = 65536, top-k = 32 blocks) on one of its KV groups: reverse-index
-    rows of > 100 chunks, sub-unit splitting and the work ring at full length.  The eager model needs
-    17 GB per head there, so parity is checked on sampled query positions with the one-row oracle:
-    selection (stable top-k of independently computed scores, flips only at near-ties), out, lse,
-    lse_proxy, dQ, dQp against fp32 with the bf16-rounded restatement as the yardstick."""
-    cfg = dict(b=1, s=65536, hq=8, hkv=1, hp=2, hpkv=1, kb=32, seed=11)
-    qp, kp, q, k, v, do = bf16_inputs(cfg)
+LONG = {
+    # one KV group of config 5 (B=1 S=65536 Hq=64 Hkv=8 Hp=16 Hpkv=8, top-k 32 blocks)
+    "c5_group": (dict(b=1, s=65536, hq=8, hkv=1, hp=2, hpkv=1, kb=32, seed=11), False),
+    # one KV group of config 4 (S=32768 Hq=48 Hkv=4 Hp=8 Hpkv=4, top-k 64 blocks: six main heads per proxy
+    # head, two proxy heads per proxy-K head) with its skewed key distribution (sink blocks)
+    "c4_group": (dict(b=1, s=32768, hq=12, hkv=1, hp=2, hpkv=1, kb=64, seed=12), True),
+}
+
+
+@pytest.mark.parametrize("name", list(LONG))
+def test_long_context_sampled_rows(fm, name):
+    """The sequence lengths of configs 5 and 4 on one of their KV groups: reverse-index rows of > 100
+    chunks, sub-unit splitting and the work ring at full length.  The eager model needs 17 GB per head at
+    S = 65536, so parity is checked on sampled query positions with the one-row oracle: selection (stable
+    top-k of independently computed scores, flips only at near-ties), out, dQ, dQp against fp32 with the
+    bf16-rounded restatement as the yardstick."""
+    cfg, skew = LONG[name]
+    qp, kp, q, k, v, do = bf16_inputs(cfg, skew=skew)
     out, grads, node = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, grad_kl=1.0)
     idx = node.block_indices
     nb, mpp = cfg["s"] // 128, cfg["hq"] // cfg["hp"]
     dqp, dq = grads[0], grads[2]
     flips = near = 0
+    worst = {"out": 0.0, "dq": 0.0, "dq_proxy": 0.0}
     for p in range(cfg["hp"]):
-        for qpos in (0, 127, 128, 4321, 33000, 65535):
+        for qpos in (0, 127, 128, 4321, cfg["s"] // 2 + 232, cfg["s"] - 1):
             row = idx[0, p, qpos]
             r32 = O.row_reference(qp, kp, q, k, v, do, SCALE, 0, p, qpos, row, 1.0)
             r16 = O.row_reference(qp, kp, q, k, v, do, SCALE, 0, p, qpos, row, 1.0, rounded=True)
@@ -118,10 +129,16 @@ def test_long_context_sampled_rows(fm):
             assert int(row[0]) == qpos // 128
             heads = slice(p * mpp, (p + 1) * mpp)
             o = out[0, qpos].view(cfg["hq"], 128)[heads]
+            worst["out"] = max(worst["out"], yardstick_ratio(o, r32["out"], r16["out"]))
             yardstick_check("out", o, r32["out"], r16["out"], 2e-3 * r32["out"].abs().max().item())
-            yardstick_check("dq", dq[0, heads, qpos], r32["dq"], r16["dq"], 2e-3 * r32["dq"].abs().max().item() + 1e-6)
+            # dQ and dQp are sums of per-edge contributions that the kernel rounds to bf16 one by one (up to Kb
+            # of them per row); the floor is one bf16 ulp of the row's largest element
+            worst["dq"] = max(worst["dq"], yardstick_ratio(dq[0, heads, qpos], r32["dq"], r16["dq"]))
+            worst["dq_proxy"] = max(worst["dq_proxy"], yardstick_ratio(dqp[0, p, qpos], r32["dq_proxy"], r16["dq_proxy"]))
+            yardstick_check("dq", dq[0, heads, qpos], r32["dq"], r16["dq"], 2 ** -8 * r32["dq"].abs().max().item() + 1e-6)
             yardstick_check("dq_proxy", dqp[0, p, qpos], r32["dq_proxy"], r16["dq_proxy"],
-                            2e-3 * r32["dq_proxy"].abs().max().item() + 1e-9)
+                            2 ** -8 * r32["dq_proxy"].abs().max().item() + 1e-9)
+    print(f"long-context {name}: selection flips {flips} (near-ties {near}); worst kernel/yardstick error ratio {worst}")
     assert flips <= near, (flips, near)
 
 
