@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             mbar_init(smem_u32(&sm->s_full[i]), 1);
             mbar_init(smem_u32(&sm->s_empty[i]), kFwdSoftmax / 32);
             mbar_init(smem_u32(&sm->o_full[i]), 1);
-            mbar_init(smem_u32(&sm->o_empty[i]), kFwdStore / 32);
+            mbar_init(smem_u32(&sm->o_empty[i]), (kFwdStore + kFwdSoftmax) / 32);   // both groups read O
         }
         for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sm->unit_full[i]), 1);
         fence_mbar_init();
@@ -243,8 +243,27 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             // =========================== softmax group ===========================
             const int cg = warp >> 2, c0 = cg * 32;
             int hh = 0, chunk = chunk0;
-            bool prev_main = false;
+            // The finished O^T of a main tile is written out by BOTH groups: the softmax warps take tile rows
+            // 0..63 (16 rows per warp, in the time they would otherwise wait for the next S), the store warps
+            // rows 64..127.  TMEM lane = head-dimension index, column = tile row: the 32 lanes of a warp store
+            // 64 contiguous bytes of ONE partial row per instruction.
+            bool pending = false;        // O^T of main tile prev_mt has not been written out by this warp yet
             uint32_t prev_mt = 0;
+            int prev_head = 0, prev_nrows = 0;
+            int64_t prev_slot0 = 0;
+            auto store_share = [&]() {
+                wait(B2(sm->o_full, prev_mt), (prev_mt >> 1) & 1);   // P*V of that tile has finished (and has read P)
+                tc_fence_after_sync();
+                uint32_t v[16];
+                tmem_ld16(tmem_addr(tmem_o0 + (prev_mt & 1) * 128, quarter, 16 * cg), v);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                warp_arrive(B2(sm->o_empty, prev_mt));
+                const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
+                store_transposed_bf16_16(P.o_part + ((prev_slot0 + 16 * cg) * P.mpp + prev_head) * kHeadDim + row, rstride, v,
+                                         16 * cg, prev_nrows);
+                pending = false;
+            };
             for (int t = 0; t < ntiles; ++t, ++gt) {
                 const bool is_proxy = hh == P.mpp;
                 const int sb = gt & 1;
@@ -276,7 +295,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 named_barrier_sync(1 + quarter, 128);   // the four warps that share these 32 rows
                 const float m = fmaxf(fmaxf(sm->rmax[0][row], sm->rmax[1][row]), fmaxf(sm->rmax[2][row], sm->rmax[3][row])) *
                                 P.scale_log2e;
-                if (!is_proxy && prev_main) wait(B2(sm->o_full, prev_mt), (prev_mt >> 1) & 1);   // P*V of the previous tile has read P
+                if (pending) store_share();   // (also: P*V of the previous main tile has read P)
                 uint64_t l2 = f2_pack(0.f, 0.f);
                 const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e), nm2 = f2_pack(-m, -m);
 #pragma unroll
@@ -313,8 +332,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 if (!is_proxy) {
                     fence_async_smem();
                     warp_arrive(p_full);
-                    prev_main = true;
+                    pending = true;
                     prev_mt = mt;
+                    prev_head = hh;
+                    prev_nrows = nrows;
+                    prev_slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
                     ++mt;
                 }
                 sm->lsum[cg][row] = l;
@@ -329,10 +351,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     ++chunk;
                 }
             }
+            if (pending) store_share();
         } else {
             // =========================== store group ===========================
             const int etid = tid - kFwdSoftmax;
-            const int c0 = ((warp - 16) >> 2) * 64;   // this thread's 64 tile rows of the transposed accumulator
+            const int c0 = 64 + ((warp - 16) >> 2) * 32;   // this thread's 32 tile rows of the transposed accumulator (rows 0..63: softmax warps)
             const GatherLane glane = make_gather_lane(etid);
             const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
             const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
@@ -373,7 +396,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 __nv_bfloat16* dst = P.o_part + ((m.slot0 + c0) * P.mpp + m.head) * kHeadDim + row;
                 const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
 #pragma unroll
-                for (int c = 0; c < 64; c += 16) {
+                for (int c = 0; c < 32; c += 16) {
                     uint32_t v[16];
                     tmem_ld16(tmem_addr(tmem_o0 + ob * 128, quarter, c0 + c), v);
                     tmem_ld_wait();
