@@ -21,9 +21,8 @@
 // implicit schedule: it is the warmup forward (flash_msa/warmup/msa_forward_cutedsl_warmup.py:22-67)
 // and the full-sequence proxy log-sum-exp (warmup/msa_backward_cutedsl_warmup.py:83-114).
 //
-// Scheduling: persistent CTAs (one per SM) take units from a global counter, early key blocks
-// (the long rows under causality) first.  CTA-wide phases are separated by block barriers; the
-// gather of the next tile and the epilogue of the previous tile overlap the current tile.
+// Scheduling: persistent CTAs (one per SM) take sub-units of reverse-index rows from a global counter;
+// inside a CTA the roles (softmax, gather, MMA issue) run decoupled, see sparse_fwd_kernel.
 #include "host_common.h"
 #include "msa_common.cuh"
 #include "sm100.cuh"
@@ -53,10 +52,10 @@ struct FwdParams {
 
 struct FwdSmem {
     uint64_t bar_kv, bar_kp, bar_done;
-    uint64_t q_full[2];              // Q rows of a tile have landed (arrivals: the store group)
+    uint64_t q_full[2];              // Q rows of a tile have landed (arrivals: the gather group)
     uint64_t s_full[2], s_empty[2];  // S accumulator written by the tensor core / read by the softmax group
     uint64_t p_full;                 // P written to shared memory (arrivals: the softmax group)
-    uint64_t o_full[2], o_empty[2];  // O accumulator written by the tensor core / read by the store group
+    uint64_t o_full[2], o_empty[2];  // O accumulator written by the tensor core / read back by the softmax group
     uint64_t unit_full[4];           // a sub-unit index has been published in unit_ring
     int32_t unit_ring[4];
     uint32_t tmem_slot;
@@ -66,21 +65,24 @@ struct FwdSmem {
 };
 
 constexpr int kFwdSoftmax = 512;                              // 16 warps: thread = (tile row, 32 columns)
-constexpr int kFwdStore = 256;                                // 8 warps: thread = (head-dim lane, 64 tile rows)
+constexpr int kFwdStore = 256;                                // 8 warps: row lists and cp.async gathers of the Q rows
 constexpr int kFwdThreads = kFwdSoftmax + kFwdStore + 32;     // + one warp that issues tcgen05.mma
 constexpr size_t kFwdSmemBytes = 6 * kTileBytes + 1024 + sizeof(FwdSmem);
 
 // Warp-specialised forward.  Three roles run decoupled and meet only through mbarriers:
 //   warps 0-15  softmax group : thread = (tile row, 32-column group); reads S from TMEM, writes P (bf16)
-//                               to shared memory and the per-row (max, sum) to global memory;
-//   warps 16-23 store group   : gathers the Q rows two tiles ahead (cp.async) and writes the finished
-//                               O^T accumulators out as unnormalised bf16 partial rows;
+//                               to shared memory and the per-row (max, sum) to global memory; while it
+//                               would wait for the next S it writes the finished O^T accumulator of the
+//                               previous tile out as unnormalised bf16 partial rows (thread = head-dimension
+//                               lane x 32 tile rows);
+//   warps 16-23 gather group  : draws the work, stages the row lists and gathers the Q rows two tiles
+//                               ahead (cp.async);
 //   warp 24     issuer        : loads K_j, V_j, Kp_j by TMA and issues S(t+1) = Q K^T, then
 //                               O^T(t) = V^T P^T(t), so the softmax of one tile overlaps the products of
 //                               its neighbours and the store of the tile before.  All its lanes run the
 //                               same code; only lane 0's tcgen05 instructions take effect (a lone
 //                               diverged lane is scheduled late).
-// Work is drawn from a global counter by one thread of the store group and published to the other
+// Work is drawn from a global counter by one thread of the gather group and published to the other
 // roles through a four-entry ring, so every role walks the same sequence of sub-units.
 // TMEM: S[2] at columns 0 and 128, O^T[2] at 256 and 384.
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             mbar_init(smem_u32(&sm->s_full[i]), 1);
             mbar_init(smem_u32(&sm->s_empty[i]), kFwdSoftmax / 32);
             mbar_init(smem_u32(&sm->o_full[i]), 1);
-            mbar_init(smem_u32(&sm->o_empty[i]), (kFwdStore + kFwdSoftmax) / 32);   // both groups read O
+            mbar_init(smem_u32(&sm->o_empty[i]), kFwdSoftmax / 32);
         }
         for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sm->unit_full[i]), 1);
         fence_mbar_init();
@@ -137,6 +139,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     uint32_t gt = 0;    // tiles seen so far by this CTA (every role counts the same sequence)
     uint32_t mt = 0;    // main-head tiles seen so far
     uint32_t nsub = 0;  // sub-units with work seen so far
+    uint32_t cbase = 0; // chunks of the sub-units seen so far: row lists live in ring entry (cbase + chunk - chunk0) % 8,
+                        // so the lists of a new sub-unit never land on entries the softmax group still reads
     bool bad = false;   // a bounded wait gave up: later waits are skipped, the status word is set at the end
     auto wait = [&](uint32_t bar, uint32_t parity) {
         if (!bad) bad = !mbar_wait(bar, parity);
@@ -243,10 +247,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             // =========================== softmax group ===========================
             const int cg = warp >> 2, c0 = cg * 32;
             int hh = 0, chunk = chunk0;
-            // The finished O^T of a main tile is written out by BOTH groups: the softmax warps take tile rows
-            // 0..63 (16 rows per warp, in the time they would otherwise wait for the next S), the store warps
-            // rows 64..127.  TMEM lane = head-dimension index, column = tile row: the 32 lanes of a warp store
-            // 64 contiguous bytes of ONE partial row per instruction.
+            // The finished O^T of a main tile is written out by the softmax warps themselves (32 tile rows per
+            // warp), in the time they would otherwise spend waiting for the next S: leaving it to the gather
+            // warps made them the bottleneck.  TMEM lane = head-dimension index, column = tile row: the 32 lanes
+            // of a warp store 64 contiguous bytes of ONE partial row per instruction.
             bool pending = false;        // O^T of main tile prev_mt has not been written out by this warp yet
             uint32_t prev_mt = 0;
             int prev_head = 0, prev_nrows = 0;
@@ -254,14 +258,19 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             auto store_share = [&]() {
                 wait(B2(sm->o_full, prev_mt), (prev_mt >> 1) & 1);   // P*V of that tile has finished (and has read P)
                 tc_fence_after_sync();
-                uint32_t v[16];
-                tmem_ld16(tmem_addr(tmem_o0 + (prev_mt & 1) * 128, quarter, 16 * cg), v);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                warp_arrive(B2(sm->o_empty, prev_mt));
                 const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
-                store_transposed_bf16_16(P.o_part + ((prev_slot0 + 16 * cg) * P.mpp + prev_head) * kHeadDim + row, rstride, v,
-                                         16 * cg, prev_nrows);
+#pragma unroll
+                for (int c = 0; c < 32; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_addr(tmem_o0 + (prev_mt & 1) * 128, quarter, 32 * cg + c), v);
+                    tmem_ld_wait();
+                    if (c == 16) {
+                        tc_fence_before_sync();
+                        warp_arrive(B2(sm->o_empty, prev_mt));
+                    }
+                    store_transposed_bf16_16(P.o_part + ((prev_slot0 + 32 * cg + c) * P.mpp + prev_head) * kHeadDim + row, rstride, v,
+                                             32 * cg + c, prev_nrows);
+                }
                 pending = false;
             };
             for (int t = 0; t < ntiles; ++t, ++gt) {
@@ -270,8 +279,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 const int nrows = min(kBlock, n - chunk * kBlock);
                 wait(B2(sm->s_full, gt), (gt >> 1) & 1);
                 tc_fence_after_sync();
-                // (the row list was published by the store group before it released the Q rows S was computed from)
-                const int qid = sm->rows[(chunk - chunk0) & 7][row];
+                // (the row list was published by the gather group before it released the Q rows S was computed from)
+                const int qid = sm->rows[(cbase + chunk - chunk0) & 7][row];
                 const bool live = qid >= 0;
                 // only the first chunk of a reverse-index row can hold rows of the key block itself
                 const bool masked = (chunk == 0);
@@ -353,9 +362,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             }
             if (pending) store_share();
         } else {
-            // =========================== store group ===========================
+            // =========================== gather group ===========================
             const int etid = tid - kFwdSoftmax;
-            const int c0 = 64 + ((warp - 16) >> 2) * 32;   // this thread's 32 tile rows of the transposed accumulator (rows 0..63: softmax warps)
             const GatherLane glane = make_gather_lane(etid);
             const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
             const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
@@ -370,13 +378,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                             qid = -1;
                         }
                     }
-                    sm->rows[(chunk - chunk0) & 7][etid] = qid;
+                    sm->rows[(cbase + chunk - chunk0) & 7][etid] = qid;
                 }
             };
             // 256 threads move a 128-row tile: thread (r0 = etid/16, 16-byte chunk etid%16) covers rows r0 + 16k
             auto gather_q = [&](int hh, int chunk, uint32_t gtile) {
                 const uint32_t dst = tile_q0 + (gtile & 1) * kTileBytes;
-                const int* rows = sm->rows[(chunk - chunk0) & 7];
+                const int* rows = sm->rows[(cbase + chunk - chunk0) & 7];
                 const __nv_bfloat16* base = (hh < P.mpp) ? q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh : qp_bp;
                 const int64_t stride = (hh < P.mpp) ? P.q_ss : P.qp_ss;
 #pragma unroll
@@ -386,28 +394,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     cp_async_16(dst + glane.dst_off + k * 2048, base + static_cast<int64_t>(ok ? rowid : 0) * stride + glane.col, ok);
                 }
             };
-            struct Meta { int64_t slot0; int nrows; int head; uint32_t mt; };
-            auto epilogue = [&](const Meta& m) {
-                const int ob = m.mt & 1;
-                wait(B2(sm->o_full, m.mt), (m.mt >> 1) & 1);
-                tc_fence_after_sync();
-                // O^T: TMEM lane = head-dimension index, column = tile row: 32 lanes store 64 contiguous
-                // bytes of ONE partial row per instruction
-                __nv_bfloat16* dst = P.o_part + ((m.slot0 + c0) * P.mpp + m.head) * kHeadDim + row;
-                const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
-#pragma unroll
-                for (int c = 0; c < 32; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_addr(tmem_o0 + ob * 128, quarter, c0 + c), v);
-                    tmem_ld_wait();
-                    store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, m.nrows);
-                }
-                tc_fence_before_sync();
-                warp_arrive(B2(sm->o_empty, m.mt));
-            };
-
-            // tile walk (head, chunk) for tiles t, t+1, t+2, t+3 without divisions
-            int hh = 0, chunk = chunk0;
+            // tile walk (head, chunk) for tiles t+1, t+2, t+3 without divisions
             int hh1 = 1, chunk_1 = chunk0;
             if (hh1 == hpc) { hh1 = 0; ++chunk_1; }
             int hh2 = hh1 + 1, chunk_2 = chunk_1;
@@ -426,10 +413,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             cp_async_wait<1>();
             fence_async_smem();
             warp_arrive(B2(sm->q_full, gt));
-            Meta prev{};
-            bool have_prev = false;
             for (int t = 0; t < ntiles; ++t, ++gt) {
-                const bool is_proxy = hh == P.mpp;
                 int hh3 = hh2 + 1, chunk_3 = chunk_2;
                 if (hh3 == hpc) { hh3 = 0; ++chunk_3; }
                 // Q rows of tile t+2 go into the buffer S(t) has finished reading
@@ -445,22 +429,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     warp_arrive(B2(sm->q_full, gt + 1));
                 }
                 named_barrier_sync(5, kFwdStore);   // row list of tile t+3 visible to the whole group before its gather
-                if (have_prev) epilogue(prev);
-                have_prev = false;
-                if (!is_proxy) {
-                    prev.slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
-                    prev.nrows = min(kBlock, n - chunk * kBlock);
-                    prev.head = hh;
-                    prev.mt = mt;
-                    ++mt;
-                    have_prev = true;
-                }
-                hh = hh1; chunk = chunk_1;
                 hh1 = hh2; chunk_1 = chunk_2;
                 hh2 = hh3; chunk_2 = chunk_3;
             }
-            if (have_prev) epilogue(prev);
         }
+        cbase += static_cast<uint32_t>(chunk1 - chunk0);
         ++nsub;
     }
     cp_async_wait<0>();
