@@ -54,6 +54,8 @@ def _declare(lib):
     lib.fmsa_abi_version.argtypes = []
     lib.fmsa_umma_selftest.restype = c_int
     lib.fmsa_umma_selftest.argtypes = [P, P, P, c_int, c_int, c_int, P, P]
+    lib.fmsa_pipeline_selftest.restype = c_int
+    lib.fmsa_pipeline_selftest.argtypes = [P, c_int64, P, P, P, P, P, c_int, c_int64, P, P]
     lib.fmsa_select_topk.restype = c_int
     lib.fmsa_select_topk.argtypes = [P, P, c_int64, c_int32, c_int32, P]
     lib.fmsa_reverse_index_workspace_bytes.restype = c_size_t

@@ -89,10 +89,127 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
     if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
+
+// Second known-answer hook: the staging and operand forms that only the attention kernels use.
+//   1. the A tile is gathered row by row with TMA (tile::gather4; rows outside the matrix read as zeros),
+//      D1 = A_g B^T as usual;
+//   2. bf16(D1 / 16) is written back into TMEM with tcgen05.st as a packed 16-bit A operand, split in two
+//      32-column halves exactly as the backward places P^T and dS^T, and feeds D2 = A2 * B (B used MN-major);
+//   3. the same bf16 rows leave through a swizzled staging tile and two TMA tile stores into a
+//      [slots][heads][128] partial-row buffer.
+// `withhold` = 1 skips the commit of the second product: the bounded wait for it (limit `limit_ns`) then
+// runs out, the kernel reports kStatusWaitTimeout and returns normally; this is how the tests exercise
+// the timeout path without hanging anything.
+__global__ void __launch_bounds__(128) pipeline_selftest_kernel(const __grid_constant__ CUtensorMap tmap_src,
+                                                                const __grid_constant__ CUtensorMap tmap_b,
+                                                                const __grid_constant__ CUtensorMap tmap_part,
+                                                                const int* __restrict__ rows, float* __restrict__ d1,
+                                                                float* __restrict__ d2, int withhold, uint64_t limit_ns,
+                                                                int* __restrict__ status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tile_a = base, tile_b = base + kTileBytes, tile_st = base + 2 * kTileBytes;
+    __shared__ __align__(8) uint64_t bars[3];
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t bar_tma = smem_u32(&bars[0]), bar_m1 = smem_u32(&bars[1]), bar_m2 = smem_u32(&bars[2]);
+
+    if (tid == 0) {
+        mbar_init(bar_tma, 1);
+        mbar_init(bar_m1, 1);
+        mbar_init(bar_m2, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t t_d1 = tmem, t_a2lo = tmem + 128, t_a2hi = tmem + 192, t_d2 = tmem + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(bar_tma, 2 * kTileBytes);
+            tma_load_2d(tile_b, &tmap_b, 0, 0, bar_tma);
+            tma_load_2d(tile_b + kPanelBytes, &tmap_b, 64, 0, bar_tma);
+        }
+        __syncwarp();
+        const int r0 = rows[4 * lane], r1 = rows[4 * lane + 1], r2 = rows[4 * lane + 2], r3 = rows[4 * lane + 3];
+        tma_gather4(tile_a + lane * 512, &tmap_src, 0, r0, r1, r2, r3, bar_tma);
+        tma_gather4(tile_a + kPanelBytes + lane * 512, &tmap_src, 64, r0, r1, r2, r3, bar_tma);
+    }
+    bool ok = mbar_wait(bar_tma, 0, limit_ns);
+    if (ok && tid == 0) {
+        tc_fence_after_sync();
+        umma_tile_128<false, false>(t_d1, tile_a, tile_b, false);
+        umma_commit(bar_m1);
+    }
+    ok = ok && mbar_wait(bar_m1, 0, limit_ns);
+    const int row = warp * 32 + lane;
+    if (ok) {
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_addr(t_d1, warp, c), r);
+            tmem_ld_wait();
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) d1[row * 128 + c + i] = __uint_as_float(r[i]);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                pk[i] = pack_bf16(__uint_as_float(r[2 * i]) * 0.0625f, __uint_as_float(r[2 * i + 1]) * 0.0625f);
+            // packed A operand: reduction elements c..c+31 -> 16 columns of the lower or upper half
+            tmem_st16(tmem_addr(c < 64 ? t_a2lo : t_a2hi, warp, (c & 63) >> 1), pk);
+            // the same values into the swizzled staging tile (row `row`, 16-byte chunks c/8 .. c/8+3)
+#pragma unroll
+            for (int k8 = 0; k8 < 4; ++k8)
+                st_shared_v4(tile_st + swz_offset(row, (c >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
+        }
+        tmem_st_wait();
+        fence_async_smem();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (ok && tid == 0) {
+        tc_fence_after_sync();
+        umma_tile_128_ts<true>(t_d2, t_a2lo, t_a2hi, tile_b, false);
+        if (!withhold) umma_commit(bar_m2);
+        tma_store_3d(&tmap_part, tile_st, 0, 1, 0);
+        tma_store_3d(&tmap_part, tile_st + kPanelBytes, 64, 1, 0);
+        tma_store_commit();
+        tma_store_wait_all();
+    }
+    ok = ok && mbar_wait(bar_m2, 0, limit_ns);
+    if (ok) {
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_addr(t_d2, warp, c), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) d2[row * 128 + c + i] = __uint_as_float(r[i]);
+        }
+    }
+    if (!ok) atomicMax(status, kStatusWaitTimeout);
+    if (withhold && tid == 0) {
+        // the product that nobody waited for must still have finished before its TMEM columns are freed
+        umma_commit(bar_m2);
+        mbar_wait(bar_m2, 0);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
 }  // namespace
 }  // namespace fmsa
 
-extern "C" int fmsa_abi_version(void) { return 2; }
+extern "C" int fmsa_abi_version(void) { return 3; }
 
 extern "C" int fmsa_umma_selftest(const void* a, const void* b, float* d, int a_mn, int b_mn, int use_tma, int* status,
                                   void* stream) {
@@ -111,5 +228,23 @@ extern "C" int fmsa_umma_selftest(const void* a, const void* b, float* d, int a_
         return FMSA_ERR_CUDA;
     umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, a_mn, b_mn, use_tma, ta, tb, status);
+    return check_launch();
+}
+
+extern "C" int fmsa_pipeline_selftest(const void* src, int64_t src_rows, const int32_t* rows, const void* b, float* d1,
+                                      float* d2, void* part, int withhold, int64_t limit_ns, int* status, void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(src && rows && b && d1 && d2 && part && status && src_rows > 0 && limit_ns > 0);
+    FMSA_REQUIRE(aligned16(src) && aligned16(b) && aligned16(part));
+    CUtensorMap ts, tb, tp;
+    if (!make_tmap_gather(&ts, src, static_cast<uint64_t>(src_rows)) || !make_tmap_rows(&tb, b, 128, 256, 128) ||
+        !make_tmap_partials_swz(&tp, part, 128, 2))
+        return FMSA_ERR_CUDA;
+    const size_t smem = 3 * kTileBytes + 1024;
+    if (cudaFuncSetAttribute(pipeline_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+        return FMSA_ERR_CUDA;
+    pipeline_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+        ts, tb, tp, rows, d1, d2, withhold, static_cast<uint64_t>(limit_ns), status);
     return check_launch();
 }

@@ -84,21 +84,39 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after about two seconds of wall time and returns false.  Callers vote
-// on the result with a block-wide barrier so that the whole CTA leaves together.
+// Bounded wait: gives up after `limit_ns` of wall time (about two seconds by default) and returns false.
 // The polling loop is kept out of line: the warp-specialised kernels have dozens of wait sites, and
 // their code has to stay small enough for the instruction cache (several roles run different code
 // at the same time, and a kernel much above 100 KB was measured to run several times slower).
-static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
         if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
-        if (global_timer_ns() - t0 > 2000000000ull) return false;
+        if (global_timer_ns() - t0 > limit_ns) return false;
     }
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_poll(bar, parity);
+    return mbar_wait_poll(bar, parity, limit_ns);
+}
+// Variant for kernels whose roles run decoupled: `abort_flag` is a word in shared memory that any thread sets
+// when one of its waits ran out.  Every other waiter sees it within one parking period and gives up as well,
+// so the whole CTA leaves its loops together instead of each role waiting out its own limit in turn.
+static __device__ __noinline__ bool mbar_wait_poll_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_poll_abortable(bar, parity, abort_flag);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -257,6 +275,61 @@ __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp_in_group, 
     return base + (static_cast<uint32_t>(warp_in_group * 32) << 16) + static_cast<uint32_t>(col);
 }
 
+// TMEM stores: the mirror image of the loads above (thread i of warp w writes lane 32*(w%4)+i).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05.mma with the A operand in TMEM ("TS" form): D[128 x 128] (+)= A[128 x 128] * B^T.
+// A is a 128 x 128 bf16 matrix whose row m lives in TMEM lane m; a 32-bit column holds the two
+// consecutive reduction elements (2c, 2c+1), the even one in the low half, so the whole operand
+// takes 64 columns and one instruction (16 reduction elements) reads 8 of them.  The operand may
+// be split: `a_lo` is the TMEM address of reduction elements 0..63 (32 columns), `a_hi` that of
+// elements 64..127.  B is a shared-memory tile as in umma_tile_128.
+// ---------------------------------------------------------------------------------------------
+template <bool B_MN>
+__device__ __forceinline__ void umma_tile_128_ts(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_tile,
+                                                 bool accumulate, uint32_t elect = 1u) {
+    constexpr uint32_t idesc = umma_idesc(128, false, B_MN);
+    const uint64_t b0 = B_MN ? desc_mnmajor(b_tile, 0) : desc_kmajor(b_tile, 0);
+#define FMSA_UMMA_TS_STEP(AREG, AOFF, BI)                                       \
+    "add.u32 a, " #AREG ", " #AOFF ";\n"                                        \
+    "add.s64 b, %3, " #BI ";\n"                                                 \
+    "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %4, t;\n"
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q, t;\n"
+        ".reg .b64 b;\n"
+        ".reg .b32 a;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "setp.ne.b32 q, %6, 0;\n"
+        "setp.eq.b32 t, %6, %6;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %3, %4, p;\n"
+        FMSA_UMMA_TS_STEP(%1, 8, %7) FMSA_UMMA_TS_STEP(%1, 16, %8) FMSA_UMMA_TS_STEP(%1, 24, %9)
+        FMSA_UMMA_TS_STEP(%2, 0, %10) FMSA_UMMA_TS_STEP(%2, 8, %11) FMSA_UMMA_TS_STEP(%2, 16, %12)
+        FMSA_UMMA_TS_STEP(%2, 24, %13)
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "l"(b0), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(elect),
+        "n"(umma_kstep(B_MN, 1)), "n"(umma_kstep(B_MN, 2)), "n"(umma_kstep(B_MN, 3)), "n"(umma_kstep(B_MN, 4)),
+        "n"(umma_kstep(B_MN, 5)), "n"(umma_kstep(B_MN, 6)), "n"(umma_kstep(B_MN, 7))
+        : "memory");
+#undef FMSA_UMMA_TS_STEP
+}
+
 // ---------------------------------------------------------------------------------------------
 // cp.async row gather into a swizzled tile
 // ---------------------------------------------------------------------------------------------
@@ -351,6 +424,18 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int 
 __device__ __forceinline__ void tma_load_tile(uint32_t tile, const void* tmap, int s0, int h, int b, uint32_t bar) {
     tma_load_4d(tile, tmap, 0, s0, h, b, bar);
     tma_load_4d(tile + kPanelBytes, tmap, 64, s0, h, b, bar);
+}
+// TMA row gather: four rows r0..r3 of a 2-D bf16 matrix (tensor map with a 64-column x 1-row box, 128-byte
+// swizzle), 64 columns starting at `col`, land as four consecutive 128-byte rows at `dst`.  `dst` must be
+// 512-byte aligned inside a 1024-byte aligned tile so that the swizzle pattern matches the operand layout.
+// A row index outside the matrix yields a row of zeros.  Completes 512 bytes on `bar`.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int col, int r0, int r1, int r2, int r3,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+        "l"(tmap), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+        : "memory");
 }
 // TMA tile STORE shared -> global (bulk-group completion).  The source tile must have been made
 // visible to the async proxy (fence_async_smem + a barrier) before the elected thread issues it.

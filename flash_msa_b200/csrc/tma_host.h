@@ -69,6 +69,43 @@ inline bool make_tmap_partials(CUtensorMap* map, const void* base, uint64_t slot
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Row-gather view of a (B, H, S, 128) bf16 activation whose strides are all multiples of 128 elements: a
+// 2-D matrix of 256-byte rows in which element row (b, h, s) has index (b*stride_b + h*stride_h +
+// s*stride_s) / 128.  Box = 64 columns x 1 row, 128-byte swizzle: the form tile::gather4 loads take.
+inline bool gather_compatible(const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && sb > 0 && sh > 0 && ss > 0 && sb % 128 == 0 && sh % 128 == 0 &&
+           ss % 128 == 0;
+}
+inline bool make_tmap_gather(CUtensorMap* map, const void* base, uint64_t nrows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || nrows == 0 || nrows > 0x7fffffffull) return false;
+    const cuuint64_t dims[2] = {128, nrows};
+    const cuuint64_t strides[1] = {256};
+    const cuuint32_t box[2] = {64, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// Number of 256-byte rows the gather view of a (B, H, S, 128) activation spans.
+inline uint64_t gather_rows(int64_t B, int64_t H, int64_t S, int64_t sb, int64_t sh, int64_t ss) {
+    return static_cast<uint64_t>(((B - 1) * sb + (H - 1) * sh + (S - 1) * ss) / 128 + 1);
+}
+
+// Partial-row buffer [slots][heads][128] bf16 for tile STORES of 128 slots x one head from a shared-memory
+// tile in the operand layout (two 64-column panels, 128-byte swizzle): one store per panel.
+inline bool make_tmap_partials_swz(CUtensorMap* map, const void* base, uint64_t slots, uint64_t heads) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {128, heads, slots};
+    const cuuint64_t strides[2] = {256, 256 * heads};
+    const cuuint32_t box[3] = {64, 1, 128};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // A TMA-loadable activation: last dimension contiguous, every stride a multiple of 8 elements
 // (16 bytes), base 16-byte aligned.
 inline bool tma_compatible(const void* ptr, int64_t sb, int64_t sh, int64_t ss) {

@@ -69,6 +69,25 @@ def umma_selftest(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool, use_
     return d, status
 
 
+def pipeline_selftest(src: torch.Tensor, rows: torch.Tensor, b: torch.Tensor, withhold: bool = False,
+                      limit_ns: int = 2_000_000_000):
+    """Test hook: TMA row gather -> product -> packed TMEM operand -> product, plus a swizzled TMA tile store.
+    Returns (d1, d2, part, status); see fmsa_pipeline_selftest in the header."""
+    _require_cuda(src, rows, b)
+    lib = _lib.load()
+    src, b = src.contiguous(), b.contiguous()
+    rows = rows.to(torch.int32).contiguous()
+    dev = src.device
+    d1 = torch.zeros(128, 128, dtype=torch.float32, device=dev)
+    d2 = torch.zeros(128, 128, dtype=torch.float32, device=dev)
+    part = torch.zeros(128, 2, 128, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    _lib.check(lib.fmsa_pipeline_selftest(src.data_ptr(), src.shape[0], rows.data_ptr(), b.data_ptr(), d1.data_ptr(),
+                                          d2.data_ptr(), part.data_ptr(), int(withhold), int(limit_ns),
+                                          status.data_ptr(), _stream(dev)), "fmsa_pipeline_selftest")
+    return d1, d2, part, status
+
+
 def select_topk(block_scores: torch.Tensor, top_k_blocks: int) -> torch.Tensor:
     """Top-k over fp32 block scores [B,Hp,S,NB] -> int32 [B,Hp,S,Kb]; order (score desc, index
     asc), own block first, sentinel NB in unused slots."""

@@ -59,6 +59,18 @@ int fmsa_abi_version(void);
 int fmsa_umma_selftest(const void* a, const void* b, float* d, int a_mn, int b_mn, int use_tma, int* status,
                        void* stream);
 
+/* Test hook for the staging and operand forms that only the attention kernels use: the A tile is
+ * gathered row by row with TMA (tile::gather4; row ids outside [0, src_rows) read as zeros), D1 = A_g B^T;
+ * bf16(D1/16) goes back into TMEM with tcgen05.st as a packed A operand and feeds D2 = A2 * B (B used
+ * MN-major); the same bf16 rows leave through a swizzled staging tile and TMA tile stores into
+ * part[slot][1][:] of a [128][2][128] bf16 buffer.
+ *   src bf16 [src_rows][128];  rows int32[128];  b bf16 [128][128];  d1, d2 fp32 [128][128];  status int32[1].
+ * withhold = 1 leaves out the completion signal of the second product: the wait for it, bounded by
+ * limit_ns, runs out, status becomes 1 and the kernel returns normally (how the tests reach the
+ * timeout path).  No counterpart in the reference. */
+int fmsa_pipeline_selftest(const void* src, int64_t src_rows, const int32_t* rows, const void* b, float* d1, float* d2,
+                           void* part, int withhold, int64_t limit_ns, int* status, void* stream);
+
 /* Per-row top-k over materialised block scores.
  * Replaces the running top-k of the reference select kernel
  * (flash_msa/msa_select_cutedsl.py:310-329, 370-392): total order (score descending, block

@@ -14,7 +14,7 @@ def test_library_builds_and_exports_declared_symbols():
     assert "fmsa_select_topk" in names and "fmsa_reverse_index" in names
     for name in names:
         assert hasattr(lib, name), name
-    assert lib.fmsa_abi_version() == 2          # 2: kl_value argument of fmsa_sparse_bwd, fmsa_copy2d_async
+    assert lib.fmsa_abi_version() == 3          # 3: fmsa_pipeline_selftest
 
 
 def test_argument_errors_do_not_launch():

@@ -32,6 +32,48 @@ def test_umma_tile_product(ops, a_mn, b_mn, use_tma):
     assert err <= 1e-2, err     # bf16 inputs are exact in fp32; only the summation order differs
 
 
+def test_gather_tmem_operand_and_tile_store(ops):
+    """TMA row gather (with out-of-range rows), a product whose A operand was written to TMEM with tcgen05.st,
+    and the swizzled TMA tile store of partial rows."""
+    g = torch.Generator(device="cpu").manual_seed(11)
+    src = torch.randn(1000, 128, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(128, 128, generator=g).to(torch.bfloat16).cuda()
+    rows = torch.randint(0, 1000, (128,), generator=g)
+    rows[5] = 1000          # first row outside the matrix
+    rows[77] = 2 ** 30      # far outside
+    rows[100:104] = torch.tensor([999, 0, 999, 0])
+    d1, d2, part, status = ops.pipeline_selftest(src, rows.cuda(), b)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    a = src.float()[rows.clamp(max=999)]
+    a[5] = 0
+    a[77] = 0
+    ref1 = a @ b.float().t()
+    assert (d1 - ref1).abs().max().item() <= 1e-2
+    a2 = (d1 * 0.0625).to(torch.bfloat16)
+    ref2 = a2.float() @ b.float()
+    assert (d2 - ref2).abs().max().item() <= 2e-2
+    assert torch.equal(part[:, 1, :], a2)
+    assert part[:, 0, :].abs().max().item() == 0
+
+
+def test_bounded_wait_runs_out(ops):
+    """A completion signal that never comes: the bounded wait gives up after its limit, the kernel returns
+    normally and reports status 1 (nothing traps or spins on)."""
+    g = torch.Generator(device="cpu").manual_seed(12)
+    src = torch.randn(256, 128, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(128, 128, generator=g).to(torch.bfloat16).cuda()
+    rows = torch.arange(128)
+    d1, d2, part, status = ops.pipeline_selftest(src, rows.cuda(), b, withhold=True, limit_ns=3_000_000)
+    torch.cuda.synchronize()
+    assert status.item() == 1
+    assert (d1 - src.float()[:128] @ b.float().t()).abs().max().item() <= 1e-2   # the first product still arrived
+    # the context stays usable
+    d1b, _, _, status_b = ops.pipeline_selftest(src, rows.cuda(), b)
+    torch.cuda.synchronize()
+    assert status_b.item() == 0 and torch.equal(d1, d1b)
+
+
 @pytest.mark.parametrize("s,kb", [(128, 1), (512, 2), (1024, 4), (2048, 16), (4096, 32), (8192, 33), (8192, 64), (16384, 128)])
 def test_topk_bit_exact(ops, s, kb):
     nb = s // 128
