@@ -8,7 +8,8 @@ import re
 from ctypes import c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libflash_msa_b200.so")
+# FLASH_MSA_B200_LIB selects another build of the library (e.g. one compiled with extra diagnostics).
+LIB_PATH = os.environ.get("FLASH_MSA_B200_LIB") or os.path.join(PKG_DIR, "libflash_msa_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "flash_msa_b200.h")
 
 FMSA_OK = 0

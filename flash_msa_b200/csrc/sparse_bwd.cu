@@ -2,22 +2,27 @@
 //
 // Work unit = (batch, KV head, key block j), exactly as in the forward: K_j and V_j stay in shared
 // memory, the unit walks the reverse-index row of every proxy head of its group in chunks of 128
-// gathered query rows.  For each chunk the main heads of the proxy head run one after another
-//     S  = Q_g K_j^T            dP = dO_g V_j^T                     (tcgen05, K-major operands)
-//     P  = exp2(S*c - lse)      dS = P o (dP - delta)               (fp32, rounded to bf16 in smem)
-//     dV += P^T dO_g            dK += dS^T Q_g                      (MN-major operands, TMEM-resident
-//                                                                    accumulators for the whole unit)
-//     dQ  = dS K_j  -> scaled, reduced into the fp32 dQ buffer with vector red.add
-// while every thread sums the bf16-rounded P of its (row, columns) over the heads: the KL teacher.
+// gathered query rows.  For each chunk the main heads of the proxy head run one after another.  Scores
+// are computed TRANSPOSED (TMEM lane = key, column = query) so that P^T and dS^T, written back into TMEM
+// as bf16 over the columns S^T and dP^T occupied, are the TMEM operands of the dV and dK products:
+//     S^T = K_j Q_g^T           dP^T = V_j dO_g^T                   (both operands in shared memory)
+//     P^T = exp2(S^T*c - lse)   dS^T = P^T o (dP^T - delta)         (fp32, rounded to bf16)
+//     dV += P^T dO_g            dK += dS^T Q_g                      (A operand in TMEM; accumulators stay in
+//                                                                    TMEM for the whole sub-unit)
+//     dQ  = dS K_j                                                  (dS^T also goes to shared memory)
+// while every thread sums the P of its (key, queries) over the heads: the KL teacher.
 // Then one proxy tile:
-//     Sp = Qp_g Kp_j^T          p_px = exp2(Sp*c - lse_proxy)       dSp = p_px - teacher/mpp
-//     dQp = dSp Kp_j, dKp = dSp^T Qp_g -> scaled by scale/(B*Hp*S), reduced into fp32 buffers.
-// The unit owns dK_j and dV_j, so they are written once, in bf16, without atomics.
+//     Sp^T = Kp_j Qp_g^T        p_px = exp2(Sp^T*c - lse_proxy)     dSp^T = p_px - teacher/mpp
+//     dKp = dSp^T Qp_g, dQp = dSp Kp_j.
+// dQ and dQp leave as bf16 per-edge partial rows (a combine kernel sums them per query row, applying
+// scale and scale/(B*Hp*S)); dK, dV (once per sub-unit) and dKp (once per proxy tile) are added to fp32
+// accumulators with vector reductions and cast afterwards.
 //
 // Formulas and rounding points follow the reference kernel
 // (flash_msa/msa_backward_cutedsl.py:456-733: P and dS rounded to the input type before the
-// second products, teacher averaged from the rounded P, ds_px = c*(p_px - teacher)) and
-// flash_msa/flash_msa.py:99-125 (delta, 1/(B*Hp*S), grad_kl applied afterwards on the device).
+// second products, ds_px = c*(p_px - teacher)) and flash_msa/flash_msa.py:99-125 (delta, 1/(B*Hp*S),
+// grad_kl applied afterwards on the device).  Differences: the teacher is summed from the unrounded P in
+// fp16 pairs, and dSp is rounded to bf16 before the 1/(B*Hp*S) factor is applied.
 // `dense` mode is the warmup backward (flash_msa/warmup/msa_backward_cutedsl_warmup.py:117-191):
 // every causal (query block, key block) pair, with the schedule implied instead of built on the host.
 #include <cuda_fp16.h>
@@ -30,17 +35,22 @@
 namespace fmsa {
 namespace {
 
+#ifdef FMSA_TRACE
+// Debug builds only: cycles each warp of CTA 0 spent inside its role (slot 0) and inside waits of kind 1..7.
+__device__ unsigned long long g_bwd_trace[16][8];
+#endif
+
 struct BwdParams {
-    const __nv_bfloat16 *q, *qp, *kp, *dout;
-    int64_t q_sb, q_sh, q_ss;
-    int64_t qp_sb, qp_sh, qp_ss;
-    int64_t kp_sb, kp_sh, kp_ss;
-    int64_t do_sb, do_sh, do_ss;
+    // Row-gather views: element row (b, h, s) of q / d_out / q_proxy is matrix row b*row_b + h*row_h + s*row_s.
+    int64_t q_row_b, q_row_h, q_row_s;
+    int64_t do_row_b, do_row_h, do_row_s;
+    int64_t qp_row_b, qp_row_h, qp_row_s;
+    int32_t q_rows_total, do_rows_total, qp_rows_total;   // first row index outside each view (reads as zeros)
     const float *lse, *lse_proxy, *delta;   // [B,Hq,S], [B,Hp,S], [B,Hq,S]
     const int32_t* row_ptr;
     const int32_t* col_q;
-    __nv_bfloat16* dq_part;    // [(edge - edge_base) * mpp + head][128]: per-edge dQ contributions
-    __nv_bfloat16* dqp_part;   // [(edge - edge_base)][128]: per-edge dQp contributions (already * scale/(B*Hp*S))
+    __nv_bfloat16* dq_part;    // [(edge - edge_base) * mpp + head][128]: per-edge dQ contributions (unscaled)
+    __nv_bfloat16* dqp_part;   // [(edge - edge_base)][128]: per-edge dQp contributions (unscaled)
     // fp32, zero-initialised: [B,Hpkv,S,128], [B,Hkv,S,128] x2
     float *dkp_acc, *dk_acc, *dv_acc;
     int32_t* counter;
@@ -49,74 +59,116 @@ struct BwdParams {
     int g_begin, G;
     int64_t n_subunits;
     int with_kl, dense;
-    float scale, scale_log2e, kl_out_scale;   // kl_out_scale = scale / (B*Hp*S)
-    float* kl_value;    // optional: += KL(teacher || proxy) summed over this launch's rows, / (B*Hp*S)
+    float scale_log2e;
+    float* kl_value;        // optional: += KL(teacher || proxy) summed over this launch's rows, / (B*Hp*S)
     float kl_value_scale;   // ln(2) / (B*Hp*S)
 };
 
-struct BwdSmem {
-    uint64_t bar_kv, bar_a, bar_dq, bar_dv, bar_dk;
-    uint32_t tmem_slot;
-    int32_t unit;
-    int32_t rows[3][128];
+struct BwdUnit {
+    int32_t j, b, kvh, p, n, chunk0, chunk1, pad;   // chunk1 < 0: no more work
+    int64_t e0;
 };
 
-constexpr int kBwdWorkers = 512;            // 16 worker warps
-constexpr int kBwdThreads = kBwdWorkers + 32;   // + one warp whose lane 0 only issues tcgen05.mma
-constexpr size_t kBwdSmemBytes = 7 * kTileBytes + 1024 + sizeof(BwdSmem);
+constexpr int kBwdUnitRing = 8;
 
-// Roles.  Worker warp w (0..15) may read TMEM lanes 32*(w%4)..+31 and owns the 32 accumulator
-// columns starting at 32*(w/4).  Warp 16 is the MMA issuer: a thread that issues tcgen05.mma is held
-// while the tensor core's queue is full, so it must not carry any other work.
-//
-// Shared memory: K_j, V_j (resident), two Q buffers (rows gathered one tile ahead), one dO buffer
-// (refilled as soon as dV has consumed it), P and dS.
-// TMEM (512 columns): [0,128) S, then dKp^T in a proxy tile; [128,256) dP, then dQ^T / dQp^T;
-// [256,384) dV^T; [384,512) dK^T.
-//
-// Products of the second group are issued TRANSPOSED (M = head dimension): a TMEM lane is then a
-// head-dimension index and a column a row of the output, so the 32 lanes of a warp write 32
-// consecutive elements of ONE output row per instruction.
-//
-// Per tile:   issuer:  [S ahead] dP | ......... | dQ^T dV^T dK^T S(next) |
-//             workers: gather Q(next), wait | P, dS | wait dQ, store it; refill dO; (dKp) |
-// dQ and dQp leave the kernel as bf16 per-edge partial rows (summed per query row by
-// bwd_combine_kernel): fp32 atomics for them would move ~6 GB through the L2 atomic units per step.
-__global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
+// Per-tile facts about the 128 gathered query rows (= TMEM columns), staged for the compute groups.
+struct BwdRowStats {
+    float neg_lse[128];    // -lse * log2(e); -inf for a dead row, whose probabilities then come out as 0
+    float neg_delta[128];  // -delta
+    uint8_t limit[128];    // last visible key of the row inside this key block (127 = all)
+};
+
+struct BwdCtrl {
+    uint64_t k_full, v_full, kv_empty, acc_full, acc_free;
+    uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2], st_full[2], st_empty[2];
+    uint64_t sdp_full, pds_full, dq_full, r0_free, ds_free, dkp_full, r1_free;
+    uint64_t unit_full[kBwdUnitRing];
+    BwdUnit units[kBwdUnitRing];
+    BwdRowStats stats[2];
+    uint32_t tmem_slot;
+    int32_t abort_flag;
+};
+
+// Roles (warp index): 0-3 compute group A (queries 0..63 of a tile), 4-7 compute group B (queries 64..127),
+// 8-11 output group, 12 row gather (Q, dO, Qp; Kp_j), 13 K/V loads and row statistics, 14 MMA issue.
+constexpr int kBwdThreads = 16 * 32;   // (warp 15 only takes part in the block-wide steps)
+constexpr size_t kBwdTileBytes = 7 * static_cast<size_t>(kTileBytes);   // K, V, Q x2, dO x2, dS^T
+constexpr size_t kBwdSmemBytes = 232448;                                 // everything a CTA can have
+static_assert(kBwdTileBytes + sizeof(BwdCtrl) <= kBwdSmemBytes, "shared memory budget of one CTA");
+constexpr int kStatusBadSmem = 3;   // the dynamic shared memory window does not start on a 1024-byte boundary
+
+// Warp-specialised backward.  Every role walks the same sequence of sub-units (published by the gather warp in a
+// ring) and of tiles.  TMEM (512 columns):
+//   R0 [0,128)   S^T, overwritten in place by P^T (bf16: queries 0..63 in columns 0..31, queries 64..127 in columns
+//                64..95), then dQ (lane = query).  Proxy tile: Sp^T, dSp^T in place, then dQp.
+//   R1 [128,256) dP^T, overwritten by dS^T in the same split.  Proxy tile: dKp (lane = key).
+//   R2 [256,384) dV, R3 [384,512) dK (lane = key), accumulated over the sub-unit.
+// Issue order of a main tile t (one full product always lies between a product that reads a TMEM operand and a
+// later one that overwrites those columns):
+//   [compute(t) done]  dV += P^T dO,  dK += dS^T Q,  dQ = dS K -> R0,  dP^T(t+1) -> R1,  [dQ read out]  S^T(t+1) -> R0.
+// Hand-offs (mbarriers; one arrival per warp or per tcgen05.commit): q_full/do_full (TMA bytes) <- q_empty/do_empty;
+// st_full <- st_empty (row statistics); sdp_full (S^T and dP^T of a tile), pds_full (P^T, dS^T written), dq_full,
+// r0_free (dQ read out), ds_free (the dS^T tile, which doubles as the staging tile of the dQ store, is reusable),
+// dkp_full / r1_free (proxy tile), acc_full / acc_free (dV, dK flushed at the end of a sub-unit).
+__global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                                    const __grid_constant__ CUtensorMap tmap_do,
+                                                                    const __grid_constant__ CUtensorMap tmap_qp,
+                                                                    const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
+                                                                    const __grid_constant__ CUtensorMap tmap_kp,
                                                                     const __grid_constant__ CUtensorMap tmap_dq,
                                                                     const __grid_constant__ CUtensorMap tmap_dqp,
                                                                     const BwdParams P) {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    if ((tiles - smem_u32(smem_raw)) + kBwdTileBytes + sizeof(BwdCtrl) > kBwdSmemBytes) {
+        if (threadIdx.x == 0) atomicMax(P.status, kStatusBadSmem);
+        return;
+    }
     const uint32_t tile_k = tiles, tile_v = tiles + kTileBytes;
-    const uint32_t tile_q0 = tiles + 2 * kTileBytes, tile_do = tiles + 4 * kTileBytes;
-    const uint32_t tile_p = tiles + 5 * kTileBytes, tile_ds = tiles + 6 * kTileBytes;
-    BwdSmem* sm = reinterpret_cast<BwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 7 * kTileBytes);
+    const uint32_t tile_q0 = tiles + 2 * kTileBytes, tile_do0 = tiles + 4 * kTileBytes, tile_ds = tiles + 6 * kTileBytes;
+    BwdCtrl* sm = reinterpret_cast<BwdCtrl*>(smem_raw + (tiles - smem_u32(smem_raw)) + kBwdTileBytes);
 
-    // The warp index goes through a shuffle so that the compiler knows it, and every branch on the warp's
-    // role, to be uniform across the warp: the issuer's descriptor arithmetic can then use the uniform datapath.
     const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
-    const bool worker = warp < 16;
-    const bool issuer = (warp == 16);            // the whole warp runs the issue sequence ...
-    const uint32_t elect = (lane == 0) ? 1u : 0u;   // ... and only this lane's instructions take effect
-    const int quarter = warp & 3, cg = (warp >> 2) & 3;
-    const int row = quarter * 32 + lane, c0 = cg * 32;
-    const GatherLane glane = make_gather_lane(tid & 511);
-    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_a = smem_u32(&sm->bar_a), bar_dq = smem_u32(&sm->bar_dq);
-    const uint32_t bar_dv = smem_u32(&sm->bar_dv), bar_dk = smem_u32(&sm->bar_dk);
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;   // TMEM lane of this thread: key (compute, dKp/dV/dK read-out) or query (dQ read-out)
+    const uint32_t elect = (lane == 0) ? 1u : 0u;
+    auto BAR = [&](uint64_t& b) { return smem_u32(&b); };
 
     if (tid == 0) {
-        mbar_init(bar_kv, 1);
-        mbar_init(bar_a, 1);
-        mbar_init(bar_dq, 1);
-        mbar_init(bar_dv, 1);
-        mbar_init(bar_dk, 1);
+        mbar_init(BAR(sm->k_full), 1);
+        mbar_init(BAR(sm->v_full), 1);
+        mbar_init(BAR(sm->kv_empty), 1);
+        mbar_init(BAR(sm->acc_full), 1);
+        mbar_init(BAR(sm->acc_free), 4);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(sm->q_full[i]), 1);
+            mbar_init(BAR(sm->q_empty[i]), 1);
+            mbar_init(BAR(sm->do_full[i]), 1);
+            mbar_init(BAR(sm->do_empty[i]), 1);
+            mbar_init(BAR(sm->st_full[i]), 1);
+            mbar_init(BAR(sm->st_empty[i]), 8);
+        }
+        mbar_init(BAR(sm->sdp_full), 1);
+        mbar_init(BAR(sm->pds_full), 8);
+        mbar_init(BAR(sm->dq_full), 1);
+        mbar_init(BAR(sm->r0_free), 4);
+        mbar_init(BAR(sm->ds_free), 1);
+        mbar_init(BAR(sm->dkp_full), 1);
+        mbar_init(BAR(sm->r1_free), 4);
+        for (int i = 0; i < kBwdUnitRing; ++i) mbar_init(BAR(sm->unit_full[i]), 1);
+        sm->abort_flag = 0;
         fence_mbar_init();
+        prefetch_tmap(&tmap_q);
+        prefetch_tmap(&tmap_do);
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
         prefetch_tmap(&tmap_dq);
-        if (P.with_kl) prefetch_tmap(&tmap_dqp);
+        if (P.with_kl) {
+            prefetch_tmap(&tmap_qp);
+            prefetch_tmap(&tmap_kp);
+            prefetch_tmap(&tmap_dqp);
+        }
     }
     if (warp == 0) {
         tmem_alloc(smem_u32(&sm->tmem_slot), 512);
@@ -125,358 +177,490 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = __shfl_sync(0xffffffffu, sm->tmem_slot, 0);
-    const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 384;
+    const uint32_t tmem = sm->tmem_slot;
+    const uint32_t r0 = tmem, r1 = tmem + 128, r2 = tmem + 256, r3 = tmem + 384;
 
-    const int hpc = P.mpp + (P.with_kl ? 1 : 0);
-    const float inv_mpp = 1.f / static_cast<float>(P.mpp);
+    const int hpc = P.mpp + (P.with_kl ? 1 : 0);   // tiles per chunk
     const int64_t edge_base = P.dense ? dense_edge_base(static_cast<int64_t>(P.g_begin) * P.ppk, P.S, P.NB)
                                       : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
-    uint32_t ph_kv = 0, ph_a = 0, ph_dq = 0, ph_dv = 0, ph_dk = 0;
-    bool bad = false;   // a bounded wait gave up: later waits are skipped, the status word is set at the end
-    float kl_acc = 0.f;   // this thread's share of sum t * (log2 t - log2 p_proxy), when the KL value is asked for
+    volatile int* abort_flag = &sm->abort_flag;
+    bool bad = false;   // a bounded wait gave up (here or in another role): the thread stops taking work
+#ifdef FMSA_TRACE
+    unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long trace_t0 = clock64();
+#endif
+    auto wait = [&](uint32_t bar, uint32_t parity, int kind = 1) {   // every lane of the warp calls it; the verdict is warp-uniform
+#ifdef FMSA_TRACE
+        const long long w0 = clock64();
+#endif
+        if (!bad) bad = __any_sync(0xffffffffu, !mbar_wait_abortable(bar, parity, abort_flag));
+#ifdef FMSA_TRACE
+        trace_acc[kind & 7] += static_cast<unsigned long long>(clock64() - w0);
+#endif
+        (void)kind;
+    };
+    auto group_or = [&](int id, bool flag) -> bool {   // 128-thread barrier that also ORs a flag
+        uint32_t r;
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.b32 q, %1, 0;\n"
+            "barrier.cta.red.or.pred p, %2, 128, q;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(r)
+            : "r"(flag ? 1u : 0u), "r"(id)
+            : "memory");
+        return r != 0;
+    };
+    auto warp_arrive = [&](uint32_t bar) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+    };
 
-    for (;;) {
-        if (tid == 0) sm->unit = atomicAdd(P.counter, 1);
-        __syncthreads();
-        const int u = __shfl_sync(0xffffffffu, sm->unit, 0);   // (uniform anyway; tells the compiler so)
-        __syncthreads();
-        if (u >= P.n_subunits) break;
-        const SubUnit su = decode_subunit(u, P.NB, P.ppk);
-        const int j = su.j;
-        const int g = P.g_begin + su.g;
-        const int b = g / P.Hkv, kvh = g % P.Hkv;
-        const int p = kvh * P.ppk + su.pp;
-        const int kph = p / P.pg;
-        const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
-        int64_t e0;
-        int n;
-        if (P.dense) {
-            e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(j, P.S);
-            n = P.S - j * kBlock;
-        } else {
-            e0 = P.row_ptr[bp * P.NB + j];
-            n = P.row_ptr[bp * P.NB + j + 1] - static_cast<int>(e0);
-        }
-        const int chunk0 = su.chunk0;
-        const int chunk1 = min((n + kBlock - 1) / kBlock, chunk0 + kChunksPerSubUnit);
-        if (chunk1 <= chunk0) continue;   // this sub-unit lies beyond the end of the row
-        if (tid == 0) {
-            mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-            tma_load_tile(tile_k, &tmap_k, j * kBlock, kvh, b, bar_kv);
-            tma_load_tile(tile_v, &tmap_v, j * kBlock, kvh, b, bar_kv);
-        }
-        const int ntiles = (chunk1 - chunk0) * hpc;
-        const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
-        const __nv_bfloat16* do_b = P.dout + static_cast<int64_t>(b) * P.do_sb;
-        const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
-        const __nv_bfloat16* kp_blk = P.kp + static_cast<int64_t>(b) * P.kp_sb + static_cast<int64_t>(kph) * P.kp_sh +
-                                      static_cast<int64_t>(j) * kBlock * P.kp_ss;
+    uint32_t gt = 0;     // tiles seen so far by this CTA (every role counts the same sequence)
+    uint32_t pt = 0;     // proxy tiles seen so far
+    uint32_t nsub = 0;   // sub-units seen so far
+    float kl_acc = 0.f;  // compute groups: this thread's share of sum t * (log2 t - log2 p_proxy)
 
-        auto stage_rows = [&](int chunk, int rb) {
-            if (tid < kBlock) {
-                const int at = chunk * kBlock + tid;
-                int qid = -1;
-                if (at < n) {
-                    qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
-                    if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
-                        atomicMax(P.status, kStatusBadIndex);
-                        qid = -1;
+    // Next sub-unit of the common sequence (false: no more work, or the CTA is giving up).  The gather warp draws the
+    // work and publishes the decoded sub-unit; it passes over sub-units that lie beyond the end of their row, so
+    // every published entry has work (or is the end marker).  The roles are at most a few tiles apart, fewer than the
+    // ring has entries.
+    auto next_unit = [&](uint32_t draw, BwdUnit& ud) -> bool {
+        const uint32_t uslot = draw & (kBwdUnitRing - 1);
+        if (warp == 12 && lane == 0) {
+            BwdUnit nu;
+            nu.chunk1 = -1;
+            for (;;) {
+                const int64_t u = atomicAdd(P.counter, 1);
+                if (u >= P.n_subunits) break;
+                const SubUnit su = decode_subunit(u, P.NB, P.ppk);
+                const int g = P.g_begin + su.g;
+                const int b = g / P.Hkv, kvh = g % P.Hkv, p = kvh * P.ppk + su.pp;
+                const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
+                int64_t e0;
+                int n;
+                if (P.dense) {
+                    e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(su.j, P.S);
+                    n = P.S - su.j * kBlock;
+                } else {
+                    e0 = P.row_ptr[bp * P.NB + su.j];
+                    n = P.row_ptr[bp * P.NB + su.j + 1] - static_cast<int>(e0);
+                }
+                if (su.chunk0 * kBlock < n) {
+                    nu.j = su.j; nu.b = b; nu.kvh = kvh; nu.p = p; nu.n = n; nu.e0 = e0;
+                    nu.chunk0 = su.chunk0;
+                    nu.chunk1 = min((n + kBlock - 1) / kBlock, su.chunk0 + kChunksPerSubUnit);
+                    break;
+                }
+            }
+            sm->units[uslot] = nu;
+            mbar_arrive(BAR(sm->unit_full[uslot]));
+        }
+        wait(BAR(sm->unit_full[uslot]), (draw / kBwdUnitRing) & 1, 7);
+        if (warp >= 8 && warp < 12) bad = group_or(1, bad);
+        if (bad) return false;
+        ud = sm->units[uslot];
+        return ud.chunk1 >= 0;
+    };
+    // query position of row `at` of a reverse-index row, -1 when there is none (or the index is bad)
+    auto row_qid = [&](const BwdUnit& ud, int at) -> int {
+        if (at >= ud.n) return -1;
+        const int q = P.dense ? (ud.j * kBlock + at) : P.col_q[ud.e0 + at];
+        if (static_cast<unsigned>(q) >= static_cast<unsigned>(P.S) || (q >> 7) < ud.j) {
+            atomicMax(P.status, kStatusBadIndex);
+            return -1;
+        }
+        return q;
+    };
+
+    // Every role has its own loop over the common sequence of sub-units (separate loops keep the register
+    // allocation of one role from being charged with the live values of the others).
+    if (warp >= 12) {
+        if (warp == 14) {
+            // =========================== MMA issue ===========================
+            BwdUnit ud;
+            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+                const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
+                wait(BAR(sm->k_full), nsub & 1, 6);
+                wait(BAR(sm->v_full), nsub & 1, 6);
+                // S^T and dP^T of tile g (running index), whose predecessor was tile g-1
+                auto issue_front = [&](uint32_t g, bool proxy, bool prev_proxy) {
+                    const uint32_t s = g & 1, ph = (g >> 1) & 1;
+                    const uint32_t tq = tile_q0 + s * kTileBytes, tdo = tile_do0 + s * kTileBytes;
+                    wait(BAR(sm->do_full[s]), ph, 1);
+                    if (!proxy) {
+                        if (g >= 1 && prev_proxy) wait(BAR(sm->r1_free), (pt - 1) & 1, 4);   // dKp has been read out of R1
+                        tc_fence_after_sync();
+                        if (!bad) umma_tile_128<false, false>(r1, tile_v, tdo, false, elect);   // dP^T = V_j dO_g^T
+                    }
+                    wait(BAR(sm->q_full[s]), ph, 2);
+                    if (g >= 1) wait(BAR(sm->r0_free), (g - 1) & 1, 3);                       // dQ / dQp has been read out of R0
+                    tc_fence_after_sync();
+                    if (!bad) {
+                        umma_tile_128<false, false>(r0, proxy ? tdo : tile_k, tq, false, elect);   // S^T = K_j Q_g^T  (Sp^T = Kp_j Qp_g^T)
+                        umma_commit(BAR(sm->sdp_full), elect);
+                    }
+                };
+                issue_front(gt, false, P.with_kl != 0);   // (a sub-unit ends with a proxy tile when there are any)
+                int hh = 0;
+                for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
+                    const bool is_proxy = hh == P.mpp;
+                    const uint32_t s = gt & 1;
+                    const uint32_t tq = tile_q0 + s * kTileBytes, tdo = tile_do0 + s * kTileBytes;
+                    int hh1 = hh + 1;
+                    if (hh1 == hpc) hh1 = 0;
+                    wait(BAR(sm->pds_full), gt & 1, 5);
+                    tc_fence_after_sync();
+                    if (!is_proxy) {
+                        if (t == 0 && nsub > 0) wait(BAR(sm->acc_free), (nsub - 1) & 1, 6);   // dV, dK of the previous sub-unit flushed
+                        if (!bad) {
+                            umma_tile_128_ts<true>(r2, r0, r0 + 64, tdo, t != 0, elect);    // dV += P^T dO_g
+                            umma_commit(BAR(sm->do_empty[s]), elect);
+                            umma_tile_128_ts<true>(r3, r1, r1 + 64, tq, t != 0, elect);     // dK += dS^T Q_g
+                            umma_commit(BAR(sm->q_empty[s]), elect);
+                            umma_tile_128<true, true>(r0, tile_ds, tile_k, false, elect);   // dQ = dS K_j
+                            umma_commit(BAR(sm->dq_full), elect);
+                        }
+                    } else {
+                        if (!bad) {
+                            umma_tile_128_ts<true>(r1, r0, r0 + 64, tq, false, elect);      // dKp = dSp^T Qp_g
+                            umma_commit(BAR(sm->dkp_full), elect);
+                        }
+                        wait(BAR(sm->dkp_full), pt & 1, 4);   // dSp^T in R0 has been consumed before dQp overwrites it
+                        tc_fence_after_sync();
+                        if (!bad) {
+                            umma_tile_128<true, true>(r0, tile_ds, tdo, false, elect);      // dQp = dSp Kp_j
+                            umma_commit(BAR(sm->dq_full), elect);
+                            umma_commit(BAR(sm->q_empty[s]), elect);
+                            umma_commit(BAR(sm->do_empty[s]), elect);
+                        }
+                        ++pt;
+                    }
+                    if (t + 1 < ntiles) issue_front(gt + 1, hh1 == P.mpp, is_proxy);
+                    hh = hh1;
+                }
+                if (!bad) {
+                    umma_commit(BAR(sm->kv_empty), elect);
+                    umma_commit(BAR(sm->acc_full), elect);
+                }
+            }
+        } else if (warp == 13) {
+            // =========================== K / V loads, row statistics ===========================
+            BwdUnit ud;
+            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+                const int64_t bp = static_cast<int64_t>(ud.b) * P.Hp + ud.p;
+                if (nsub > 0) wait(BAR(sm->kv_empty), (nsub - 1) & 1, 1);
+                if (!bad && lane == 0) {
+                    mbar_arrive_expect_tx(BAR(sm->k_full), kTileBytes);
+                    tma_load_tile(tile_k, &tmap_k, ud.j * kBlock, ud.kvh, ud.b, BAR(sm->k_full));
+                    mbar_arrive_expect_tx(BAR(sm->v_full), kTileBytes);
+                    tma_load_tile(tile_v, &tmap_v, ud.j * kBlock, ud.kvh, ud.b, BAR(sm->v_full));
+                }
+                __syncwarp();
+                for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
+                    int qid[4];
+                    uint32_t lim4 = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        qid[i] = row_qid(ud, chunk * kBlock + 4 * lane + i);
+                        const uint32_t lim = (qid[i] >= 0 && (qid[i] >> 7) == ud.j) ? static_cast<uint32_t>(qid[i] & 127) : 127u;
+                        lim4 |= lim << (8 * i);
+                    }
+                    for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
+                        const uint32_t s = gt & 1;
+                        const bool proxy = hh == P.mpp;
+                        float nl[4], dl[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            nl[i] = -INFINITY;
+                            dl[i] = 0.f;
+                            if (qid[i] >= 0) {
+                                if (proxy) {
+                                    nl[i] = -P.lse_proxy[bp * P.S + qid[i]] * kLog2e;
+                                } else {
+                                    const int64_t at = (static_cast<int64_t>(ud.b) * P.Hq + ud.p * P.mpp + hh) * P.S + qid[i];
+                                    nl[i] = -P.lse[at] * kLog2e;
+                                    dl[i] = -P.delta[at];
+                                }
+                            }
+                        }
+                        if (gt >= 2) wait(BAR(sm->st_empty[s]), ((gt >> 1) - 1) & 1, 2);
+                        if (bad) break;
+                        BwdRowStats* st = &sm->stats[s];
+                        reinterpret_cast<float4*>(st->neg_lse)[lane] = make_float4(nl[0], nl[1], nl[2], nl[3]);
+                        reinterpret_cast<float4*>(st->neg_delta)[lane] = make_float4(dl[0], dl[1], dl[2], dl[3]);
+                        reinterpret_cast<uint32_t*>(st->limit)[lane] = lim4;
+                        warp_arrive(BAR(sm->st_full[s]));
                     }
                 }
-                sm->rows[rb][tid] = qid;
             }
-        };
-        // Q rows of a tile (main head hh or the proxy head) into Q buffer `par` (workers only)
-        auto gather_q = [&](int hh, int rb, int par) {
-            const uint32_t dst = tile_q0 + par * kTileBytes;
-            if (hh < P.mpp)
-                gather_tile_512(dst, q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh, P.q_ss, sm->rows[rb], glane);
-            else
-                gather_tile_512(dst, qp_bp, P.qp_ss, sm->rows[rb], glane);
-        };
-        // dO rows of a main tile, or the proxy keys Kp_j of a proxy tile, into the dO buffer
-        auto gather_do = [&](int hh, int rb) {
-            if (hh < P.mpp)
-                gather_tile_512(tile_do, do_b + static_cast<int64_t>(p * P.mpp + hh) * P.do_sh, P.do_ss, sm->rows[rb], glane);
-            else
-                load_tile_512(tile_do, kp_blk, P.kp_ss, glane);
-        };
-
-        // ---- prologue: operands of tile 0, S of tile 0 ----
-        stage_rows(chunk0, 0);
-        if (ntiles > 1 && hpc == 1) stage_rows(chunk0 + 1, 1);
-        __syncthreads();
-        if (worker) {
-            gather_q(0, 0, 0);
-            gather_do(0, 0);
-            cp_async_commit();
-            cp_async_wait<0>();
-            fence_async_smem();
-        }
-        __syncthreads();
-        if (issuer) {
-            if (!bad) bad = !mbar_wait(bar_kv, ph_kv);
-            tc_fence_after_sync();
-            umma_tile_128<false, false>(t_s, tile_q0, tile_k, false, elect);   // S(0); tile 0 is always a main head
-        }
-        ph_kv ^= 1;
-        bool s_issued = true;
-        bool kv_acc = false;       // dK/dV accumulators hold something
-        bool dk_pending = false;   // bar_dk of the previous tile has not been waited for yet
-
-        // sum over the main heads of P for this thread's 32 columns: the KL teacher.  Kept as packed
-        // fp16 pairs (values in [0,1], at most Hq/Hp addends; the result is rounded to bf16 anyway).
-        __half2 teacher[16];
+        } else if (warp == 12) {
+            // =========================== row gather ===========================
+            // Lane l fetches rows 4l .. 4l+3 of every tile: one gather4 per 64-column panel and tensor.
+            BwdUnit ud;
+            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+                const int64_t q_base = static_cast<int64_t>(ud.b) * P.q_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.q_row_h;
+                const int64_t do_base = static_cast<int64_t>(ud.b) * P.do_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.do_row_h;
+                const int64_t qp_base = static_cast<int64_t>(ud.b) * P.qp_row_b + static_cast<int64_t>(ud.p) * P.qp_row_h;
+                for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
+                    int qid[4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) teacher[i] = __floats2half2_rn(0.f, 0.f);
-
-        int hh = 0, chunk = chunk0, rb = 0;   // head, chunk and row-list buffer of the current tile
-        for (int t = 0; t < ntiles; ++t) {
-            const bool is_proxy = hh == P.mpp;
-            const bool has_next = t + 1 < ntiles;
-            // the next two tiles, without divisions
-            int hh1 = hh + 1, chunk_1 = chunk, rb1 = rb;
-            if (hh1 == hpc) {
-                hh1 = 0;
-                ++chunk_1;
-                rb1 = (rb == 2) ? 0 : rb + 1;
-            }
-            int hh2 = hh1 + 1, chunk_2 = chunk_1, rb2 = rb1;
-            if (hh2 == hpc) {
-                hh2 = 0;
-                ++chunk_2;
-                rb2 = (rb1 == 2) ? 0 : rb1 + 1;
-            }
-            const bool next_proxy = has_next && (hh1 == P.mpp);
-            const uint32_t qbuf = tile_q0 + (t & 1) * kTileBytes;
-            const int nrows = min(kBlock, n - chunk * kBlock);
-            const int64_t slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
-
-            // ---- A: issuer: S (unless issued ahead) and dP;  workers: fetch the next tile's Q rows ----
-            if (issuer) {
-                tc_fence_after_sync();
-                if (is_proxy) {
-                    umma_tile_128<false, false>(t_s, qbuf, tile_do, false, elect);              // Sp = Qp_g Kp_j^T
-                } else {
-                    if (!s_issued) umma_tile_128<false, false>(t_s, qbuf, tile_k, false, elect);   // S  = Q_g K_j^T
-                    umma_tile_128<false, false>(t_dp, tile_do, tile_v, false, elect);           // dP = dO_g V_j^T
-                }
-                umma_commit(bar_a, elect);
-            }
-            if (worker) {
-                // per-row statistics: only the loads are issued here; they are consumed after the waits below
-                float raw_lse = INFINITY, row_delta = 0.f;   // +inf: exp2(-inf) = 0, a dead row contributes nothing
-                int limit = 127;
-                {
-                    const int qid = sm->rows[rb][row];
-                    if (qid >= 0) {
-                        if ((qid >> 7) == j) limit = qid & 127;
-                        if (is_proxy) {
-                            raw_lse = P.lse_proxy[bp * P.S + qid];
+                    for (int i = 0; i < 4; ++i) qid[i] = row_qid(ud, chunk * kBlock + 4 * lane + i);
+                    for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
+                        const uint32_t s = gt & 1, ph = (gt >> 1) & 1;
+                        const bool proxy = hh == P.mpp;
+                        const uint32_t qf = BAR(sm->q_full[s]), df = BAR(sm->do_full[s]);
+                        const uint32_t tq = tile_q0 + s * kTileBytes + lane * 512, tdo = tile_do0 + s * kTileBytes;
+                        int r[4];
+                        // dO rows first (dP^T is issued before S^T); for a proxy tile the proxy keys of the block
+                        if (gt >= 2) wait(BAR(sm->do_empty[s]), ph ^ 1, 1);
+                        if (bad) break;
+                        if (lane == 0) mbar_arrive_expect_tx(df, kTileBytes);
+                        __syncwarp();
+                        if (proxy) {
+                            if (lane == 0) tma_load_tile(tdo, &tmap_kp, ud.j * kBlock, ud.p / P.pg, ud.b, df);
                         } else {
-                            const int64_t at = (static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + qid;
-                            raw_lse = P.lse[at];
-                            row_delta = P.delta[at];
+                            const int64_t base = do_base + static_cast<int64_t>(hh) * P.do_row_h;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                r[i] = qid[i] >= 0 ? static_cast<int>(base + qid[i] * P.do_row_s) : P.do_rows_total;
+                            tma_gather4(tdo + lane * 512, &tmap_do, 0, r[0], r[1], r[2], r[3], df);
+                            tma_gather4(tdo + lane * 512 + kPanelBytes, &tmap_do, 64, r[0], r[1], r[2], r[3], df);
+                        }
+                        if (gt >= 2) wait(BAR(sm->q_empty[s]), ph ^ 1, 2);
+                        if (bad) break;
+                        if (lane == 0) mbar_arrive_expect_tx(qf, kTileBytes);
+                        __syncwarp();
+                        if (proxy) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                r[i] = qid[i] >= 0 ? static_cast<int>(qp_base + qid[i] * P.qp_row_s) : P.qp_rows_total;
+                            tma_gather4(tq, &tmap_qp, 0, r[0], r[1], r[2], r[3], qf);
+                            tma_gather4(tq + kPanelBytes, &tmap_qp, 64, r[0], r[1], r[2], r[3], qf);
+                        } else {
+                            const int64_t base = q_base + static_cast<int64_t>(hh) * P.q_row_h;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                r[i] = qid[i] >= 0 ? static_cast<int>(base + qid[i] * P.q_row_s) : P.q_rows_total;
+                            tma_gather4(tq, &tmap_q, 0, r[0], r[1], r[2], r[3], qf);
+                            tma_gather4(tq + kPanelBytes, &tmap_q, 64, r[0], r[1], r[2], r[3], qf);
                         }
                     }
                 }
-                if (dk_pending) {          // dK^T of the previous tile still reads the other Q buffer
-                    if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
-                    ph_dk ^= 1;
-                }
-                if (has_next) gather_q(hh1, rb1, (t + 1) & 1);
-                cp_async_commit();
-                if (!bad) bad = !mbar_wait(bar_a, ph_a);
-                ph_a ^= 1;
-                tc_fence_after_sync();
-                if (t + 2 < ntiles && chunk_2 != chunk_1) stage_rows(chunk_2, rb2);
-
-                // ---- B: P, dS (or dSp) for this thread's (row, 32 columns) ----
-                // Only the first chunk of a reverse-index row can hold rows of the key block itself
-                // (they are the smallest query positions), so only there the causal mask is needed.
-                const bool masked = (chunk == 0);
-                const float neg_lse = -raw_lse * kLog2e;
-                const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e), nl2 = f2_pack(neg_lse, neg_lse);
-                const uint64_t nd2 = f2_pack(-row_delta, -row_delta);
+            }
+        }
+    } else if (warp >= 8) {
+        // =========================== output group ===========================
+        const int otid = tid - 8 * 32;
+        // Reads accumulator `acc` (lane = key row of the block) and adds it to the fp32 rows starting at `dst`.
+        auto flush_rows = [&](uint32_t acc, float* dst) {
+            float* drow = dst + static_cast<int64_t>(row) * kHeadDim;
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_addr(acc, quarter, c), v);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; c += 16) {
-                    uint32_t sv[16], dv[16];
-                    tmem_ld16(tmem_addr(t_s, quarter, c0 + c), sv);
-                    if (!is_proxy) tmem_ld16(tmem_addr(t_dp, quarter, c0 + c), dv);
+                for (int i = 0; i < 32; i += 4)
+                    red_add_v4(drow + c + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                               __uint_as_float(v[i + 3]));
+            }
+        };
+        BwdUnit ud;
+        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
+            const int64_t slot_base = ud.e0 - edge_base;
+            const int kph = ud.p / P.pg;
+            int hh = 0, chunk = ud.chunk0;
+            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
+                const bool is_proxy = hh == P.mpp;
+                const int nrows = min(kBlock, ud.n - chunk * kBlock);
+                const int64_t slot0 = slot_base + static_cast<int64_t>(chunk) * kBlock;
+                const bool full = nrows == kBlock;
+                if (is_proxy) {
+                    wait(BAR(sm->dkp_full), pt & 1, 1);
+                    if (!bad) {
+                        tc_fence_after_sync();
+                        flush_rows(r1, P.dkp_acc + ((static_cast<int64_t>(ud.b) * P.Hpkv + kph) * P.S + ud.j * kBlock) * kHeadDim);
+                        tc_fence_before_sync();
+                        warp_arrive(BAR(sm->r1_free));
+                    }
+                    ++pt;
+                }
+                wait(BAR(sm->dq_full), gt & 1, 2);
+                bad = group_or(1, bad);
+                if (bad) break;
+                tc_fence_after_sync();
+                __nv_bfloat16* grow = is_proxy ? P.dqp_part + (slot0 + row) * kHeadDim
+                                               : P.dq_part + ((slot0 + row) * P.mpp + hh) * kHeadDim;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_addr(r0, quarter, c), v);
                     tmem_ld_wait();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    if (full) {
+                        // the dS^T tile is free (dQ has been computed): it stages the rows for one TMA tile store
+#pragma unroll
+                        for (int k8 = 0; k8 < 4; ++k8)
+                            st_shared_v4(tile_ds + swz_offset(row, (c >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2],
+                                         pk[4 * k8 + 3]);
+                    } else if (row < nrows) {
+#pragma unroll
+                        for (int k8 = 0; k8 < 4; ++k8)
+                            *reinterpret_cast<uint4*>(grow + c + 8 * k8) =
+                                make_uint4(pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
+                    }
+                }
+                tc_fence_before_sync();
+                warp_arrive(BAR(sm->r0_free));
+                if (full) {
+                    fence_async_smem();
+                    named_barrier_sync(1, 128);
+                    if (otid == 0) {
+                        const void* tm = is_proxy ? static_cast<const void*>(&tmap_dqp) : static_cast<const void*>(&tmap_dq);
+                        tma_store_3d(tm, tile_ds, 0, is_proxy ? 0 : hh, static_cast<int>(slot0));
+                        tma_store_3d(tm, tile_ds + kPanelBytes, 64, is_proxy ? 0 : hh, static_cast<int>(slot0));
+                        tma_store_commit();
+                        tma_store_wait_read();
+                    }
+                }
+                if (otid == 0) mbar_arrive(BAR(sm->ds_free));
+                if (++hh == hpc) {
+                    hh = 0;
+                    ++chunk;
+                }
+            }
+            if (!bad) {
+                // sub-unit epilogue: add this sub-unit's share of dV_j and dK_j
+                wait(BAR(sm->acc_full), nsub & 1, 3);
+                if (!bad) {
+                    tc_fence_after_sync();
+                    const int64_t at = ((static_cast<int64_t>(ud.b) * P.Hkv + ud.kvh) * P.S + ud.j * kBlock) * kHeadDim;
+                    flush_rows(r2, P.dv_acc + at);
+                    flush_rows(r3, P.dk_acc + at);
+                    tc_fence_before_sync();
+                    warp_arrive(BAR(sm->acc_free));
+                }
+            }
+        }
+        if (otid == 0) tma_store_wait_all();
+    } else {
+        // =========================== compute groups ===========================
+        // Thread = (key `row`, the 64 queries of its group).  Reads S^T and dP^T, writes P^T and dS^T back into
+        // TMEM over them (bf16) and dS^T into the shared tile that feeds dQ = dS K.
+        const int hf = warp >> 2;          // which half of the queries
+        const int cbase = hf * 64;
+        const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e);
+        const float inv_mpp = 1.f / static_cast<float>(P.mpp);
+        // sum over the main heads of P for this thread's 64 queries: the KL teacher, as packed fp16 pairs
+        // (values in [0,1], at most Hq/Hp addends; the result is rounded to bf16 anyway)
+        __half2 teacher[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) teacher[i] = __floats2half2_rn(0.f, 0.f);
+        BwdUnit ud;
+        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
+            int hh = 0, chunk = ud.chunk0;
+            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
+                const bool is_proxy = hh == P.mpp;
+                const uint32_t s = gt & 1;
+                wait(BAR(sm->st_full[s]), (gt >> 1) & 1, 1);
+                if (gt >= 1) wait(BAR(sm->ds_free), (gt - 1) & 1, 2);
+                wait(BAR(sm->sdp_full), gt & 1, 3);
+                if (bad) break;
+                tc_fence_after_sync();
+                const BwdRowStats* st = &sm->stats[s];
+                // only the first chunk of a reverse-index row can hold rows of the key block itself
+                const bool masked = (chunk == 0);
+#pragma unroll
+                for (int c = 0; c < 64; c += 16) {
+                    uint32_t sv[16], dv[16];
+                    tmem_ld16(tmem_addr(r0, quarter, cbase + c), sv);
+                    if (!is_proxy) tmem_ld16(tmem_addr(r1, quarter, cbase + c), dv);
+                    tmem_ld_wait();
+                    uint32_t lim[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+                    if (masked) {
+                        const uint4 l4 = *reinterpret_cast<const uint4*>(&st->limit[cbase + c]);
+                        lim[0] = l4.x; lim[1] = l4.y; lim[2] = l4.z; lim[3] = l4.w;
+                    }
                     uint32_t pk[8], dk[8];
 #pragma unroll
                     for (int i = 0; i < 16; i += 2) {
                         float a0, a1;   // log2 of the probability
+                        const uint64_t nl2 = *reinterpret_cast<const uint64_t*>(&st->neg_lse[cbase + c + i]);
                         f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl2), a0, a1);
                         float p0 = fast_exp2(a0);
                         float p1 = fast_exp2(a1);
                         if (masked) {
-                            p0 = (c0 + c + i <= limit) ? p0 : 0.f;
-                            p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
+                            const int l0 = static_cast<int>((lim[i >> 2] >> (8 * (i & 3))) & 0xffu);
+                            const int l1 = static_cast<int>((lim[i >> 2] >> (8 * ((i + 1) & 3))) & 0xffu);
+                            p0 = (row <= l0) ? p0 : 0.f;
+                            p1 = (row <= l1) ? p1 : 0.f;
                         }
+                        const int ti = (c + i) >> 1;
                         if (!is_proxy) {
-                            const uint64_t pp = f2_pack(p0, p1);
                             float d0, d1;   // dS = P o (dP - delta)
-                            f2_unpack(f2_mul(pp, f2_add(f2_pack(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), nd2)), d0, d1);
+                            const uint64_t nd2 = *reinterpret_cast<const uint64_t*>(&st->neg_delta[cbase + c + i]);
+                            f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), nd2)),
+                                      d0, d1);
                             pk[i >> 1] = pack_bf16(p0, p1);
                             dk[i >> 1] = pack_bf16(d0, d1);
-                            teacher[(c + i) >> 1] = __hadd2(teacher[(c + i) >> 1], __floats2half2_rn(p0, p1));
+                            if (P.with_kl) teacher[ti] = __hadd2(teacher[ti], __floats2half2_rn(p0, p1));
                         } else {
-                            const float2 tt = __half22float2(teacher[(c + i) >> 1]);
+                            const float2 tt = __half22float2(teacher[ti]);
                             const float t0 = tt.x * inv_mpp, t1 = tt.y * inv_mpp;
                             dk[i >> 1] = pack_bf16(p0 - t0, p1 - t1);
                             if (P.kl_value) {   // KL(teacher || proxy) = sum t (ln t - ln p); t = 0 contributes nothing
                                 kl_acc += (t0 > 0.f) ? t0 * (fast_log2(t0) - a0) : 0.f;
                                 kl_acc += (t1 > 0.f) ? t1 * (fast_log2(t1) - a1) : 0.f;
                             }
-                            teacher[(c + i) >> 1] = __floats2half2_rn(0.f, 0.f);
+                            teacher[ti] = __floats2half2_rn(0.f, 0.f);
                         }
                     }
-#pragma unroll
-                    for (int k8 = 0; k8 < 2; ++k8) {
-                        const uint32_t off = swz_offset(row, ((c0 + c) >> 3) + k8);
-                        if (!is_proxy) st_shared_v4(tile_p + off, pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
-                        st_shared_v4(tile_ds + off, dk[4 * k8], dk[4 * k8 + 1], dk[4 * k8 + 2], dk[4 * k8 + 3]);
+                    // bf16 operands back into TMEM over the columns this thread has consumed: two queries per column
+                    if (!is_proxy) {
+                        tmem_st8(tmem_addr(r0, quarter, cbase + (c >> 1)), pk);
+                        tmem_st8(tmem_addr(r1, quarter, cbase + (c >> 1)), dk);
+                    } else {
+                        tmem_st8(tmem_addr(r0, quarter, cbase + (c >> 1)), dk);
                     }
+                    // dS^T tile in shared memory: row = key, columns = queries
+                    st_shared_v4(tile_ds + swz_offset(row, (cbase + c) >> 3), dk[0], dk[1], dk[2], dk[3]);
+                    st_shared_v4(tile_ds + swz_offset(row, ((cbase + c) >> 3) + 1), dk[4], dk[5], dk[6], dk[7]);
                 }
-                cp_async_wait<0>();      // Q rows of the next tile have landed
+                tmem_st_wait();
                 fence_async_smem();
                 tc_fence_before_sync();
-            }
-            __syncthreads();
-
-            // ---- C: issuer: dV^T (frees the dO and P buffers), dQ^T, dK^T, S of the next main tile ----
-            const bool s_ahead = has_next && !next_proxy && !is_proxy;
-            if (issuer) {
-                tc_fence_after_sync();
-                if (is_proxy) {
-                    umma_tile_128<true, false>(t_dp, tile_do, tile_ds, false, elect);   // dQp^T = Kp_j^T dSp^T
-                    umma_commit(bar_dq, elect);
-                    umma_commit(bar_dv, elect);
-                    umma_tile_128<true, true>(t_s, qbuf, tile_ds, false, elect);        // dKp^T = Qp_g^T dSp
-                    umma_commit(bar_dk, elect);
-                } else {
-                    umma_tile_128<true, true>(t_dv, tile_do, tile_p, kv_acc, elect);    // dV^T += dO_g^T P  (frees dO and P)
-                    umma_commit(bar_dv, elect);
-                    umma_tile_128<true, false>(t_dp, tile_k, tile_ds, false, elect);    // dQ^T  = K_j^T dS^T
-                    umma_commit(bar_dq, elect);
-                    umma_tile_128<true, true>(t_dk, qbuf, tile_ds, kv_acc, elect);      // dK^T += Q_g^T dS
-                    umma_commit(bar_dk, elect);
-                    if (s_ahead) umma_tile_128<false, false>(t_s, tile_q0 + ((t + 1) & 1) * kTileBytes, tile_k, false, elect);
+                warp_arrive(BAR(sm->pds_full));
+                warp_arrive(BAR(sm->st_empty[s]));
+                if (++hh == hpc) {
+                    hh = 0;
+                    ++chunk;
                 }
             }
-            if (!is_proxy) kv_acc = true;
-            s_issued = s_ahead;
-            dk_pending = true;
-
-            // ---- D: workers: refill the dO buffer, write dQ^T out, reduce dKp^T ----
-            if (worker) {
-                if (!bad) bad = !mbar_wait(bar_dv, ph_dv);
-                ph_dv ^= 1;
-                if (has_next) gather_do(hh1, rb1);
-                cp_async_commit();
-                if (!bad) bad = !mbar_wait(bar_dq, ph_dq);
-                ph_dq ^= 1;
-                tc_fence_after_sync();
-                {
-                    // This thread holds head-dimension index `row` of the output rows c0 .. c0+31 (the
-                    // factor scale, or scale/(B*Hp*S) for the proxy, is applied by the combine kernel).
-                    // A full chunk is transposed through the P buffer (free since dV^T) into dense
-                    // [row][d] order and leaves with ONE TMA tile store; the partial last chunk of a
-                    // reverse-index row is written directly.
-                    const bool full = (nrows == kBlock);
-                    __nv_bfloat16* dst = is_proxy ? P.dqp_part + (slot0 + c0) * kHeadDim + row
-                                                  : P.dq_part + ((slot0 + c0) * P.mpp + hh) * kHeadDim + row;
-                    const int64_t rstride = is_proxy ? kHeadDim : static_cast<int64_t>(P.mpp) * kHeadDim;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 16) {
-                        uint32_t v[16];
-                        tmem_ld16(tmem_addr(t_dp, quarter, c0 + c), v);
-                        tmem_ld_wait();
-                        if (full) {
-                            const uint32_t sbase = tile_p + static_cast<uint32_t>((c0 + c) * 256 + row * 2);
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const __nv_bfloat16 hv = __float2bfloat16_rn(__uint_as_float(v[i]));
-                                asm volatile("st.shared.b16 [%0], %1;" ::"r"(sbase + i * 256), "h"(*reinterpret_cast<const uint16_t*>(&hv)) : "memory");
-                            }
-                        } else {
-                            store_transposed_bf16_16(dst + c * rstride, rstride, v, c0 + c, nrows);
-                        }
-                    }
-                    if (full) {
-                        fence_async_smem();
-                        named_barrier_sync(5, kBwdWorkers);
-                        if (tid == 0) {
-                            if (is_proxy) tma_store_3d(&tmap_dqp, tile_p, 0, 0, static_cast<int>(slot0));
-                            else tma_store_3d(&tmap_dq, tile_p, 0, hh, static_cast<int>(slot0));
-                            tma_store_commit();
-                        }
-                    }
-                }
-                if (is_proxy) {
-                    if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
-                    ph_dk ^= 1;
-                    tc_fence_after_sync();
-                    float* kbase = P.dkp_acc + ((static_cast<int64_t>(b) * P.Hpkv + kph) * P.S + j * kBlock + c0) * kHeadDim + row;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 16) {
-                        uint32_t v[16];
-                        tmem_ld16(tmem_addr(t_s, quarter, c0 + c), v);
-                        tmem_ld_wait();
-#pragma unroll
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) atomicAdd(kbase + (c + i) * kHeadDim, __uint_as_float(v[i]));
-                    }
-                }
-                cp_async_wait<0>();      // dO rows (or Kp_j) of the next tile have landed
-                if (tid == 0) tma_store_wait_read();   // the P buffer may be overwritten by the next tile
-                fence_async_smem();
-                tc_fence_before_sync();
-            }
-            if (is_proxy) dk_pending = false;
-            __syncthreads();
-            hh = hh1;
-            chunk = chunk_1;
-            rb = rb1;
         }
-        // ---- sub-unit epilogue: add this sub-unit's share of dK_j and dV_j ----
-        if (worker) {
-            if (dk_pending) {
-                if (!bad) bad = !mbar_wait(bar_dk, ph_dk);
-                ph_dk ^= 1;
-            }
-            tc_fence_after_sync();
-            // accumulators are transposed: lane = head-dimension index, column = key row of the block
-            const int64_t at = ((static_cast<int64_t>(b) * P.Hkv + kvh) * P.S + j * kBlock) * kHeadDim + row;
-#pragma unroll 1
-            for (int which = 0; which < 2; ++which) {
-                float* dst = (which == 0 ? P.dv_acc : P.dk_acc) + at;
-#pragma unroll
-                for (int c = 0; c < 32; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_addr(which == 0 ? t_dv : t_dk, quarter, c0 + c), v);
-                    tmem_ld_wait();
-                    if (kv_acc) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            atomicAdd(dst + static_cast<int64_t>(c0 + c + i) * kHeadDim, __uint_as_float(v[i]));
-                    }
-                }
-            }
-            tc_fence_before_sync();
-        }
-        __syncthreads();
     }
-    cp_async_wait<0>();
-    if (tid == 0) tma_store_wait_all();
-    if (P.kl_value && worker) {
+#ifdef FMSA_TRACE
+    if (blockIdx.x == 0 && lane == 0) {
+        trace_acc[0] = static_cast<unsigned long long>(clock64() - trace_t0);
+        for (int i = 0; i < 8; ++i) g_bwd_trace[warp][i] = trace_acc[i];
+    }
+#endif
+    if (P.kl_value && warp < 8) {
         for (int o = 16; o > 0; o >>= 1) kl_acc += __shfl_xor_sync(0xffffffffu, kl_acc, o);
         if (lane == 0) atomicAdd(P.kl_value, kl_acc * P.kl_value_scale);
     }
-    if (bad) atomicMax(P.status, kStatusWaitTimeout);
+    if (bad) {
+        atomicMax(P.status, kStatusWaitTimeout);
+        // Give loads and products that are still in flight time to finish before shared memory and TMEM are released.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000) __nanosleep(1000);
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -729,27 +913,32 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     }
     FMSA_REQUIRE(aligned16(dq_part) && aligned16(dk_acc) && aligned16(dv_acc) &&
                  (!with_kl || (aligned16(dqp_part) && aligned16(dkp_acc))));
-    CUtensorMap tk, tv, tdq, tdqp;
-    if (!make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
+    FMSA_REQUIRE(gather_compatible(q->ptr, q->stride_b, q->stride_h, q->stride_s));
+    FMSA_REQUIRE(gather_compatible(d_out->ptr, d_out->stride_b, d_out->stride_h, d_out->stride_s));
+    if (with_kl) FMSA_REQUIRE(gather_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
+    FMSA_REQUIRE(part_slots > 0 && part_slots < 0x7fffffffLL);
+    const fmsa_tensor* qpx = with_kl ? q_proxy : q;
+    const fmsa_tensor* kpx = with_kl ? k_proxy : k;
+    const int h_qpx = with_kl ? pb->Hp : pb->Hq, h_kpx = with_kl ? pb->Hpkv : pb->Hkv;
+    const uint64_t q_rows = gather_rows(pb->B, pb->Hq, pb->S, q->stride_b, q->stride_h, q->stride_s);
+    const uint64_t do_rows = gather_rows(pb->B, pb->Hq, pb->S, d_out->stride_b, d_out->stride_h, d_out->stride_s);
+    const uint64_t qp_rows = gather_rows(pb->B, h_qpx, pb->S, qpx->stride_b, qpx->stride_h, qpx->stride_s);
+    CUtensorMap tq, tdo, tqp, tk, tv, tkp, tdq, tdqp;
+    if (!make_tmap_gather(&tq, q->ptr, q_rows) || !make_tmap_gather(&tdo, d_out->ptr, do_rows) ||
+        !make_tmap_gather(&tqp, qpx->ptr, qp_rows) ||
+        !make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
         !make_tmap_bhsd(&tv, v->ptr, pb->B, pb->Hkv, pb->S, v->stride_b, v->stride_h, v->stride_s, 128) ||
-        !make_tmap_partials(&tdq, dq_part, part_slots, pb->Hq / pb->Hp) ||
-        !make_tmap_partials(&tdqp, with_kl ? dqp_part : dq_part, part_slots, 1))
+        !make_tmap_bhsd(&tkp, kpx->ptr, pb->B, h_kpx, pb->S, kpx->stride_b, kpx->stride_h, kpx->stride_s, 128) ||
+        !make_tmap_partials_swz(&tdq, dq_part, static_cast<uint64_t>(part_slots), static_cast<uint64_t>(pb->Hq / pb->Hp)) ||
+        !make_tmap_partials_swz(&tdqp, with_kl ? dqp_part : dq_part, static_cast<uint64_t>(part_slots), 1))
         return FMSA_ERR_CUDA;
 
     BwdParams P;
-    P.q = static_cast<const __nv_bfloat16*>(q->ptr);
-    P.q_sb = q->stride_b; P.q_sh = q->stride_h; P.q_ss = q->stride_s;
-    P.dout = static_cast<const __nv_bfloat16*>(d_out->ptr);
-    P.do_sb = d_out->stride_b; P.do_sh = d_out->stride_h; P.do_ss = d_out->stride_s;
-    if (with_kl) {
-        P.qp = static_cast<const __nv_bfloat16*>(q_proxy->ptr);
-        P.qp_sb = q_proxy->stride_b; P.qp_sh = q_proxy->stride_h; P.qp_ss = q_proxy->stride_s;
-        P.kp = static_cast<const __nv_bfloat16*>(k_proxy->ptr);
-        P.kp_sb = k_proxy->stride_b; P.kp_sh = k_proxy->stride_h; P.kp_ss = k_proxy->stride_s;
-    } else {
-        P.qp = P.q; P.qp_sb = P.qp_sh = P.qp_ss = 0;
-        P.kp = P.q; P.kp_sb = P.kp_sh = P.kp_ss = 0;
-    }
+    P.q_row_b = q->stride_b / 128; P.q_row_h = q->stride_h / 128; P.q_row_s = q->stride_s / 128;
+    P.do_row_b = d_out->stride_b / 128; P.do_row_h = d_out->stride_h / 128; P.do_row_s = d_out->stride_s / 128;
+    P.qp_row_b = qpx->stride_b / 128; P.qp_row_h = qpx->stride_h / 128; P.qp_row_s = qpx->stride_s / 128;
+    P.q_rows_total = static_cast<int32_t>(q_rows); P.do_rows_total = static_cast<int32_t>(do_rows);
+    P.qp_rows_total = static_cast<int32_t>(qp_rows);
     P.lse = lse; P.lse_proxy = lse_proxy; P.delta = delta;
     P.row_ptr = row_ptr; P.col_q = col_q;
     P.dq_part = static_cast<__nv_bfloat16*>(dq_part); P.dqp_part = static_cast<__nv_bfloat16*>(dqp_part);
@@ -759,23 +948,18 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.mpp = pb->Hq / pb->Hp; P.ppk = pb->Hp / pb->Hkv; P.pg = pb->Hp / pb->Hpkv;
     P.g_begin = g_begin; P.G = g_count;
     P.with_kl = with_kl ? 1 : 0; P.dense = dense ? 1 : 0;
-    P.scale = pb->scale; P.scale_log2e = pb->scale * kLog2e;
-    P.kl_out_scale = pb->scale / (static_cast<float>(pb->B) * pb->Hp * pb->S);
+    P.scale_log2e = pb->scale * kLog2e;
     P.kl_value = with_kl ? kl_value : nullptr;
     P.kl_value_scale = kLn2 / (static_cast<float>(pb->B) * pb->Hp * pb->S);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        return FMSA_ERR_CUDA;
-    if (cudaFuncSetAttribute(sparse_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdSmemBytes)) !=
-        cudaSuccess)
-        return FMSA_ERR_CUDA;
+    const int sms = device_sm_count();
+    if (sms <= 0 || !ensure_smem_attr(reinterpret_cast<const void*>(sparse_bwd_kernel), kBwdSmemBytes)) return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    sparse_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tk, tv, tdq, tdqp, P);
+    sparse_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
     return check_launch();
 }
 
@@ -814,3 +998,9 @@ extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_pa
         bwd_combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return check_launch();
 }
+
+#ifdef FMSA_TRACE
+extern "C" int fmsa_debug_bwd_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, fmsa::g_bwd_trace, sizeof(unsigned long long) * 16 * 8) == cudaSuccess ? 0 : -4;
+}
+#endif

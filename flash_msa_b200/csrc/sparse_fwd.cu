@@ -8,10 +8,11 @@
 // itself, which only needs its log-sum-exp.
 //
 // A tile (128 gathered rows of one head against the 128 keys of the block):
-//     S = Q_g K_j^T                tcgen05.mma, K-major x K-major, fp32 in TMEM
-//     m, P = exp2(S*c - m), l      one thread per row (TMEM lane), P rounded to bf16 into smem
-//     O_part = P V_j               tcgen05.mma, K-major x MN-major
-//     partial (O_part / l in bf16, lse = m + log l) is written to the edge's slot;
+//     S = Q_g K_j^T                tcgen05.mma, both operands in shared memory, fp32 in TMEM
+//     m, P = exp2(S*c - m), l      one thread per row (TMEM lane); P goes back into TMEM as bf16,
+//                                  over the columns S occupied
+//     O_part = P V_j               tcgen05.mma with P as the TMEM operand
+//     the partial (O_part unnormalised in bf16, row max m and row sum l) is written to the edge's slot;
 // a combine kernel merges the <= Kb partials of every query row (fmsa_sparse_fwd_combine).
 // This mirrors the numerics of the reference path, which merges bf16 partial outputs of
 // FlashAttention calls in fp32 (flash_msa/sparse_flash_varlen.py:169-244,
@@ -22,7 +23,8 @@
 // and the full-sequence proxy log-sum-exp (warmup/msa_backward_cutedsl_warmup.py:83-114).
 //
 // Scheduling: persistent CTAs (one per SM) take sub-units of reverse-index rows from a global counter;
-// inside a CTA the roles (softmax, gather, MMA issue) run decoupled, see sparse_fwd_kernel.
+// inside a CTA the roles (row gather, K/V loads, MMA issue, softmax x2, output) run decoupled and meet
+// only through mbarriers, see sparse_fwd_kernel.
 #include "host_common.h"
 #include "msa_common.cuh"
 #include "sm100.cuh"
@@ -31,11 +33,16 @@
 namespace fmsa {
 namespace {
 
+#ifdef FMSA_TRACE
+// Debug builds only: cycles each warp of CTA 0 spent inside its role (slot 0) and inside waits of kind 1..7.
+__device__ unsigned long long g_fwd_trace[16][8];
+#endif
+
 struct FwdParams {
-    const __nv_bfloat16* q;
-    int64_t q_sb, q_sh, q_ss;
-    const __nv_bfloat16* qp;
-    int64_t qp_sb, qp_sh, qp_ss;
+    // Row-gather views of q and q_proxy: element row (b, h, s) is matrix row b*row_b + h*row_h + s*row_s.
+    int64_t q_row_b, q_row_h, q_row_s;
+    int64_t qp_row_b, qp_row_h, qp_row_s;
+    int32_t q_rows_total, qp_rows_total;   // first row index outside the views (reads as zeros)
     const int32_t* row_ptr;
     const int32_t* col_q;
     __nv_bfloat16* o_part;   // [(edge - edge_base) * mpp + head][128]
@@ -50,77 +57,90 @@ struct FwdParams {
     float scale_log2e;
 };
 
-struct FwdSmem {
-    uint64_t bar_kv, bar_kp, bar_done;
-    uint64_t q_full[2];              // Q rows of a tile have landed (arrivals: the gather group)
-    uint64_t s_full[2], s_empty[2];  // S accumulator written by the tensor core / read by the softmax group
-    uint64_t p_full;                 // P written to shared memory (arrivals: the softmax group)
-    uint64_t o_full[2], o_empty[2];  // O accumulator written by the tensor core / read back by the softmax group
-    uint64_t unit_full[4];           // a sub-unit index has been published in unit_ring
-    int32_t unit_ring[4];
-    uint32_t tmem_slot;
-    int32_t rows[8][128];            // query positions of the chunks in flight (ring)
-    float rmax[4][128];              // row maxima of the four column groups
-    float lsum[4][128];              // row sums of the four column groups
+// A sub-unit as the drawing thread publishes it to the other roles.
+struct UnitDesc {
+    int32_t j, b, kvh, p, n, chunk0, chunk1, pad;   // chunk1 < 0: no more work
+    int64_t e0;                                      // position of the reverse-index row in col_q / the slot space
 };
 
-constexpr int kFwdSoftmax = 512;                              // 16 warps: thread = (tile row, 32 columns)
-constexpr int kFwdStore = 256;                                // 8 warps: row lists and cp.async gathers of the Q rows
-constexpr int kFwdThreads = kFwdSoftmax + kFwdStore + 32;     // + one warp that issues tcgen05.mma
-constexpr size_t kFwdSmemBytes = 6 * kTileBytes + 1024 + sizeof(FwdSmem);
+constexpr int kFwdQStages = 3;
+constexpr int kUnitRing = 16;
+constexpr int kLimitRing = 8;
 
-// Warp-specialised forward.  Three roles run decoupled and meet only through mbarriers:
-//   warps 0-15  softmax group : thread = (tile row, 32-column group); reads S from TMEM, writes P (bf16)
-//                               to shared memory and the per-row (max, sum) to global memory; while it
-//                               would wait for the next S it writes the finished O^T accumulator of the
-//                               previous tile out as unnormalised bf16 partial rows (thread = head-dimension
-//                               lane x 32 tile rows);
-//   warps 16-23 gather group  : draws the work, stages the row lists and gathers the Q rows two tiles
-//                               ahead (cp.async);
-//   warp 24     issuer        : loads K_j, V_j, Kp_j by TMA and issues S(t+1) = Q K^T, then
-//                               O^T(t) = V^T P^T(t), so the softmax of one tile overlaps the products of
-//                               its neighbours and the store of the tile before.  All its lanes run the
-//                               same code; only lane 0's tcgen05 instructions take effect (a lone
-//                               diverged lane is scheduled late).
-// Work is drawn from a global counter by one thread of the gather group and published to the other
-// roles through a four-entry ring, so every role walks the same sequence of sub-units.
-// TMEM: S[2] at columns 0 and 128, O^T[2] at 256 and 384.
-__global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
+struct FwdCtrl {
+    uint64_t k_full, k_empty, v_full, v_empty, kp_full, kp_empty;
+    uint64_t q_full[kFwdQStages], q_empty[kFwdQStages];
+    uint64_t s_full[2], p_full[2], s_free[2];
+    uint64_t o_full[2], o_empty[2];
+    uint64_t unit_full[kUnitRing];
+    UnitDesc units[kUnitRing];
+    uint8_t limits[kLimitRing][128];   // per chunk in flight: last visible key of each row (127 = all)
+    uint32_t tmem_slot;
+    int32_t abort_flag;
+};
+
+// Roles (warp index): 0-3 softmax group A (tiles with an even running index, S accumulator 0),
+// 4-7 softmax group B (odd tiles, S accumulator 1), 8-11 output group, 12 row gather, 13 K/V loads, 14 MMA issue.
+constexpr int kFwdThreads = 15 * 32;
+constexpr size_t kFwdTileBytes = static_cast<size_t>(3 + kFwdQStages + 1) * kTileBytes;   // K, V, Kp, Q stages, output staging
+constexpr size_t kFwdSmemBytes = kFwdTileBytes + 1024 + sizeof(FwdCtrl);
+static_assert(kFwdSmemBytes <= 232448, "shared memory budget of one CTA");
+
+// Warp-specialised forward.  Every role walks the same sequence of sub-units (published by the gather warp in a
+// ring) and, inside a sub-unit, the same sequence of tiles: for each chunk of 128 rows, the main heads of the proxy
+// head, then the proxy head.  Hand-offs (all mbarriers, one arrival per warp or per tcgen05.commit):
+//   gather warp   q_full[stage] (TMA bytes)  <- q_empty[stage] (commit after S)
+//   K/V warp      k_full/v_full/kp_full      <- k_empty/kp_empty (commit after the last S of a sub-unit), v_empty
+//   MMA warp      S(t+1) before P V(t); s_full[t&1], o_full[mt&1]; s_free[t&1] when tile t no longer needs its S columns
+//   softmax       p_full[t&1] when P is in TMEM (or, for a proxy tile, when S has been read)
+//   output group  o_empty[mt&1] when the O accumulator has been read
+// TMEM: S[2] at columns 0 and 128 (P overwrites the first 64 columns of its S), O[2] at 256 and 384.
+__global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                                    const __grid_constant__ CUtensorMap tmap_qp,
+                                                                    const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
                                                                     const __grid_constant__ CUtensorMap tmap_kp,
+                                                                    const __grid_constant__ CUtensorMap tmap_o,
                                                                     const FwdParams P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t tile_k = tiles, tile_v = tiles + kTileBytes, tile_kp = tiles + 2 * kTileBytes;
-    const uint32_t tile_q0 = tiles + 3 * kTileBytes, tile_p = tiles + 5 * kTileBytes;
-    FwdSmem* sm = reinterpret_cast<FwdSmem*>(smem_raw + (tiles - smem_u32(smem_raw)) + 6 * kTileBytes);
+    const uint32_t tile_q0 = tiles + 3 * kTileBytes, tile_o = tiles + (3 + kFwdQStages) * kTileBytes;
+    FwdCtrl* sm = reinterpret_cast<FwdCtrl*>(smem_raw + (tiles - smem_u32(smem_raw)) + kFwdTileBytes);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int role = warp < 16 ? 0 : (warp < 24 ? 1 : 2);   // 0 softmax group, 1 store group, 2 issuer
-    const int quarter = warp & 3;                            // TMEM lane quarter this warp may read
-    const int row = quarter * 32 + lane;                     // softmax: tile row; store: head-dimension index
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
+    const int quarter = warp & 3;              // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;       // softmax / output: tile row of this thread
     const uint32_t elect = (lane == 0) ? 1u : 0u;
-    const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_kp = smem_u32(&sm->bar_kp), bar_done = smem_u32(&sm->bar_done);
-    const uint32_t p_full = smem_u32(&sm->p_full);
-    auto B2 = [&](uint64_t* arr, uint32_t i) { return smem_u32(&arr[i & 1]); };
+    auto BAR = [&](uint64_t& b) { return smem_u32(&b); };
 
     if (tid == 0) {
-        mbar_init(bar_kv, 1);
-        mbar_init(bar_kp, 1);
-        mbar_init(bar_done, 1);
-        mbar_init(p_full, kFwdSoftmax / 32);   // one arrival per warp: hundreds of arrivals on one barrier serialise
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&sm->q_full[i]), kFwdStore / 32);
-            mbar_init(smem_u32(&sm->s_full[i]), 1);
-            mbar_init(smem_u32(&sm->s_empty[i]), kFwdSoftmax / 32);
-            mbar_init(smem_u32(&sm->o_full[i]), 1);
-            mbar_init(smem_u32(&sm->o_empty[i]), kFwdSoftmax / 32);
+        mbar_init(BAR(sm->k_full), 1);
+        mbar_init(BAR(sm->k_empty), 1);
+        mbar_init(BAR(sm->v_full), 1);
+        mbar_init(BAR(sm->v_empty), 1);
+        mbar_init(BAR(sm->kp_full), 1);
+        mbar_init(BAR(sm->kp_empty), 1);
+        for (int i = 0; i < kFwdQStages; ++i) {
+            mbar_init(BAR(sm->q_full[i]), 1);
+            mbar_init(BAR(sm->q_empty[i]), 1);
         }
-        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sm->unit_full[i]), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(sm->s_full[i]), 1);
+            mbar_init(BAR(sm->p_full[i]), 4);
+            mbar_init(BAR(sm->s_free[i]), 1);
+            mbar_init(BAR(sm->o_full[i]), 1);
+            mbar_init(BAR(sm->o_empty[i]), 4);
+        }
+        for (int i = 0; i < kUnitRing; ++i) mbar_init(BAR(sm->unit_full[i]), 1);
+        sm->abort_flag = 0;
         fence_mbar_init();
+        prefetch_tmap(&tmap_q);
+        prefetch_tmap(&tmap_qp);
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
         prefetch_tmap(&tmap_kp);
+        prefetch_tmap(&tmap_o);
     }
     if (warp == 0) {
         tmem_alloc(smem_u32(&sm->tmem_slot), 512);
@@ -136,309 +156,362 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     const int lse_stride = P.mpp + 1;
     const int64_t edge_base = P.dense ? dense_edge_base(static_cast<int64_t>(P.g_begin) * P.ppk, P.S, P.NB)
                                       : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
-    uint32_t gt = 0;    // tiles seen so far by this CTA (every role counts the same sequence)
-    uint32_t mt = 0;    // main-head tiles seen so far
-    uint32_t nsub = 0;  // sub-units with work seen so far
-    uint32_t cbase = 0; // chunks of the sub-units seen so far: row lists live in ring entry (cbase + chunk - chunk0) % 8,
-                        // so the lists of a new sub-unit never land on entries the softmax group still reads
-    bool bad = false;   // a bounded wait gave up: later waits are skipped, the status word is set at the end
-    auto wait = [&](uint32_t bar, uint32_t parity) {
-        if (!bad) bad = !mbar_wait(bar, parity);
+    volatile int* abort_flag = &sm->abort_flag;
+    bool bad = false;   // a bounded wait gave up (here or in another role): the thread stops taking work
+#ifdef FMSA_TRACE
+    unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long trace_t0 = clock64();
+#endif
+    auto wait = [&](uint32_t bar, uint32_t parity, int kind = 1) {   // every lane of the warp calls it; the verdict is warp-uniform
+#ifdef FMSA_TRACE
+        const long long w0 = clock64();
+#endif
+        if (!bad) bad = __any_sync(0xffffffffu, !mbar_wait_abortable(bar, parity, abort_flag));
+#ifdef FMSA_TRACE
+        trace_acc[kind & 7] += static_cast<unsigned long long>(clock64() - w0);
+#endif
+        (void)kind;
+    };
+    // block barrier of one 128-thread group that also ORs a flag: the roles that use named barriers must
+    // leave their loops together
+    auto group_or = [&](int id, bool flag) -> bool {
+        uint32_t r;
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.b32 q, %1, 0;\n"
+            "barrier.cta.red.or.pred p, %2, 128, q;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(r)
+            : "r"(flag ? 1u : 0u), "r"(id)
+            : "memory");
+        return r != 0;
     };
     auto warp_arrive = [&](uint32_t bar) {   // every lane has finished (and fenced) its part; one arrival per warp
         __syncwarp();
         if (lane == 0) mbar_arrive(bar);
     };
 
-    for (uint32_t draw = 0;; ++draw) {
-        // One thread draws the work and publishes it in a ring.  It passes over sub-units that lie
-        // beyond the end of their row, so every published entry has work (or is the end marker) and
-        // the drawing thread, whose own role needs the other roles' results to finish a sub-unit,
-        // cannot get more than three entries ahead of the slowest role: a ring of four is enough.
-        if (tid == kFwdSoftmax) {
-            int64_t u;
+    uint32_t gt = 0;     // tiles seen so far by this CTA (every role counts the same sequence)
+    uint32_t mt = 0;     // main-head tiles seen so far
+    uint32_t nsub = 0;   // sub-units seen so far
+    uint32_t cbase = 0;  // chunks of the sub-units seen so far: the row limits of chunk c of a sub-unit live in ring
+                         // entry (cbase + c - chunk0) % kLimitRing
+    uint32_t qs = 0, qph = 0;   // gather warp / MMA warp: Q stage of tile gt and the phase bit of its barriers
+
+    for (uint32_t draw = 0; !bad; ++draw) {
+        const uint32_t uslot = draw & (kUnitRing - 1);
+        // The gather warp draws the work and publishes the decoded sub-unit.  It passes over sub-units that lie beyond
+        // the end of their row, so every published entry has work (or is the end marker).  The roles are at most a
+        // handful of tiles apart (Q stages + S and O accumulators), far fewer than the ring has entries.
+        if (warp == 12 && lane == 0) {
+            UnitDesc ud;
+            ud.chunk1 = -1;
             for (;;) {
-                u = atomicAdd(P.counter, 1);
+                const int64_t u = atomicAdd(P.counter, 1);
                 if (u >= P.n_subunits) break;
                 const SubUnit su = decode_subunit(u, P.NB, P.ppk);
+                const int g = P.g_begin + su.g;
+                const int b = g / P.Hkv, kvh = g % P.Hkv, p = kvh * P.ppk + su.pp;
+                const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
+                int64_t e0;
                 int n;
                 if (P.dense) {
+                    e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(su.j, P.S);
                     n = P.S - su.j * kBlock;
                 } else {
-                    const int g = P.g_begin + su.g;
-                    const int64_t r = (static_cast<int64_t>(g / P.Hkv) * P.Hp + (g % P.Hkv) * P.ppk + su.pp) * P.NB + su.j;
-                    n = P.row_ptr[r + 1] - P.row_ptr[r];
+                    e0 = P.row_ptr[bp * P.NB + su.j];
+                    n = P.row_ptr[bp * P.NB + su.j + 1] - static_cast<int>(e0);
                 }
-                if (su.chunk0 * kBlock < n) break;
+                if (su.chunk0 * kBlock < n) {
+                    ud.j = su.j; ud.b = b; ud.kvh = kvh; ud.p = p; ud.n = n; ud.e0 = e0;
+                    ud.chunk0 = su.chunk0;
+                    ud.chunk1 = min((n + kBlock - 1) / kBlock, su.chunk0 + kChunksPerSubUnit);
+                    break;
+                }
             }
-            sm->unit_ring[draw & 3] = static_cast<int32_t>(u < P.n_subunits ? u : P.n_subunits);
-            mbar_arrive(smem_u32(&sm->unit_full[draw & 3]));
+            sm->units[uslot] = ud;
+            mbar_arrive(BAR(sm->unit_full[uslot]));
         }
-        wait(smem_u32(&sm->unit_full[draw & 3]), (draw >> 2) & 1);
-        const int64_t u = sm->unit_ring[draw & 3];
-        if (u >= P.n_subunits) break;
-        const SubUnit su = decode_subunit(u, P.NB, P.ppk);
-        const int j = su.j;
-        const int g = P.g_begin + su.g;
-        const int b = g / P.Hkv, kvh = g % P.Hkv;
-        const int p = kvh * P.ppk + su.pp;
-        const int64_t bp = static_cast<int64_t>(b) * P.Hp + p;
-        int64_t e0;
-        int n;
-        if (P.dense) {
-            e0 = dense_edge_base(bp, P.S, P.NB) + dense_row_offset(j, P.S);
-            n = P.S - j * kBlock;
-        } else {
-            e0 = P.row_ptr[bp * P.NB + j];
-            n = P.row_ptr[bp * P.NB + j + 1] - static_cast<int>(e0);
-        }
-        const int chunk0 = su.chunk0;
-        const int chunk1 = min((n + kBlock - 1) / kBlock, chunk0 + kChunksPerSubUnit);
-        if (chunk1 <= chunk0) continue;   // this sub-unit lies beyond the end of the row
+        wait(BAR(sm->unit_full[uslot]), (draw / kUnitRing) & 1, 7);
+        if (warp >= 8 && warp < 12) bad = group_or(1, bad);
+        if (bad) break;
+        const UnitDesc ud = sm->units[uslot];
+        if (ud.chunk1 < 0) break;
+        const int j = ud.j, b = ud.b, p = ud.p, n = ud.n, chunk0 = ud.chunk0, chunk1 = ud.chunk1;
         const int ntiles = (chunk1 - chunk0) * hpc;
+        const int64_t slot_base = ud.e0 - edge_base;   // slot of the first row of the reverse-index row
 
-        if (role == 2) {
-            // =========================== issuer ===========================
-            if (nsub > 0) wait(bar_done, (nsub - 1) & 1);   // every product of the previous sub-unit has finished
-            if (elect) {
-                mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-                tma_load_tile(tile_k, &tmap_k, j * kBlock, kvh, b, bar_kv);
-                tma_load_tile(tile_v, &tmap_v, j * kBlock, kvh, b, bar_kv);
-                if (P.with_proxy) {
-                    mbar_arrive_expect_tx(bar_kp, kTileBytes);
-                    tma_load_tile(tile_kp, &tmap_kp, j * kBlock, p / P.pg, b, bar_kp);
-                }
-            }
-            __syncwarp();
-            wait(bar_kv, nsub & 1);
-            bool kp_ready = false;
-            auto issue_s = [&](bool proxy, uint32_t gtile) {
+        if (warp == 14) {
+            // =========================== MMA issue ===========================
+            wait(BAR(sm->k_full), nsub & 1, 5);
+            bool kp_ready = false, v_ready = false;
+            uint32_t gts = gt;   // running index of the next S to issue
+            int hs = 0;          // its head
+            auto next_s = [&]() {
+                const bool proxy = hs == P.mpp;
                 if (proxy && !kp_ready) {
-                    wait(bar_kp, nsub & 1);
+                    wait(BAR(sm->kp_full), nsub & 1, 5);
                     kp_ready = true;
                 }
-                wait(B2(sm->q_full, gtile), (gtile >> 1) & 1);
-                if (gtile >= 2) wait(B2(sm->s_empty, gtile), ((gtile >> 1) - 1) & 1);
+                wait(BAR(sm->q_full[qs]), qph, 1);
+                if (gts >= 2) wait(BAR(sm->s_free[gts & 1]), ((gts >> 1) - 1) & 1, 2);
                 tc_fence_after_sync();
-                umma_tile_128<false, false>(tmem_s0 + (gtile & 1) * 128, tile_q0 + (gtile & 1) * kTileBytes,
-                                            proxy ? tile_kp : tile_k, false, elect);
-                umma_commit(B2(sm->s_full, gtile), elect);
+                if (!bad) {
+                    umma_tile_128<false, false>(tmem_s0 + (gts & 1) * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k,
+                                                false, elect);
+                    umma_commit(BAR(sm->s_full[gts & 1]), elect);
+                    umma_commit(BAR(sm->q_empty[qs]), elect);
+                }
+                if (++qs == kFwdQStages) {
+                    qs = 0;
+                    qph ^= 1;
+                }
+                ++gts;
+                if (++hs == hpc) hs = 0;
             };
-            issue_s(false, gt);
+            next_s();
             int hh = 0;
-            for (int t = 0; t < ntiles; ++t, ++gt) {
+            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
                 const bool is_proxy = hh == P.mpp;
-                int hh1 = hh + 1;
-                if (hh1 == hpc) hh1 = 0;
-                if (t + 1 < ntiles) issue_s(hh1 == P.mpp, gt + 1);     // S of the next tile first: the softmax group never starves
+                if (t + 1 < ntiles) {
+                    next_s();   // S of the next tile first: the softmax groups never starve
+                } else if (!bad) {
+                    umma_commit(BAR(sm->k_empty), elect);    // every S of this sub-unit has been issued
+                    umma_commit(BAR(sm->kp_empty), elect);
+                }
+                wait(BAR(sm->p_full[gt & 1]), (gt >> 1) & 1, 3);
                 if (!is_proxy) {
-                    wait(p_full, mt & 1);
-                    if (mt >= 2) wait(B2(sm->o_empty, mt), ((mt >> 1) - 1) & 1);
+                    if (!v_ready) {
+                        wait(BAR(sm->v_full), nsub & 1, 5);
+                        v_ready = true;
+                    }
+                    if (mt >= 2) wait(BAR(sm->o_empty[mt & 1]), ((mt >> 1) - 1) & 1, 4);
                     tc_fence_after_sync();
-                    umma_tile_128<true, false>(tmem_o0 + (mt & 1) * 128, tile_v, tile_p, false, elect);   // O^T = V_j^T P^T
-                    umma_commit(B2(sm->o_full, mt), elect);
+                    if (!bad) {
+                        const uint32_t ts = tmem_s0 + (gt & 1) * 128;
+                        umma_tile_128_ts<true>(tmem_o0 + (mt & 1) * 128, ts, ts + 32, tile_v, false, elect);   // O = P V_j
+                        umma_commit(BAR(sm->o_full[mt & 1]), elect);
+                    }
                     ++mt;
                 }
-                hh = hh1;
+                if (!bad) umma_commit(BAR(sm->s_free[gt & 1]), elect);
+                if (++hh == hpc) hh = 0;
             }
-            umma_commit(bar_done, elect);
-            if (P.with_proxy && !kp_ready) wait(bar_kp, nsub & 1);   // (every chunk has a proxy tile, so this never waits)
-        } else if (role == 0) {
-            // =========================== softmax group ===========================
-            const int cg = warp >> 2, c0 = cg * 32;
-            int hh = 0, chunk = chunk0;
-            // The finished O^T of a main tile is written out by the softmax warps themselves (32 tile rows per
-            // warp), in the time they would otherwise spend waiting for the next S: leaving it to the gather
-            // warps made them the bottleneck.  TMEM lane = head-dimension index, column = tile row: the 32 lanes
-            // of a warp store 64 contiguous bytes of ONE partial row per instruction.
-            bool pending = false;        // O^T of main tile prev_mt has not been written out by this warp yet
-            uint32_t prev_mt = 0;
-            int prev_head = 0, prev_nrows = 0;
-            int64_t prev_slot0 = 0;
-            auto store_share = [&]() {
-                wait(B2(sm->o_full, prev_mt), (prev_mt >> 1) & 1);   // P*V of that tile has finished (and has read P)
-                tc_fence_after_sync();
-                const int64_t rstride = static_cast<int64_t>(P.mpp) * kHeadDim;
-#pragma unroll
-                for (int c = 0; c < 32; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_addr(tmem_o0 + (prev_mt & 1) * 128, quarter, 32 * cg + c), v);
-                    tmem_ld_wait();
-                    if (c == 16) {
-                        tc_fence_before_sync();
-                        warp_arrive(B2(sm->o_empty, prev_mt));
-                    }
-                    store_transposed_bf16_16(P.o_part + ((prev_slot0 + 32 * cg + c) * P.mpp + prev_head) * kHeadDim + row, rstride, v,
-                                             32 * cg + c, prev_nrows);
+            if (!bad) umma_commit(BAR(sm->v_empty), elect);
+        } else if (warp == 13) {
+            // =========================== K / V / Kp loads ===========================
+            if (nsub > 0) wait(BAR(sm->k_empty), (nsub - 1) & 1);
+            if (!bad && lane == 0) {
+                mbar_arrive_expect_tx(BAR(sm->k_full), kTileBytes);
+                tma_load_tile(tile_k, &tmap_k, j * kBlock, ud.kvh, b, BAR(sm->k_full));
+            }
+            if (P.with_proxy) {
+                if (nsub > 0) wait(BAR(sm->kp_empty), (nsub - 1) & 1);
+                if (!bad && lane == 0) {
+                    mbar_arrive_expect_tx(BAR(sm->kp_full), kTileBytes);
+                    tma_load_tile(tile_kp, &tmap_kp, j * kBlock, p / P.pg, b, BAR(sm->kp_full));
                 }
-                pending = false;
-            };
-            for (int t = 0; t < ntiles; ++t, ++gt) {
-                const bool is_proxy = hh == P.mpp;
-                const int sb = gt & 1;
-                const int nrows = min(kBlock, n - chunk * kBlock);
-                wait(B2(sm->s_full, gt), (gt >> 1) & 1);
-                tc_fence_after_sync();
-                // (the row list was published by the gather group before it released the Q rows S was computed from)
-                const int qid = sm->rows[(cbase + chunk - chunk0) & 7][row];
-                const bool live = qid >= 0;
-                // only the first chunk of a reverse-index row can hold rows of the key block itself
-                const bool masked = (chunk == 0);
-                const int limit = (masked && live && (qid >> 7) == j) ? (qid & 127) : 127;
-                const uint32_t ts = tmem_s0 + sb * 128;
-                float mloc = -INFINITY;
+            }
+            if (nsub > 0) wait(BAR(sm->v_empty), (nsub - 1) & 1);
+            if (!bad && lane == 0) {
+                mbar_arrive_expect_tx(BAR(sm->v_full), kTileBytes);
+                tma_load_tile(tile_v, &tmap_v, j * kBlock, ud.kvh, b, BAR(sm->v_full));
+            }
+            __syncwarp();
+        } else if (warp == 12) {
+            // =========================== row gather ===========================
+            // Lane l fetches rows 4l .. 4l+3 of every tile: one gather4 per 64-column panel.
+            const int64_t q_base = static_cast<int64_t>(b) * P.q_row_b + static_cast<int64_t>(p) * P.mpp * P.q_row_h;
+            const int64_t qp_base = static_cast<int64_t>(b) * P.qp_row_b + static_cast<int64_t>(p) * P.qp_row_h;
+            for (int chunk = chunk0; chunk < chunk1 && !bad; ++chunk) {
+                int qid[4];
+                uint32_t lim4 = 0;
 #pragma unroll
-                for (int c = 0; c < 32; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_addr(ts, quarter, c0 + c), v);
-                    tmem_ld_wait();
-                    if (masked) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) mloc = (c0 + c + i <= limit) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; i += 2) mloc = fmax3(mloc, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-                    }
-                }
-                sm->rmax[cg][row] = mloc;               // raw logits: scale > 0, so the maximum commutes with it
-                named_barrier_sync(1 + quarter, 128);   // the four warps that share these 32 rows
-                const float m = fmaxf(fmaxf(sm->rmax[0][row], sm->rmax[1][row]), fmaxf(sm->rmax[2][row], sm->rmax[3][row])) *
-                                P.scale_log2e;
-                if (pending) store_share();   // (also: P*V of the previous main tile has read P)
-                uint64_t l2 = f2_pack(0.f, 0.f);
-                const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e), nm2 = f2_pack(-m, -m);
-#pragma unroll
-                for (int c = 0; c < 32; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_addr(ts, quarter, c0 + c), v);
-                    tmem_ld_wait();
-                    uint32_t pk[8];
-#pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        float p0, p1;
-                        f2_unpack(f2_fma(f2_pack(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2), p0, p1);
-                        p0 = fast_exp2(p0);
-                        p1 = fast_exp2(p1);
-                        if (masked) {
-                            p0 = (c0 + c + i <= limit) ? p0 : 0.f;
-                            p1 = (c0 + c + i + 1 <= limit) ? p1 : 0.f;
+                for (int i = 0; i < 4; ++i) {
+                    const int at = chunk * kBlock + 4 * lane + i;
+                    int q = -1;
+                    if (at < n) {
+                        q = P.dense ? (j * kBlock + at) : P.col_q[ud.e0 + at];
+                        if (static_cast<unsigned>(q) >= static_cast<unsigned>(P.S) || (q >> 7) < j) {
+                            atomicMax(P.status, kStatusBadIndex);
+                            q = -1;
                         }
-                        l2 = f2_add(l2, f2_pack(p0, p1));
-                        pk[i >> 1] = pack_bf16(p0, p1);
                     }
-                    if (!is_proxy) {
+                    qid[i] = q;
+                    const uint32_t lim = (q >= 0 && (q >> 7) == j) ? static_cast<uint32_t>(q & 127) : 127u;
+                    lim4 |= lim << (8 * i);
+                }
+                reinterpret_cast<uint32_t*>(sm->limits[(cbase + chunk - chunk0) & (kLimitRing - 1)])[lane] = lim4;
+                for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
+                    if (gt >= kFwdQStages) wait(BAR(sm->q_empty[qs]), qph ^ 1);
+                    if (bad) break;
+                    const uint32_t full = BAR(sm->q_full[qs]);
+                    if (lane == 0) mbar_arrive_expect_tx(full, kTileBytes);
+                    __syncwarp();
+                    const bool proxy = hh == P.mpp;
+                    const int64_t base = proxy ? qp_base : q_base + static_cast<int64_t>(hh) * P.q_row_h;
+                    const int64_t rs = proxy ? P.qp_row_s : P.q_row_s;
+                    const int oob = proxy ? P.qp_rows_total : P.q_rows_total;
+                    int r[4];
 #pragma unroll
-                        for (int k8 = 0; k8 < 2; ++k8)
-                            st_shared_v4(tile_p + swz_offset(row, ((c0 + c) >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1],
-                                         pk[4 * k8 + 2], pk[4 * k8 + 3]);
+                    for (int i = 0; i < 4; ++i) r[i] = qid[i] >= 0 ? static_cast<int>(base + qid[i] * rs) : oob;
+                    const uint32_t dst = tile_q0 + qs * kTileBytes + lane * 512;
+                    const void* tm = proxy ? static_cast<const void*>(&tmap_qp) : static_cast<const void*>(&tmap_q);
+                    tma_gather4(dst, tm, 0, r[0], r[1], r[2], r[3], full);
+                    tma_gather4(dst + kPanelBytes, tm, 64, r[0], r[1], r[2], r[3], full);
+                    if (++qs == kFwdQStages) {
+                        qs = 0;
+                        qph ^= 1;
                     }
                 }
-                float l, l_hi;
-                f2_unpack(l2, l, l_hi);
-                l += l_hi;
-                tc_fence_before_sync();
-                warp_arrive(B2(sm->s_empty, gt));
-                if (!is_proxy) {
-                    fence_async_smem();
-                    warp_arrive(p_full);
-                    pending = true;
-                    prev_mt = mt;
-                    prev_head = hh;
-                    prev_nrows = nrows;
-                    prev_slot0 = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock;
-                    ++mt;
-                }
-                sm->lsum[cg][row] = l;
-                named_barrier_sync(1 + quarter, 128);
-                if (cg == 0 && live && row < nrows) {
-                    const int64_t slot = e0 - edge_base + static_cast<int64_t>(chunk) * kBlock + row;
-                    float2* st = reinterpret_cast<float2*>(P.stat_part) + slot * lse_stride + hh;
-                    *st = make_float2(m, sm->lsum[0][row] + sm->lsum[1][row] + sm->lsum[2][row] + sm->lsum[3][row]);
+            }
+        } else if (warp < 8) {
+            // =========================== softmax groups ===========================
+            const uint32_t wg = static_cast<uint32_t>(warp >> 2);
+            const uint32_t ts = tmem_s0 + wg * 128;
+            const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e);
+            int hh = 0, chunk = chunk0;
+            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
+                if ((gt & 1) == wg) {
+                    const bool is_proxy = hh == P.mpp;
+                    const int nrows = min(kBlock, n - chunk * kBlock);
+                    wait(BAR(sm->s_full[wg]), (gt >> 1) & 1);
+                    if (bad) break;
+                    tc_fence_after_sync();
+                    // only the first chunk of a reverse-index row can hold rows of the key block itself
+                    const bool masked = (chunk == 0);
+                    const int limit = masked ? sm->limits[(cbase + chunk - chunk0) & (kLimitRing - 1)][row] : 127;
+                    float mloc = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_addr(ts, quarter, c), v);
+                        tmem_ld_wait();
+                        if (masked) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) mloc = (c + i <= limit) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) mloc = fmax3(mloc, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                        }
+                    }
+                    const float m = mloc * P.scale_log2e;   // raw logits: scale > 0, so the maximum commutes with it
+                    const uint64_t nm2 = f2_pack(-m, -m);
+                    uint64_t l2 = f2_pack(0.f, 0.f);
+#pragma unroll
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_addr(ts, quarter, c), v);
+                        tmem_ld_wait();
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float p0, p1;
+                            f2_unpack(f2_fma(f2_pack(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2), p0, p1);
+                            p0 = fast_exp2(p0);
+                            p1 = fast_exp2(p1);
+                            if (masked) {
+                                p0 = (c + i <= limit) ? p0 : 0.f;
+                                p1 = (c + i + 1 <= limit) ? p1 : 0.f;
+                            }
+                            l2 = f2_add(l2, f2_pack(p0, p1));
+                            pk[i >> 1] = pack_bf16(p0, p1);
+                        }
+                        // P (bf16, two keys per column) over the S columns this thread has already consumed
+                        if (!is_proxy) tmem_st16(tmem_addr(ts, quarter, c >> 1), pk);
+                    }
+                    if (!is_proxy) tmem_st_wait();
+                    tc_fence_before_sync();
+                    warp_arrive(BAR(sm->p_full[wg]));
+                    float l, l_hi;
+                    f2_unpack(l2, l, l_hi);
+                    l += l_hi;
+                    if (row < nrows) {
+                        const int64_t slot = slot_base + static_cast<int64_t>(chunk) * kBlock + row;
+                        reinterpret_cast<float2*>(P.stat_part)[slot * lse_stride + hh] = make_float2(m, l);
+                    }
                 }
                 if (++hh == hpc) {
                     hh = 0;
                     ++chunk;
                 }
             }
-            if (pending) store_share();
-        } else {
-            // =========================== gather group ===========================
-            const int etid = tid - kFwdSoftmax;
-            const GatherLane glane = make_gather_lane(etid);
-            const __nv_bfloat16* q_b = P.q + static_cast<int64_t>(b) * P.q_sb;
-            const __nv_bfloat16* qp_bp = P.qp + static_cast<int64_t>(b) * P.qp_sb + static_cast<int64_t>(p) * P.qp_sh;
-            auto stage_rows = [&](int chunk) {
-                if (etid < kBlock) {
-                    const int at = chunk * kBlock + etid;
-                    int qid = -1;
-                    if (at < n) {
-                        qid = P.dense ? (j * kBlock + at) : P.col_q[e0 + at];
-                        if (static_cast<unsigned>(qid) >= static_cast<unsigned>(P.S) || (qid >> 7) < j) {
-                            atomicMax(P.status, kStatusBadIndex);
-                            qid = -1;
+        } else if (warp < 12) {
+            // =========================== output group ===========================
+            // Thread = row of the O accumulator: bf16, staged in the operand layout, one TMA tile store per panel.
+            // The last, partial chunk of a reverse-index row is written row by row (its slots end where the next
+            // row's begin).
+            const int otid = tid - 8 * 32;
+            int hh = 0, chunk = chunk0;
+            for (int t = 0; t < ntiles && !bad; ++t) {
+                if (hh != P.mpp) {
+                    const int nrows = min(kBlock, n - chunk * kBlock);
+                    const int64_t slot0 = slot_base + static_cast<int64_t>(chunk) * kBlock;
+                    const bool full = nrows == kBlock;
+                    const uint32_t to = tmem_o0 + (mt & 1) * 128;
+                    if (otid == 0) tma_store_wait_read();   // the staging tile's previous store has read it
+                    wait(BAR(sm->o_full[mt & 1]), (mt >> 1) & 1);
+                    bad = group_or(1, bad);
+                    if (bad) break;
+                    tc_fence_after_sync();
+                    __nv_bfloat16* grow = P.o_part + ((slot0 + row) * P.mpp + hh) * kHeadDim;
+#pragma unroll
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_addr(to, quarter, c), v);
+                        tmem_ld_wait();
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        if (full) {
+#pragma unroll
+                            for (int k8 = 0; k8 < 4; ++k8)
+                                st_shared_v4(tile_o + swz_offset(row, (c >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2],
+                                             pk[4 * k8 + 3]);
+                        } else if (row < nrows) {
+#pragma unroll
+                            for (int k8 = 0; k8 < 4; ++k8)
+                                *reinterpret_cast<uint4*>(grow + c + 8 * k8) =
+                                    make_uint4(pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
                         }
                     }
-                    sm->rows[(cbase + chunk - chunk0) & 7][etid] = qid;
+                    tc_fence_before_sync();
+                    warp_arrive(BAR(sm->o_empty[mt & 1]));
+                    if (full) {
+                        fence_async_smem();
+                        named_barrier_sync(1, 128);
+                        if (otid == 0) {
+                            tma_store_3d(&tmap_o, tile_o, 0, hh, static_cast<int>(slot0));
+                            tma_store_3d(&tmap_o, tile_o + kPanelBytes, 64, hh, static_cast<int>(slot0));
+                            tma_store_commit();
+                        }
+                    }
+                    ++mt;
                 }
-            };
-            // 256 threads move a 128-row tile: thread (r0 = etid/16, 16-byte chunk etid%16) covers rows r0 + 16k
-            auto gather_q = [&](int hh, int chunk, uint32_t gtile) {
-                const uint32_t dst = tile_q0 + (gtile & 1) * kTileBytes;
-                const int* rows = sm->rows[(cbase + chunk - chunk0) & 7];
-                const __nv_bfloat16* base = (hh < P.mpp) ? q_b + static_cast<int64_t>(p * P.mpp + hh) * P.q_sh : qp_bp;
-                const int64_t stride = (hh < P.mpp) ? P.q_ss : P.qp_ss;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int rowid = rows[glane.r0 + 16 * k];
-                    const bool ok = rowid >= 0;
-                    cp_async_16(dst + glane.dst_off + k * 2048, base + static_cast<int64_t>(ok ? rowid : 0) * stride + glane.col, ok);
+                if (++hh == hpc) {
+                    hh = 0;
+                    ++chunk;
                 }
-            };
-            // tile walk (head, chunk) for tiles t+1, t+2, t+3 without divisions
-            int hh1 = 1, chunk_1 = chunk0;
-            if (hh1 == hpc) { hh1 = 0; ++chunk_1; }
-            int hh2 = hh1 + 1, chunk_2 = chunk_1;
-            if (hh2 == hpc) { hh2 = 0; ++chunk_2; }
-            // prologue: row lists of the first three tiles, Q rows of the first two
-            stage_rows(chunk0);
-            if (ntiles > 1 && chunk_1 != chunk0) stage_rows(chunk_1);
-            if (ntiles > 2 && chunk_2 != chunk_1) stage_rows(chunk_2);
-            named_barrier_sync(5, kFwdStore);
-            if (gt >= 2) wait(B2(sm->s_full, gt), ((gt >> 1) - 1) & 1);        // the Q buffers' last readers are done
-            if (gt >= 1) wait(B2(sm->s_full, gt + 1), (((gt + 1) >> 1) - 1) & 1);
-            gather_q(0, chunk0, gt);
-            cp_async_commit();
-            if (ntiles > 1) gather_q(hh1, chunk_1, gt + 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-            fence_async_smem();
-            warp_arrive(B2(sm->q_full, gt));
-            for (int t = 0; t < ntiles; ++t, ++gt) {
-                int hh3 = hh2 + 1, chunk_3 = chunk_2;
-                if (hh3 == hpc) { hh3 = 0; ++chunk_3; }
-                // Q rows of tile t+2 go into the buffer S(t) has finished reading
-                if (t + 2 < ntiles) {
-                    wait(B2(sm->s_full, gt), (gt >> 1) & 1);
-                    gather_q(hh2, chunk_2, gt + 2);
-                }
-                cp_async_commit();
-                if (t + 3 < ntiles && chunk_3 != chunk_2) stage_rows(chunk_3);
-                if (t + 1 < ntiles) {
-                    cp_async_wait<1>();     // tile t+1 has landed (t+2 may still be in flight)
-                    fence_async_smem();
-                    warp_arrive(B2(sm->q_full, gt + 1));
-                }
-                named_barrier_sync(5, kFwdStore);   // row list of tile t+3 visible to the whole group before its gather
-                hh1 = hh2; chunk_1 = chunk_2;
-                hh2 = hh3; chunk_2 = chunk_3;
             }
         }
         cbase += static_cast<uint32_t>(chunk1 - chunk0);
         ++nsub;
     }
-    cp_async_wait<0>();
-    if (role == 2 && nsub > 0) wait(bar_done, (nsub - 1) & 1);
-    if (bad) atomicMax(P.status, kStatusWaitTimeout);
+    if (tid == 8 * 32) tma_store_wait_all();
+#ifdef FMSA_TRACE
+    if (blockIdx.x == 0 && lane == 0) {
+        trace_acc[0] = static_cast<unsigned long long>(clock64() - trace_t0);
+        for (int i = 0; i < 8; ++i) g_fwd_trace[warp][i] = trace_acc[i];
+    }
+#endif
+    if (bad) {
+        atomicMax(P.status, kStatusWaitTimeout);
+        // Give loads that are still in flight time to land before the CTA's shared memory is released.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000) __nanosleep(1000);
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -696,18 +769,25 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
         FMSA_REQUIRE(tma_compatible(kp->ptr, kp->stride_b, kp->stride_h, kp->stride_s));
         FMSA_REQUIRE(tma_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
     }
-    CUtensorMap tk, tv, tkp;
-    if (!make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
+    FMSA_REQUIRE(gather_compatible(q->ptr, q->stride_b, q->stride_h, q->stride_s));
+    if (with_proxy) FMSA_REQUIRE(gather_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
+    const fmsa_tensor* qpx = with_proxy ? q_proxy : q;
+    const int hq_px = with_proxy ? pb->Hp : pb->Hq;
+    const uint64_t q_rows = gather_rows(pb->B, pb->Hq, pb->S, q->stride_b, q->stride_h, q->stride_s);
+    const uint64_t qp_rows = gather_rows(pb->B, hq_px, pb->S, qpx->stride_b, qpx->stride_h, qpx->stride_s);
+    CUtensorMap tq, tqp, tk, tv, tkp, to;
+    if (!make_tmap_gather(&tq, q->ptr, q_rows) || !make_tmap_gather(&tqp, qpx->ptr, qp_rows) ||
+        !make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
         !make_tmap_bhsd(&tv, v->ptr, pb->B, pb->Hkv, pb->S, v->stride_b, v->stride_h, v->stride_s, 128) ||
-        !make_tmap_bhsd(&tkp, kp->ptr, pb->B, with_proxy ? pb->Hpkv : pb->Hkv, pb->S, kp->stride_b, kp->stride_h, kp->stride_s, 128))
+        !make_tmap_bhsd(&tkp, kp->ptr, pb->B, with_proxy ? pb->Hpkv : pb->Hkv, pb->S, kp->stride_b, kp->stride_h, kp->stride_s, 128) ||
+        !make_tmap_partials_swz(&to, o_part, static_cast<uint64_t>(part_slots), static_cast<uint64_t>(pb->Hq / pb->Hp)))
         return FMSA_ERR_CUDA;
+    FMSA_REQUIRE(aligned16(o_part) && part_slots < 0x7fffffffLL);
 
     FwdParams P;
-    P.q = static_cast<const __nv_bfloat16*>(q->ptr);
-    P.q_sb = q->stride_b; P.q_sh = q->stride_h; P.q_ss = q->stride_s;
-    P.qp = with_proxy ? static_cast<const __nv_bfloat16*>(q_proxy->ptr) : P.q;
-    P.qp_sb = with_proxy ? q_proxy->stride_b : 0; P.qp_sh = with_proxy ? q_proxy->stride_h : 0;
-    P.qp_ss = with_proxy ? q_proxy->stride_s : 0;
+    P.q_row_b = q->stride_b / 128; P.q_row_h = q->stride_h / 128; P.q_row_s = q->stride_s / 128;
+    P.qp_row_b = qpx->stride_b / 128; P.qp_row_h = qpx->stride_h / 128; P.qp_row_s = qpx->stride_s / 128;
+    P.q_rows_total = static_cast<int32_t>(q_rows); P.qp_rows_total = static_cast<int32_t>(qp_rows);
     P.row_ptr = row_ptr; P.col_q = col_q;
     P.o_part = static_cast<__nv_bfloat16*>(o_part); P.stat_part = lse_part;
     P.counter = counter; P.status = status;
@@ -717,17 +797,13 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.scale_log2e = pb->scale * kLog2e;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        return FMSA_ERR_CUDA;
-    if (cudaFuncSetAttribute(sparse_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kFwdSmemBytes)) !=
-        cudaSuccess)
-        return FMSA_ERR_CUDA;
+    const int sms = device_sm_count();
+    if (sms <= 0 || !ensure_smem_attr(reinterpret_cast<const void*>(sparse_fwd_kernel), kFwdSmemBytes)) return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    sparse_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tk, tv, tkp, P);
+    sparse_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
     return check_launch();
 }
 
@@ -761,3 +837,9 @@ extern "C" int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_par
         combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return check_launch();
 }
+
+#ifdef FMSA_TRACE
+extern "C" int fmsa_debug_fwd_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, fmsa::g_fwd_trace, sizeof(unsigned long long) * 16 * 8) == cudaSuccess ? 0 : -4;
+}
+#endif

@@ -180,10 +180,12 @@ def build_reverse_index_static(block_indices: torch.Tensor, row_ptr: torch.Tenso
 # ----------------------------------------------------------------------------------------------
 
 def _as_kernel_input(t: torch.Tensor) -> torch.Tensor:
-    """Kernels read (B,H,S,128) bf16 with a contiguous last dimension and 16-byte aligned rows;
-    anything else (for instance an odd storage offset) is copied once."""
-    ok = (t.stride(3) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.stride(2) % 8 == 0
-          and t.stride(2) >= 128 and t.data_ptr() % 16 == 0 and t.stride(0) > 0 and t.stride(1) > 0)
+    """Kernels read (B,H,S,128) bf16 with a contiguous last dimension and strides that are multiples of one
+    128-element row (so that a row of any (batch, head, position) is a row of one 2-D matrix the TMA row
+    gather can index): contiguous (B,H,S,D) tensors, (B,S,H,D)-backed views and slices of a packed QKV
+    buffer all qualify.  Anything else (for instance an odd storage offset) is copied once."""
+    ok = (t.stride(3) == 1 and t.stride(0) % 128 == 0 and t.stride(1) % 128 == 0 and t.stride(2) % 128 == 0
+          and t.data_ptr() % 16 == 0 and t.stride(0) > 0 and t.stride(1) > 0 and t.stride(2) > 0)
     return t if ok else t.contiguous()
 
 

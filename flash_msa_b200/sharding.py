@@ -65,7 +65,10 @@ def head_ranges(shard: Shard, hq: int, hkv: int, hp: int, hpkv: int):
     pg = hp // hpkv
     p0, p1 = shard.kv0 * ppk, shard.kv1 * ppk
     kp0, kp1 = p0 // pg, (p1 - 1) // pg + 1
-    if p0 % pg != 0 and (kp1 - kp0) > 1:
+    # The kernels recompute pg from the shard's own head counts and map local proxy head i to local proxy-K
+    # head i // pg_local.  That equals the global map only if the shard lies inside one proxy-K group
+    # (one local proxy-K head) or both of its ends fall on group boundaries.
+    if (kp1 - kp0) > 1 and (p0 % pg != 0 or p1 % pg != 0):
         raise ValueError("shard boundary cuts a proxy-K head group unevenly")
     return (shard.kv0 * g, shard.kv1 * g), (shard.kv0, shard.kv1), (p0, p1), (kp0, kp1)
 
@@ -80,6 +83,22 @@ def needs_dk_proxy_allreduce(hkv: int, hp: int, hpkv: int, shards: List[List[Sha
                 for p in range(s.kv0 * ppk, s.kv1 * ppk):
                     owners.setdefault((b, p // pg), set()).add(r)
     return any(len(v) > 1 for v in owners.values())
+
+
+def allreduce_dk_proxy(dk_proxy_local, shard: Shard, batch: int, hq: int, hkv: int, hp: int, hpkv: int, group=None):
+    """Sums dk_proxy over the ranks that share a proxy-K head (needed when `needs_dk_proxy_allreduce`, e.g. the
+    reference's default Hpkv = 1 cut by KV group): every rank places its local gradient [b, kp, S, D] into a
+    zero tensor of the global shape [batch, Hpkv, S, D], one all-reduce(SUM) runs over `group`, and the rank
+    reads its own slice back.  Returns a tensor shaped like `dk_proxy_local`.  This is the only collective the
+    path can need; it is off the kernel path (after the backward) and all BASELINE configurations avoid it."""
+    import torch
+    import torch.distributed as dist
+    _, _, _, (kp0, kp1) = head_ranges(shard, hq, hkv, hp, hpkv)
+    s, d = dk_proxy_local.shape[2], dk_proxy_local.shape[3]
+    full = torch.zeros(batch, hpkv, s, d, dtype=torch.float32, device=dk_proxy_local.device)
+    full[shard.b0:shard.b1, kp0:kp1] = dk_proxy_local.float()
+    dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
+    return full[shard.b0:shard.b1, kp0:kp1].to(dk_proxy_local.dtype)
 
 
 def slice_inputs(shard: Shard, q_proxy, k_proxy, q, k, v):

@@ -43,6 +43,29 @@ def test_dk_proxy_allreduce_detection():
     assert sh.needs_dk_proxy_allreduce(2, 4, 1, sh.partition(1, 2, 2))      # reference default Hpkv=1
 
 
+def test_head_ranges_reject_shards_that_break_the_proxy_k_map():
+    """A shard is usable only if the kernels' local map (local proxy head // local pg) equals the global one."""
+    # starts on a proxy-K group boundary but ends inside one, spanning two proxy-K heads: rejected
+    pieces = sh.partition(3, 8, 4)[0]
+    assert (pieces[0].kv0, pieces[0].kv1) == (0, 6)
+    with pytest.raises(ValueError):
+        sh.head_ranges(pieces[0], 32, 8, 8, 2)
+    # every accepted shard reproduces the global map
+    for b, hq, hkv, hp, hpkv, world in [(1, 64, 8, 16, 8, 8), (1, 64, 8, 16, 8, 2), (2, 32, 8, 8, 2, 4), (1, 16, 2, 4, 1, 2),
+                                        (2, 32, 8, 8, 8, 16), (1, 32, 8, 8, 2, 8), (3, 32, 8, 8, 2, 4), (1, 48, 4, 8, 4, 2)]:
+        pg = hp // hpkv
+        for pcs in sh.partition(b, hkv, world):
+            for s in pcs:
+                try:
+                    _, _, (p0, p1), (kp0, kp1) = sh.head_ranges(s, hq, hkv, hp, hpkv)
+                except ValueError:
+                    continue
+                assert (p1 - p0) % (kp1 - kp0) == 0
+                pg_local = (p1 - p0) // (kp1 - kp0)
+                for p in range(p0, p1):
+                    assert (p - p0) // pg_local + kp0 == p // pg
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -86,6 +109,39 @@ def _worker(rank, world, port, cfg, result_file):
             f.write("ok" if ok else "mismatch")
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _worker_shared_kp(rank, world, port, cfg, result_file):
+    """Ranks split the KV groups of a problem with ONE proxy-K head: dk_proxy needs the all-reduce."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    qp, kp, q, k, v, do = O.make_inputs(cfg["b"], cfg["s"], cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"], seed=5)
+    shards = sh.partition(cfg["b"], cfg["hkv"], world)
+    assert sh.needs_dk_proxy_allreduce(cfg["hkv"], cfg["hp"], cfg["hpkv"], shards)
+    (shard,) = shards[rank]
+    lqp, lkp, lq, lk, lv = sh.slice_inputs(shard, qp, kp, q, k, v)
+    (h0, h1), _, _, _ = sh.head_ranges(shard, cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"])
+    ldo = do.view(cfg["b"], cfg["s"], cfg["hq"], 128)[shard.b0:shard.b1, :, h0:h1].reshape(shard.b1 - shard.b0, cfg["s"], -1)
+    w = sh.kl_weight(shard, cfg["b"], cfg["hkv"])
+    r = O.sparse_forward_backward(lqp, lkp, lq, lk, lv, cfg["kb"] * 128, SCALE, ldo, grad_kl=w)
+    dkp = sh.allreduce_dk_proxy(r["dk_proxy"], shard, cfg["b"], cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"])
+    full = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, grad_kl=1.0)
+    ok = torch.allclose(dkp.double(), full["dk_proxy"].double(), atol=1e-7)
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(ok))
+    if rank == 0:
+        with open(result_file, "w") as f:
+            f.write("ok" if all(flags) else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_dk_proxy_allreduce_two_ranks(tmp_path):
+    cfg = dict(b=1, s=256, hq=8, hkv=2, hp=4, hpkv=1, kb=2)      # the reference's default: one proxy-K head
+    result = tmp_path / "result.txt"
+    mp.spawn(_worker_shared_kp, args=(2, _free_port(), cfg, str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"
 
 
 @pytest.mark.parametrize("cfg", [dict(b=2, s=256, hq=4, hkv=2, hp=2, hpkv=2, kb=2),      # split by batch
