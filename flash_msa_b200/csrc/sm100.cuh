@@ -100,10 +100,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_poll(bar, parity, limit_ns);
 }
+// (Inlined: a kernel that re-divides its registers between warpgroups with setmaxnreg cannot make calls.)
 // Variant for kernels whose roles run decoupled: `abort_flag` is a word in shared memory that any thread sets
 // when one of its waits ran out.  Every other waiter sees it within one parking period and gives up as well,
 // so the whole CTA leaves its loops together instead of each role waiting out its own limit in turn.
-static __device__ __noinline__ bool mbar_wait_poll_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+static __device__ __forceinline__ bool mbar_wait_poll_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
         if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
@@ -117,6 +118,16 @@ static __device__ __noinline__ bool mbar_wait_poll_abortable(uint32_t bar, uint3
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_poll_abortable(bar, parity, abort_flag);
+}
+
+// Re-division of the register file between the warpgroups of a CTA (all four warps of a warpgroup execute it).
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -266,6 +277,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -477,29 +494,12 @@ __device__ __forceinline__ float fast_log2(float x) {
 }
 // Packed fp32 pairs (sm_100 executes fma/add/mul on two floats per instruction) and 3-input max:
 // they halve the instruction count of the element-wise softmax / dS arithmetic, which is issue bound.
-__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
+// The compiler's own float2 built-ins are used so that it can keep the pairs in adjacent registers
+// (inline asm on 64-bit operands costs extra moves around every instruction).
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 f2_mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 f2_from_bits(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

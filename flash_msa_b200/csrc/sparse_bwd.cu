@@ -27,6 +27,8 @@
 // every causal (query block, key block) pair, with the schedule implied instead of built on the host.
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "host_common.h"
 #include "msa_common.cuh"
 #include "sm100.cuh"
@@ -37,7 +39,7 @@ namespace {
 
 #ifdef FMSA_TRACE
 // Debug builds only: cycles each warp of CTA 0 spent inside its role (slot 0) and inside waits of kind 1..7.
-__device__ unsigned long long g_bwd_trace[16][8];
+__device__ unsigned long long g_bwd_trace[20][8];
 #endif
 
 struct BwdParams {
@@ -90,8 +92,19 @@ struct BwdCtrl {
 };
 
 // Roles (warp index): 0-3 compute group A (queries 0..63 of a tile), 4-7 compute group B (queries 64..127),
-// 8-11 output group, 12 row gather (Q, dO, Qp; Kp_j), 13 K/V loads and row statistics, 14 MMA issue.
-constexpr int kBwdThreads = 16 * 32;   // (warp 15 only takes part in the block-wide steps)
+// 8-11 output group, 12-15 row gather (Q, dO, Qp; Kp_j), 16 K/V loads and row statistics, 17 MMA issue (18, 19 only
+// take part in the block-wide steps).  A TMA row gather costs the issuing warp ~65 cycles whatever its size, so the
+// 128 gathers of a tile are spread over four warps.
+constexpr int kBwdGatherWarps = 4;
+constexpr int kBwdThreads = 20 * 32;
+// Registers per thread after the warpgroups re-divide the register file (setmaxnreg).  A CTA of 640 threads is
+// launched with 96 registers per thread; an increase can only be served from what the other warpgroups of the
+// same CTA gave up, so the five warpgroups must not ask for more than 5 x 96 in total (a warpgroup that asks for
+// registers nobody released waits forever).
+constexpr int kBwdRegsLaunch = 96, kBwdRegsCompute = 136, kBwdRegsOutput = 88, kBwdRegsGather = 56, kBwdRegsMisc = 64;
+static_assert(2 * kBwdRegsCompute + kBwdRegsOutput + kBwdRegsGather + kBwdRegsMisc <= 5 * kBwdRegsLaunch,
+              "register re-division must balance");
+static_assert(kBwdRegsLaunch == (65536 / kBwdThreads) / 8 * 8, "registers per thread at launch");
 constexpr size_t kBwdTileBytes = 7 * static_cast<size_t>(kTileBytes);   // K, V, Q x2, dO x2, dS^T
 constexpr size_t kBwdSmemBytes = 232448;                                 // everything a CTA can have
 static_assert(kBwdTileBytes + sizeof(BwdCtrl) <= kBwdSmemBytes, "shared memory budget of one CTA");
@@ -100,8 +113,8 @@ constexpr int kStatusBadSmem = 3;   // the dynamic shared memory window does not
 // Warp-specialised backward.  Every role walks the same sequence of sub-units (published by the gather warp in a
 // ring) and of tiles.  TMEM (512 columns):
 //   R0 [0,128)   S^T, overwritten in place by P^T (bf16: queries 0..63 in columns 0..31, queries 64..127 in columns
-//                64..95), then dQ (lane = query).  Proxy tile: Sp^T, dSp^T in place, then dQp.
-//   R1 [128,256) dP^T, overwritten by dS^T in the same split.  Proxy tile: dKp (lane = key).
+//                64..95), then dQ (lane = query).  Proxy tile: Sp^T, dSp^T parked in place, then dQp.
+//   R1 [128,256) dP^T, overwritten by dS^T in the same split.  Proxy tile: dKp^T (lane = head dimension).
 //   R2 [256,384) dV, R3 [384,512) dK (lane = key), accumulated over the sub-unit.
 // Issue order of a main tile t (one full product always lies between a product that reads a TMEM operand and a
 // later one that overwrites those columns):
@@ -142,9 +155,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         mbar_init(BAR(sm->acc_full), 1);
         mbar_init(BAR(sm->acc_free), 4);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(sm->q_full[i]), 1);
+            mbar_init(BAR(sm->q_full[i]), kBwdGatherWarps);
             mbar_init(BAR(sm->q_empty[i]), 1);
-            mbar_init(BAR(sm->do_full[i]), 1);
+            mbar_init(BAR(sm->do_full[i]), kBwdGatherWarps);
             mbar_init(BAR(sm->do_empty[i]), 1);
             mbar_init(BAR(sm->st_full[i]), 1);
             mbar_init(BAR(sm->st_empty[i]), 8);
@@ -277,8 +290,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
 
     // Every role has its own loop over the common sequence of sub-units (separate loops keep the register
     // allocation of one role from being charged with the live values of the others).
-    if (warp >= 12) {
-        if (warp == 14) {
+    if (warp >= 16) {
+        reg_dec<kBwdRegsMisc>();
+        if (warp == 17) {
             // =========================== MMA issue ===========================
             BwdUnit ud;
             for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
@@ -325,12 +339,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                         }
                     } else {
                         if (!bad) {
-                            umma_tile_128_ts<true>(r1, r0, r0 + 64, tq, false, elect);      // dKp = dSp^T Qp_g
+                            umma_tile_128<true, false>(r1, tq, tile_ds, false, elect);      // dKp^T = Qp_g^T dSp  (lane = head dim)
                             umma_commit(BAR(sm->dkp_full), elect);
-                        }
-                        wait(BAR(sm->dkp_full), pt & 1, 4);   // dSp^T in R0 has been consumed before dQp overwrites it
-                        tc_fence_after_sync();
-                        if (!bad) {
                             umma_tile_128<true, true>(r0, tile_ds, tdo, false, elect);      // dQp = dSp Kp_j
                             umma_commit(BAR(sm->dq_full), elect);
                             umma_commit(BAR(sm->q_empty[s]), elect);
@@ -346,7 +356,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     umma_commit(BAR(sm->acc_full), elect);
                 }
             }
-        } else if (warp == 13) {
+        } else if (warp == 16) {
             // =========================== K / V loads, row statistics ===========================
             BwdUnit ud;
             for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
@@ -396,62 +406,75 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     }
                 }
             }
-        } else if (warp == 12) {
-            // =========================== row gather ===========================
-            // Lane l fetches rows 4l .. 4l+3 of every tile: one gather4 per 64-column panel and tensor.
-            BwdUnit ud;
-            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
-                const int64_t q_base = static_cast<int64_t>(ud.b) * P.q_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.q_row_h;
-                const int64_t do_base = static_cast<int64_t>(ud.b) * P.do_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.do_row_h;
-                const int64_t qp_base = static_cast<int64_t>(ud.b) * P.qp_row_b + static_cast<int64_t>(ud.p) * P.qp_row_h;
-                for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
-                    int qid[4];
+        }
+    } else if (warp >= 12) {
+        reg_dec<kBwdRegsGather>();
+        // =========================== row gather ===========================
+        // Gather warp g fetches rows 32g .. 32g+31 of every tile: lanes 0..15 issue the dO rows (dP^T is issued before
+        // S^T), lanes 16..31 the Q rows; a lane takes row quad (lane/2)%8 and 64-column panel lane%2.  Lane r holds the
+        // query position of row 32g + r.  In a proxy tile the Q stage takes the Qp rows and the dO stage the proxy keys
+        // of the block (one ordinary tile load by the first gather warp).
+        const int g = warp - 12;
+        const int quad = (lane >> 1) & 7, panel = lane & 1;
+        const bool q_lane = lane >= 16;
+        BwdUnit ud;
+        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            const int64_t q_base = static_cast<int64_t>(ud.b) * P.q_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.q_row_h;
+            const int64_t do_base = static_cast<int64_t>(ud.b) * P.do_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.do_row_h;
+            const int64_t qp_base = static_cast<int64_t>(ud.b) * P.qp_row_b + static_cast<int64_t>(ud.p) * P.qp_row_h;
+            for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
+                const int q = row_qid(ud, chunk * kBlock + 32 * g + lane);
+                int qr[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) qid[i] = row_qid(ud, chunk * kBlock + 4 * lane + i);
-                    for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
-                        const uint32_t s = gt & 1, ph = (gt >> 1) & 1;
-                        const bool proxy = hh == P.mpp;
-                        const uint32_t qf = BAR(sm->q_full[s]), df = BAR(sm->do_full[s]);
-                        const uint32_t tq = tile_q0 + s * kTileBytes + lane * 512, tdo = tile_do0 + s * kTileBytes;
-                        int r[4];
-                        // dO rows first (dP^T is issued before S^T); for a proxy tile the proxy keys of the block
-                        if (gt >= 2) wait(BAR(sm->do_empty[s]), ph ^ 1, 1);
-                        if (bad) break;
-                        if (lane == 0) mbar_arrive_expect_tx(df, kTileBytes);
-                        __syncwarp();
-                        if (proxy) {
-                            if (lane == 0) tma_load_tile(tdo, &tmap_kp, ud.j * kBlock, ud.p / P.pg, ud.b, df);
+                for (int i = 0; i < 4; ++i) qr[i] = __shfl_sync(0xffffffffu, q, 4 * quad + i);
+                for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
+                    const uint32_t s = gt & 1, ph = (gt >> 1) & 1;
+                    const bool proxy = hh == P.mpp;
+                    const uint32_t qf = BAR(sm->q_full[s]), df = BAR(sm->do_full[s]);
+                    const uint32_t off = panel * kPanelBytes + (32 * g + 4 * quad) * 128;
+                    if (gt >= 2) {
+                        wait(BAR(sm->do_empty[s]), ph ^ 1, 1);
+                        wait(BAR(sm->q_empty[s]), ph ^ 1, 2);
+                    }
+                    if (bad) break;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(qf, kTileBytes / kBwdGatherWarps);
+                        if (!proxy) {
+                            mbar_arrive_expect_tx(df, kTileBytes / kBwdGatherWarps);
+                        } else if (g == 0) {
+                            mbar_arrive_expect_tx(df, kTileBytes);
+                            tma_load_tile(tile_do0 + s * kTileBytes, &tmap_kp, ud.j * kBlock, ud.p / P.pg, ud.b, df);
                         } else {
+                            mbar_arrive(df);
+                        }
+                    }
+                    __syncwarp();
+                    int r[4];
+                    if (!q_lane) {
+                        if (!proxy) {
                             const int64_t base = do_base + static_cast<int64_t>(hh) * P.do_row_h;
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
-                                r[i] = qid[i] >= 0 ? static_cast<int>(base + qid[i] * P.do_row_s) : P.do_rows_total;
-                            tma_gather4(tdo + lane * 512, &tmap_do, 0, r[0], r[1], r[2], r[3], df);
-                            tma_gather4(tdo + lane * 512 + kPanelBytes, &tmap_do, 64, r[0], r[1], r[2], r[3], df);
+                                r[i] = qr[i] >= 0 ? static_cast<int>(base + qr[i] * P.do_row_s) : P.do_rows_total;
+                            tma_gather4(tile_do0 + s * kTileBytes + off, &tmap_do, panel * 64, r[0], r[1], r[2], r[3], df);
                         }
-                        if (gt >= 2) wait(BAR(sm->q_empty[s]), ph ^ 1, 2);
-                        if (bad) break;
-                        if (lane == 0) mbar_arrive_expect_tx(qf, kTileBytes);
-                        __syncwarp();
-                        if (proxy) {
+                    } else if (proxy) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                r[i] = qid[i] >= 0 ? static_cast<int>(qp_base + qid[i] * P.qp_row_s) : P.qp_rows_total;
-                            tma_gather4(tq, &tmap_qp, 0, r[0], r[1], r[2], r[3], qf);
-                            tma_gather4(tq + kPanelBytes, &tmap_qp, 64, r[0], r[1], r[2], r[3], qf);
-                        } else {
-                            const int64_t base = q_base + static_cast<int64_t>(hh) * P.q_row_h;
+                        for (int i = 0; i < 4; ++i)
+                            r[i] = qr[i] >= 0 ? static_cast<int>(qp_base + qr[i] * P.qp_row_s) : P.qp_rows_total;
+                        tma_gather4(tile_q0 + s * kTileBytes + off, &tmap_qp, panel * 64, r[0], r[1], r[2], r[3], qf);
+                    } else {
+                        const int64_t base = q_base + static_cast<int64_t>(hh) * P.q_row_h;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                r[i] = qid[i] >= 0 ? static_cast<int>(base + qid[i] * P.q_row_s) : P.q_rows_total;
-                            tma_gather4(tq, &tmap_q, 0, r[0], r[1], r[2], r[3], qf);
-                            tma_gather4(tq + kPanelBytes, &tmap_q, 64, r[0], r[1], r[2], r[3], qf);
-                        }
+                        for (int i = 0; i < 4; ++i)
+                            r[i] = qr[i] >= 0 ? static_cast<int>(base + qr[i] * P.q_row_s) : P.q_rows_total;
+                        tma_gather4(tile_q0 + s * kTileBytes + off, &tmap_q, panel * 64, r[0], r[1], r[2], r[3], qf);
                     }
                 }
             }
         }
     } else if (warp >= 8) {
+        reg_dec<kBwdRegsOutput>();
         // =========================== output group ===========================
         const int otid = tid - 8 * 32;
         // Reads accumulator `acc` (lane = key row of the block) and adds it to the fp32 rows starting at `dst`.
@@ -483,7 +506,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     wait(BAR(sm->dkp_full), pt & 1, 1);
                     if (!bad) {
                         tc_fence_after_sync();
-                        flush_rows(r1, P.dkp_acc + ((static_cast<int64_t>(ud.b) * P.Hpkv + kph) * P.S + ud.j * kBlock) * kHeadDim);
+                        {
+                            // dKp^T: lane = head-dimension index, column = key row: the 32 lanes of a warp add to 32
+                            // consecutive floats of one row per instruction
+                            float* kbase = P.dkp_acc + ((static_cast<int64_t>(ud.b) * P.Hpkv + kph) * P.S + ud.j * kBlock) * kHeadDim + row;
+#pragma unroll 1
+                            for (int c = 0; c < 128; c += 32) {
+                                uint32_t v[32];
+                                tmem_ld32(tmem_addr(r1, quarter, c), v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) atomicAdd(kbase + static_cast<int64_t>(c + i) * kHeadDim, __uint_as_float(v[i]));
+                            }
+                        }
                         tc_fence_before_sync();
                         warp_arrive(BAR(sm->r1_free));
                     }
@@ -550,13 +585,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         }
         if (otid == 0) tma_store_wait_all();
     } else {
+        reg_inc<kBwdRegsCompute>();
         // =========================== compute groups ===========================
         // Thread = (key `row`, the 64 queries of its group).  Reads S^T and dP^T, writes P^T and dS^T back into
         // TMEM over them (bf16) and dS^T into the shared tile that feeds dQ = dS K.
         const int hf = warp >> 2;          // which half of the queries
         const int cbase = hf * 64;
-        const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e);
+        const float2 sc2 = make_float2(P.scale_log2e, P.scale_log2e);
         const float inv_mpp = 1.f / static_cast<float>(P.mpp);
+        const bool with_kl = P.with_kl != 0;
         // sum over the main heads of P for this thread's 64 queries: the KL teacher, as packed fp16 pairs
         // (values in [0,1], at most Hq/Hp addends; the result is rounded to bf16 anyway)
         __half2 teacher[32];
@@ -570,70 +607,99 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                 const bool is_proxy = hh == P.mpp;
                 const uint32_t s = gt & 1;
                 wait(BAR(sm->st_full[s]), (gt >> 1) & 1, 1);
-                if (gt >= 1) wait(BAR(sm->ds_free), (gt - 1) & 1, 2);
                 wait(BAR(sm->sdp_full), gt & 1, 3);
                 if (bad) break;
                 tc_fence_after_sync();
                 const BwdRowStats* st = &sm->stats[s];
                 // only the first chunk of a reverse-index row can hold rows of the key block itself
                 const bool masked = (chunk == 0);
+                // The body is instantiated per (masked, proxy) combination: the common tile (neither) must not pay for
+                // predicated-off mask arithmetic or per-element branches in its inner loop, which is bound by instruction issue.
+                auto compute_tile = [&](auto masked_c, auto proxy_c) __attribute__((always_inline)) {
+                    constexpr bool kMasked = decltype(masked_c)::value;
+                    constexpr bool kProxy = decltype(proxy_c)::value;
+                    // Software pipeline over four 16-column pieces: the TMEM loads of piece c+1 are in flight while piece c
+                    // is worked on (tcgen05.wait::ld waits for every load issued so far, hence the order wait, issue, compute).
+                    uint32_t sv[2][16], dv[2][16];
+                    tmem_ld16(tmem_addr(r0, quarter, cbase), sv[0]);
+                    if (!kProxy) tmem_ld16(tmem_addr(r1, quarter, cbase), dv[0]);
 #pragma unroll
-                for (int c = 0; c < 64; c += 16) {
-                    uint32_t sv[16], dv[16];
-                    tmem_ld16(tmem_addr(r0, quarter, cbase + c), sv);
-                    if (!is_proxy) tmem_ld16(tmem_addr(r1, quarter, cbase + c), dv);
-                    tmem_ld_wait();
-                    uint32_t lim[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
-                    if (masked) {
-                        const uint4 l4 = *reinterpret_cast<const uint4*>(&st->limit[cbase + c]);
-                        lim[0] = l4.x; lim[1] = l4.y; lim[2] = l4.z; lim[3] = l4.w;
-                    }
-                    uint32_t pk[8], dk[8];
-#pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        float a0, a1;   // log2 of the probability
-                        const uint64_t nl2 = *reinterpret_cast<const uint64_t*>(&st->neg_lse[cbase + c + i]);
-                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl2), a0, a1);
-                        float p0 = fast_exp2(a0);
-                        float p1 = fast_exp2(a1);
-                        if (masked) {
-                            const int l0 = static_cast<int>((lim[i >> 2] >> (8 * (i & 3))) & 0xffu);
-                            const int l1 = static_cast<int>((lim[i >> 2] >> (8 * ((i + 1) & 3))) & 0xffu);
-                            p0 = (row <= l0) ? p0 : 0.f;
-                            p1 = (row <= l1) ? p1 : 0.f;
+                    for (int c = 0; c < 64; c += 16) {
+                        const int cur = (c >> 4) & 1;
+                        tmem_ld_wait();
+                        if (c + 16 < 64) {
+                            tmem_ld16(tmem_addr(r0, quarter, cbase + c + 16), sv[cur ^ 1]);
+                            if (!kProxy) tmem_ld16(tmem_addr(r1, quarter, cbase + c + 16), dv[cur ^ 1]);
                         }
-                        const int ti = (c + i) >> 1;
-                        if (!is_proxy) {
-                            float d0, d1;   // dS = P o (dP - delta)
-                            const uint64_t nd2 = *reinterpret_cast<const uint64_t*>(&st->neg_delta[cbase + c + i]);
-                            f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), nd2)),
-                                      d0, d1);
-                            pk[i >> 1] = pack_bf16(p0, p1);
-                            dk[i >> 1] = pack_bf16(d0, d1);
-                            if (P.with_kl) teacher[ti] = __hadd2(teacher[ti], __floats2half2_rn(p0, p1));
-                        } else {
-                            const float2 tt = __half22float2(teacher[ti]);
-                            const float t0 = tt.x * inv_mpp, t1 = tt.y * inv_mpp;
-                            dk[i >> 1] = pack_bf16(p0 - t0, p1 - t1);
-                            if (P.kl_value) {   // KL(teacher || proxy) = sum t (ln t - ln p); t = 0 contributes nothing
-                                kl_acc += (t0 > 0.f) ? t0 * (fast_log2(t0) - a0) : 0.f;
-                                kl_acc += (t1 > 0.f) ? t1 * (fast_log2(t1) - a1) : 0.f;
+                        uint32_t lim[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+                        if (kMasked) {
+                            const uint4 l4 = *reinterpret_cast<const uint4*>(&st->limit[cbase + c]);
+                            lim[0] = l4.x; lim[1] = l4.y; lim[2] = l4.z; lim[3] = l4.w;
+                        }
+                        uint32_t pk[8], dk[8];
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float2 nl2 = *reinterpret_cast<const float2*>(&st->neg_lse[cbase + c + i]);
+                            const float2 a = f2_fma(f2_from_bits(sv[cur][i], sv[cur][i + 1]), sc2, nl2);   // log2 of the probability
+                            float p0 = fast_exp2(a.x);
+                            float p1 = fast_exp2(a.y);
+                            if (kMasked) {
+                                const int l0 = static_cast<int>((lim[i >> 2] >> (8 * (i & 3))) & 0xffu);
+                                const int l1 = static_cast<int>((lim[i >> 2] >> (8 * ((i + 1) & 3))) & 0xffu);
+                                p0 = (row <= l0) ? p0 : 0.f;
+                                p1 = (row <= l1) ? p1 : 0.f;
                             }
-                            teacher[ti] = __floats2half2_rn(0.f, 0.f);
+                            const int ti = (c + i) >> 1;
+                            if (!kProxy) {
+                                // dS = P o (dP - delta)
+                                const float2 nd2 = *reinterpret_cast<const float2*>(&st->neg_delta[cbase + c + i]);
+                                const float2 d = f2_mul(make_float2(p0, p1), f2_add(f2_from_bits(dv[cur][i], dv[cur][i + 1]), nd2));
+                                pk[i >> 1] = pack_bf16(p0, p1);
+                                dk[i >> 1] = pack_bf16(d.x, d.y);
+                                if (with_kl) teacher[ti] = __hadd2(teacher[ti], __floats2half2_rn(p0, p1));
+                            } else {
+                                const float2 tt = __half22float2(teacher[ti]);
+                                const float t0 = tt.x * inv_mpp, t1 = tt.y * inv_mpp;
+                                dk[i >> 1] = pack_bf16(p0 - t0, p1 - t1);
+                                if (P.kl_value) {   // KL(teacher || proxy) = sum t (ln t - ln p); t = 0 contributes nothing
+                                    kl_acc += (t0 > 0.f) ? t0 * (fast_log2(t0) - a.x) : 0.f;
+                                    kl_acc += (t1 > 0.f) ? t1 * (fast_log2(t1) - a.y) : 0.f;
+                                }
+                                teacher[ti] = __floats2half2_rn(0.f, 0.f);
+                            }
+                        }
+                        // bf16 operands back into TMEM over the columns this thread has consumed: two queries per column.
+                        // (In a proxy tile dSp^T is only parked in R0 until it can go to shared memory, see below.)
+                        if (!kProxy) {
+                            tmem_st8(tmem_addr(r0, quarter, cbase + (c >> 1)), pk);
+                            tmem_st8(tmem_addr(r1, quarter, cbase + (c >> 1)), dk);
+                        } else {
+                            tmem_st8(tmem_addr(r0, quarter, cbase + (c >> 1)), dk);
                         }
                     }
-                    // bf16 operands back into TMEM over the columns this thread has consumed: two queries per column
-                    if (!is_proxy) {
-                        tmem_st8(tmem_addr(r0, quarter, cbase + (c >> 1)), pk);
-                        tmem_st8(tmem_addr(r1, quarter, cbase + (c >> 1)), dk);
-                    } else {
-                        tmem_st8(tmem_addr(r0, quarter, cbase + (c >> 1)), dk);
-                    }
-                    // dS^T tile in shared memory: row = key, columns = queries
-                    st_shared_v4(tile_ds + swz_offset(row, (cbase + c) >> 3), dk[0], dk[1], dk[2], dk[3]);
-                    st_shared_v4(tile_ds + swz_offset(row, ((cbase + c) >> 3) + 1), dk[4], dk[5], dk[6], dk[7]);
+                };
+                if (masked) {
+                    if (is_proxy) compute_tile(std::true_type{}, std::true_type{});
+                    else compute_tile(std::true_type{}, std::false_type{});
+                } else {
+                    if (is_proxy) compute_tile(std::false_type{}, std::true_type{});
+                    else compute_tile(std::false_type{}, std::false_type{});
                 }
                 tmem_st_wait();
+                // dS^T also goes to the shared tile that feeds dQ = dS K (row = key, columns = queries).  That tile doubles
+                // as the staging buffer of the previous tile's dQ store, so it is the last thing this tile touches: the
+                // arithmetic above overlaps the previous tile's read-out.
+                if (gt >= 1) wait(BAR(sm->ds_free), (gt - 1) & 1, 2);
+                if (bad) break;
+                {
+                    uint32_t ds[32];
+                    tmem_ld32(tmem_addr(is_proxy ? r0 : r1, quarter, cbase), ds);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; ++k8)
+                        st_shared_v4(tile_ds + swz_offset(row, (cbase >> 3) + k8), ds[4 * k8], ds[4 * k8 + 1], ds[4 * k8 + 2],
+                                     ds[4 * k8 + 3]);
+                }
                 fence_async_smem();
                 tc_fence_before_sync();
                 warp_arrive(BAR(sm->pds_full));
@@ -1001,6 +1067,6 @@ extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_pa
 
 #ifdef FMSA_TRACE
 extern "C" int fmsa_debug_bwd_trace(unsigned long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, fmsa::g_bwd_trace, sizeof(unsigned long long) * 16 * 8) == cudaSuccess ? 0 : -4;
+    return cudaMemcpyFromSymbol(host_out, fmsa::g_bwd_trace, sizeof(unsigned long long) * 20 * 8) == cudaSuccess ? 0 : -4;
 }
 #endif

@@ -25,6 +25,8 @@
 // Scheduling: persistent CTAs (one per SM) take sub-units of reverse-index rows from a global counter;
 // inside a CTA the roles (row gather, K/V loads, MMA issue, softmax x2, output) run decoupled and meet
 // only through mbarriers, see sparse_fwd_kernel.
+#include <type_traits>
+
 #include "host_common.h"
 #include "msa_common.cuh"
 #include "sm100.cuh"
@@ -35,7 +37,7 @@ namespace {
 
 #ifdef FMSA_TRACE
 // Debug builds only: cycles each warp of CTA 0 spent inside its role (slot 0) and inside waits of kind 1..7.
-__device__ unsigned long long g_fwd_trace[16][8];
+__device__ unsigned long long g_fwd_trace[24][8];
 #endif
 
 struct FwdParams {
@@ -79,22 +81,35 @@ struct FwdCtrl {
     int32_t abort_flag;
 };
 
-// Roles (warp index): 0-3 softmax group A (tiles with an even running index, S accumulator 0),
-// 4-7 softmax group B (odd tiles, S accumulator 1), 8-11 output group, 12 row gather, 13 K/V loads, 14 MMA issue.
-constexpr int kFwdThreads = 15 * 32;
+// Roles (warp index): 0-3 softmax group A (tiles with an even running index, S accumulator 0), 4-7 softmax group B
+// (odd tiles, S accumulator 1), 8-11 output group, 12-19 row gather, 20 K/V loads, 21 MMA issue (22, 23 only take
+// part in the block-wide steps).  A TMA row gather costs the issuing warp ~65 cycles whatever its size, so the 64
+// gathers of a tile are spread over eight warps.
+constexpr int kFwdGatherWarps = 8;
+constexpr int kFwdThreads = 24 * 32;
+// Registers per thread after the warpgroups re-divide the register file (setmaxnreg).  A CTA of 768 threads is
+// launched with 80 registers per thread; an increase can only be served from what the other warpgroups of the
+// same CTA gave up, so the six warpgroups must not ask for more than 6 x 80 in total (a warpgroup that asks for
+// registers nobody released waits forever).
+constexpr int kFwdRegsLaunch = 80, kFwdRegsSoftmax = 112, kFwdRegsOutput = 96, kFwdRegsGather = 48, kFwdRegsMisc = 56;
+static_assert(2 * kFwdRegsSoftmax + kFwdRegsOutput + 2 * kFwdRegsGather + kFwdRegsMisc <= 6 * kFwdRegsLaunch,
+              "register re-division must balance");
+static_assert(kFwdRegsLaunch == (65536 / kFwdThreads) / 8 * 8, "registers per thread at launch");
 constexpr size_t kFwdTileBytes = static_cast<size_t>(3 + kFwdQStages + 1) * kTileBytes;   // K, V, Kp, Q stages, output staging
 constexpr size_t kFwdSmemBytes = kFwdTileBytes + 1024 + sizeof(FwdCtrl);
 static_assert(kFwdSmemBytes <= 232448, "shared memory budget of one CTA");
 
-// Warp-specialised forward.  Every role walks the same sequence of sub-units (published by the gather warp in a
-// ring) and, inside a sub-unit, the same sequence of tiles: for each chunk of 128 rows, the main heads of the proxy
+// Warp-specialised forward.  Every role walks the same sequence of sub-units (published by the first gather warp in
+// a ring) and, inside a sub-unit, the same sequence of tiles: for each chunk of 128 rows, the main heads of the proxy
 // head, then the proxy head.  Hand-offs (all mbarriers, one arrival per warp or per tcgen05.commit):
-//   gather warp   q_full[stage] (TMA bytes)  <- q_empty[stage] (commit after S)
+//   gather warps  q_full[stage] (TMA bytes)  <- q_empty[stage] (commit after S)
 //   K/V warp      k_full/v_full/kp_full      <- k_empty/kp_empty (commit after the last S of a sub-unit), v_empty
 //   MMA warp      S(t+1) before P V(t); s_full[t&1], o_full[mt&1]; s_free[t&1] when tile t no longer needs its S columns
 //   softmax       p_full[t&1] when P is in TMEM (or, for a proxy tile, when S has been read)
 //   output group  o_empty[mt&1] when the O accumulator has been read
 // TMEM: S[2] at columns 0 and 128 (P overwrites the first 64 columns of its S), O[2] at 256 and 384.
+// The register file is re-divided between the warpgroups (setmaxnreg): the softmax and output groups get what the
+// gather and issue warps do not need.
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                     const __grid_constant__ CUtensorMap tmap_qp,
                                                                     const __grid_constant__ CUtensorMap tmap_k,
@@ -122,7 +137,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         mbar_init(BAR(sm->kp_full), 1);
         mbar_init(BAR(sm->kp_empty), 1);
         for (int i = 0; i < kFwdQStages; ++i) {
-            mbar_init(BAR(sm->q_full[i]), 1);
+            mbar_init(BAR(sm->q_full[i]), kFwdGatherWarps);
             mbar_init(BAR(sm->q_empty[i]), 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -198,16 +213,17 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     uint32_t nsub = 0;   // sub-units seen so far
     uint32_t cbase = 0;  // chunks of the sub-units seen so far: the row limits of chunk c of a sub-unit live in ring
                          // entry (cbase + c - chunk0) % kLimitRing
-    uint32_t qs = 0, qph = 0;   // gather warp / MMA warp: Q stage of tile gt and the phase bit of its barriers
+    uint32_t qs = 0, qph = 0;   // gather warps / MMA warp: Q stage of tile gt and the phase bit of its barriers
 
-    for (uint32_t draw = 0; !bad; ++draw) {
+    // Next sub-unit of the common sequence (false: no more work, or the CTA is giving up).  The first gather warp draws
+    // the work and publishes the decoded sub-unit; it passes over sub-units that lie beyond the end of their row, so
+    // every published entry has work (or is the end marker).  The roles are at most a handful of tiles apart (Q stages
+    // + S and O accumulators), far fewer than the ring has entries.
+    auto next_unit = [&](uint32_t draw, UnitDesc& ud) -> bool {
         const uint32_t uslot = draw & (kUnitRing - 1);
-        // The gather warp draws the work and publishes the decoded sub-unit.  It passes over sub-units that lie beyond
-        // the end of their row, so every published entry has work (or is the end marker).  The roles are at most a
-        // handful of tiles apart (Q stages + S and O accumulators), far fewer than the ring has entries.
         if (warp == 12 && lane == 0) {
-            UnitDesc ud;
-            ud.chunk1 = -1;
+            UnitDesc nu;
+            nu.chunk1 = -1;
             for (;;) {
                 const int64_t u = atomicAdd(P.counter, 1);
                 if (u >= P.n_subunits) break;
@@ -225,130 +241,143 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     n = P.row_ptr[bp * P.NB + su.j + 1] - static_cast<int>(e0);
                 }
                 if (su.chunk0 * kBlock < n) {
-                    ud.j = su.j; ud.b = b; ud.kvh = kvh; ud.p = p; ud.n = n; ud.e0 = e0;
-                    ud.chunk0 = su.chunk0;
-                    ud.chunk1 = min((n + kBlock - 1) / kBlock, su.chunk0 + kChunksPerSubUnit);
+                    nu.j = su.j; nu.b = b; nu.kvh = kvh; nu.p = p; nu.n = n; nu.e0 = e0;
+                    nu.chunk0 = su.chunk0;
+                    nu.chunk1 = min((n + kBlock - 1) / kBlock, su.chunk0 + kChunksPerSubUnit);
                     break;
                 }
             }
-            sm->units[uslot] = ud;
+            sm->units[uslot] = nu;
             mbar_arrive(BAR(sm->unit_full[uslot]));
         }
         wait(BAR(sm->unit_full[uslot]), (draw / kUnitRing) & 1, 7);
         if (warp >= 8 && warp < 12) bad = group_or(1, bad);
-        if (bad) break;
-        const UnitDesc ud = sm->units[uslot];
-        if (ud.chunk1 < 0) break;
-        const int j = ud.j, b = ud.b, p = ud.p, n = ud.n, chunk0 = ud.chunk0, chunk1 = ud.chunk1;
-        const int ntiles = (chunk1 - chunk0) * hpc;
-        const int64_t slot_base = ud.e0 - edge_base;   // slot of the first row of the reverse-index row
+        if (bad) return false;
+        ud = sm->units[uslot];
+        return ud.chunk1 >= 0;
+    };
 
-        if (warp == 14) {
+    // Every role has its own loop over the common sequence of sub-units.
+    if (warp >= 20) {
+        reg_dec<kFwdRegsMisc>();
+        if (warp == 21) {
             // =========================== MMA issue ===========================
-            wait(BAR(sm->k_full), nsub & 1, 5);
-            bool kp_ready = false, v_ready = false;
-            uint32_t gts = gt;   // running index of the next S to issue
-            int hs = 0;          // its head
-            auto next_s = [&]() {
-                const bool proxy = hs == P.mpp;
-                if (proxy && !kp_ready) {
-                    wait(BAR(sm->kp_full), nsub & 1, 5);
-                    kp_ready = true;
-                }
-                wait(BAR(sm->q_full[qs]), qph, 1);
-                if (gts >= 2) wait(BAR(sm->s_free[gts & 1]), ((gts >> 1) - 1) & 1, 2);
-                tc_fence_after_sync();
-                if (!bad) {
-                    umma_tile_128<false, false>(tmem_s0 + (gts & 1) * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k,
-                                                false, elect);
-                    umma_commit(BAR(sm->s_full[gts & 1]), elect);
-                    umma_commit(BAR(sm->q_empty[qs]), elect);
-                }
-                if (++qs == kFwdQStages) {
-                    qs = 0;
-                    qph ^= 1;
-                }
-                ++gts;
-                if (++hs == hpc) hs = 0;
-            };
-            next_s();
-            int hh = 0;
-            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
-                const bool is_proxy = hh == P.mpp;
-                if (t + 1 < ntiles) {
-                    next_s();   // S of the next tile first: the softmax groups never starve
-                } else if (!bad) {
-                    umma_commit(BAR(sm->k_empty), elect);    // every S of this sub-unit has been issued
-                    umma_commit(BAR(sm->kp_empty), elect);
-                }
-                wait(BAR(sm->p_full[gt & 1]), (gt >> 1) & 1, 3);
-                if (!is_proxy) {
-                    if (!v_ready) {
-                        wait(BAR(sm->v_full), nsub & 1, 5);
-                        v_ready = true;
+            UnitDesc ud;
+            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+                const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
+                wait(BAR(sm->k_full), nsub & 1, 5);
+                bool kp_ready = false, v_ready = false;
+                uint32_t gts = gt;   // running index of the next S to issue
+                int hs = 0;          // its head
+                auto next_s = [&]() {
+                    const bool proxy = hs == P.mpp;
+                    if (proxy && !kp_ready) {
+                        wait(BAR(sm->kp_full), nsub & 1, 5);
+                        kp_ready = true;
                     }
-                    if (mt >= 2) wait(BAR(sm->o_empty[mt & 1]), ((mt >> 1) - 1) & 1, 4);
+                    wait(BAR(sm->q_full[qs]), qph, 1);
+                    if (gts >= 2) wait(BAR(sm->s_free[gts & 1]), ((gts >> 1) - 1) & 1, 2);
                     tc_fence_after_sync();
                     if (!bad) {
-                        const uint32_t ts = tmem_s0 + (gt & 1) * 128;
-                        umma_tile_128_ts<true>(tmem_o0 + (mt & 1) * 128, ts, ts + 32, tile_v, false, elect);   // O = P V_j
-                        umma_commit(BAR(sm->o_full[mt & 1]), elect);
+                        umma_tile_128<false, false>(tmem_s0 + (gts & 1) * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k,
+                                                    false, elect);
+                        umma_commit(BAR(sm->s_full[gts & 1]), elect);
+                        umma_commit(BAR(sm->q_empty[qs]), elect);
                     }
-                    ++mt;
+                    if (++qs == kFwdQStages) {
+                        qs = 0;
+                        qph ^= 1;
+                    }
+                    ++gts;
+                    if (++hs == hpc) hs = 0;
+                };
+                next_s();
+                int hh = 0;
+                for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
+                    const bool is_proxy = hh == P.mpp;
+                    if (t + 1 < ntiles) {
+                        next_s();   // S of the next tile first: the softmax groups never starve
+                    } else if (!bad) {
+                        umma_commit(BAR(sm->k_empty), elect);    // every S of this sub-unit has been issued
+                        umma_commit(BAR(sm->kp_empty), elect);
+                    }
+                    wait(BAR(sm->p_full[gt & 1]), (gt >> 1) & 1, 3);
+                    if (!is_proxy) {
+                        if (!v_ready) {
+                            wait(BAR(sm->v_full), nsub & 1, 5);
+                            v_ready = true;
+                        }
+                        if (mt >= 2) wait(BAR(sm->o_empty[mt & 1]), ((mt >> 1) - 1) & 1, 4);
+                        tc_fence_after_sync();
+                        if (!bad) {
+                            const uint32_t ts = tmem_s0 + (gt & 1) * 128;
+                            umma_tile_128_ts<true>(tmem_o0 + (mt & 1) * 128, ts, ts + 32, tile_v, false, elect);   // O = P V_j
+                            umma_commit(BAR(sm->o_full[mt & 1]), elect);
+                        }
+                        ++mt;
+                    }
+                    if (!bad) umma_commit(BAR(sm->s_free[gt & 1]), elect);
+                    if (++hh == hpc) hh = 0;
                 }
-                if (!bad) umma_commit(BAR(sm->s_free[gt & 1]), elect);
-                if (++hh == hpc) hh = 0;
+                if (!bad) umma_commit(BAR(sm->v_empty), elect);
             }
-            if (!bad) umma_commit(BAR(sm->v_empty), elect);
-        } else if (warp == 13) {
+        } else if (warp == 20) {
             // =========================== K / V / Kp loads ===========================
-            if (nsub > 0) wait(BAR(sm->k_empty), (nsub - 1) & 1);
-            if (!bad && lane == 0) {
-                mbar_arrive_expect_tx(BAR(sm->k_full), kTileBytes);
-                tma_load_tile(tile_k, &tmap_k, j * kBlock, ud.kvh, b, BAR(sm->k_full));
-            }
-            if (P.with_proxy) {
-                if (nsub > 0) wait(BAR(sm->kp_empty), (nsub - 1) & 1);
+            UnitDesc ud;
+            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+                if (nsub > 0) wait(BAR(sm->k_empty), (nsub - 1) & 1);
                 if (!bad && lane == 0) {
-                    mbar_arrive_expect_tx(BAR(sm->kp_full), kTileBytes);
-                    tma_load_tile(tile_kp, &tmap_kp, j * kBlock, p / P.pg, b, BAR(sm->kp_full));
+                    mbar_arrive_expect_tx(BAR(sm->k_full), kTileBytes);
+                    tma_load_tile(tile_k, &tmap_k, ud.j * kBlock, ud.kvh, ud.b, BAR(sm->k_full));
                 }
+                if (P.with_proxy) {
+                    if (nsub > 0) wait(BAR(sm->kp_empty), (nsub - 1) & 1);
+                    if (!bad && lane == 0) {
+                        mbar_arrive_expect_tx(BAR(sm->kp_full), kTileBytes);
+                        tma_load_tile(tile_kp, &tmap_kp, ud.j * kBlock, ud.p / P.pg, ud.b, BAR(sm->kp_full));
+                    }
+                }
+                if (nsub > 0) wait(BAR(sm->v_empty), (nsub - 1) & 1);
+                if (!bad && lane == 0) {
+                    mbar_arrive_expect_tx(BAR(sm->v_full), kTileBytes);
+                    tma_load_tile(tile_v, &tmap_v, ud.j * kBlock, ud.kvh, ud.b, BAR(sm->v_full));
+                }
+                __syncwarp();
             }
-            if (nsub > 0) wait(BAR(sm->v_empty), (nsub - 1) & 1);
-            if (!bad && lane == 0) {
-                mbar_arrive_expect_tx(BAR(sm->v_full), kTileBytes);
-                tma_load_tile(tile_v, &tmap_v, j * kBlock, ud.kvh, b, BAR(sm->v_full));
-            }
-            __syncwarp();
-        } else if (warp == 12) {
-            // =========================== row gather ===========================
-            // Lane l fetches rows 4l .. 4l+3 of every tile: one gather4 per 64-column panel.
-            const int64_t q_base = static_cast<int64_t>(b) * P.q_row_b + static_cast<int64_t>(p) * P.mpp * P.q_row_h;
-            const int64_t qp_base = static_cast<int64_t>(b) * P.qp_row_b + static_cast<int64_t>(p) * P.qp_row_h;
-            for (int chunk = chunk0; chunk < chunk1 && !bad; ++chunk) {
-                int qid[4];
-                uint32_t lim4 = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int at = chunk * kBlock + 4 * lane + i;
-                    int q = -1;
-                    if (at < n) {
-                        q = P.dense ? (j * kBlock + at) : P.col_q[ud.e0 + at];
-                        if (static_cast<unsigned>(q) >= static_cast<unsigned>(P.S) || (q >> 7) < j) {
+        }
+    } else if (warp >= 12) {
+        reg_dec<kFwdRegsGather>();
+        // =========================== row gather ===========================
+        // Gather warp g fetches rows 16g .. 16g+15 of every tile: lanes 0..7 issue one gather4 each (row quad
+        // lane/2, 64-column panel lane%2).  Lanes 0..15 hold the query positions of the warp's rows.
+        const int g = warp - 12;
+        const int quad = (lane >> 1) & 3, panel = lane & 1;
+        UnitDesc ud;
+        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            const int64_t q_base = static_cast<int64_t>(ud.b) * P.q_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.q_row_h;
+            const int64_t qp_base = static_cast<int64_t>(ud.b) * P.qp_row_b + static_cast<int64_t>(ud.p) * P.qp_row_h;
+            for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
+                int q = -1;
+                if (lane < 16) {
+                    const int at = chunk * kBlock + 16 * g + lane;
+                    if (at < ud.n) {
+                        q = P.dense ? (ud.j * kBlock + at) : P.col_q[ud.e0 + at];
+                        if (static_cast<unsigned>(q) >= static_cast<unsigned>(P.S) || (q >> 7) < ud.j) {
                             atomicMax(P.status, kStatusBadIndex);
                             q = -1;
                         }
                     }
-                    qid[i] = q;
-                    const uint32_t lim = (q >= 0 && (q >> 7) == j) ? static_cast<uint32_t>(q & 127) : 127u;
-                    lim4 |= lim << (8 * i);
+                    sm->limits[(cbase + chunk - ud.chunk0) & (kLimitRing - 1)][16 * g + lane] =
+                        (q >= 0 && (q >> 7) == ud.j) ? static_cast<uint8_t>(q & 127) : static_cast<uint8_t>(127);
                 }
-                reinterpret_cast<uint32_t*>(sm->limits[(cbase + chunk - chunk0) & (kLimitRing - 1)])[lane] = lim4;
+                int qr[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qr[i] = __shfl_sync(0xffffffffu, q, 4 * quad + i);
                 for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
                     if (gt >= kFwdQStages) wait(BAR(sm->q_empty[qs]), qph ^ 1);
                     if (bad) break;
                     const uint32_t full = BAR(sm->q_full[qs]);
-                    if (lane == 0) mbar_arrive_expect_tx(full, kTileBytes);
+                    if (lane == 0) mbar_arrive_expect_tx(full, kTileBytes / kFwdGatherWarps);
                     __syncwarp();
                     const bool proxy = hh == P.mpp;
                     const int64_t base = proxy ? qp_base : q_base + static_cast<int64_t>(hh) * P.q_row_h;
@@ -356,98 +385,33 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     const int oob = proxy ? P.qp_rows_total : P.q_rows_total;
                     int r[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) r[i] = qid[i] >= 0 ? static_cast<int>(base + qid[i] * rs) : oob;
-                    const uint32_t dst = tile_q0 + qs * kTileBytes + lane * 512;
+                    for (int i = 0; i < 4; ++i) r[i] = qr[i] >= 0 ? static_cast<int>(base + qr[i] * rs) : oob;
+                    const uint32_t dst = tile_q0 + qs * kTileBytes + panel * kPanelBytes + (16 * g + 4 * quad) * 128;
                     const void* tm = proxy ? static_cast<const void*>(&tmap_qp) : static_cast<const void*>(&tmap_q);
-                    tma_gather4(dst, tm, 0, r[0], r[1], r[2], r[3], full);
-                    tma_gather4(dst + kPanelBytes, tm, 64, r[0], r[1], r[2], r[3], full);
+                    if (lane < 8) tma_gather4(dst, tm, panel * 64, r[0], r[1], r[2], r[3], full);
                     if (++qs == kFwdQStages) {
                         qs = 0;
                         qph ^= 1;
                     }
                 }
             }
-        } else if (warp < 8) {
-            // =========================== softmax groups ===========================
-            const uint32_t wg = static_cast<uint32_t>(warp >> 2);
-            const uint32_t ts = tmem_s0 + wg * 128;
-            const uint64_t sc2 = f2_pack(P.scale_log2e, P.scale_log2e);
-            int hh = 0, chunk = chunk0;
-            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
-                if ((gt & 1) == wg) {
-                    const bool is_proxy = hh == P.mpp;
-                    const int nrows = min(kBlock, n - chunk * kBlock);
-                    wait(BAR(sm->s_full[wg]), (gt >> 1) & 1);
-                    if (bad) break;
-                    tc_fence_after_sync();
-                    // only the first chunk of a reverse-index row can hold rows of the key block itself
-                    const bool masked = (chunk == 0);
-                    const int limit = masked ? sm->limits[(cbase + chunk - chunk0) & (kLimitRing - 1)][row] : 127;
-                    float mloc = -INFINITY;
-#pragma unroll
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(ts, quarter, c), v);
-                        tmem_ld_wait();
-                        if (masked) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) mloc = (c + i <= limit) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 2) mloc = fmax3(mloc, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-                        }
-                    }
-                    const float m = mloc * P.scale_log2e;   // raw logits: scale > 0, so the maximum commutes with it
-                    const uint64_t nm2 = f2_pack(-m, -m);
-                    uint64_t l2 = f2_pack(0.f, 0.f);
-#pragma unroll
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_addr(ts, quarter, c), v);
-                        tmem_ld_wait();
-                        uint32_t pk[16];
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float p0, p1;
-                            f2_unpack(f2_fma(f2_pack(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2), p0, p1);
-                            p0 = fast_exp2(p0);
-                            p1 = fast_exp2(p1);
-                            if (masked) {
-                                p0 = (c + i <= limit) ? p0 : 0.f;
-                                p1 = (c + i + 1 <= limit) ? p1 : 0.f;
-                            }
-                            l2 = f2_add(l2, f2_pack(p0, p1));
-                            pk[i >> 1] = pack_bf16(p0, p1);
-                        }
-                        // P (bf16, two keys per column) over the S columns this thread has already consumed
-                        if (!is_proxy) tmem_st16(tmem_addr(ts, quarter, c >> 1), pk);
-                    }
-                    if (!is_proxy) tmem_st_wait();
-                    tc_fence_before_sync();
-                    warp_arrive(BAR(sm->p_full[wg]));
-                    float l, l_hi;
-                    f2_unpack(l2, l, l_hi);
-                    l += l_hi;
-                    if (row < nrows) {
-                        const int64_t slot = slot_base + static_cast<int64_t>(chunk) * kBlock + row;
-                        reinterpret_cast<float2*>(P.stat_part)[slot * lse_stride + hh] = make_float2(m, l);
-                    }
-                }
-                if (++hh == hpc) {
-                    hh = 0;
-                    ++chunk;
-                }
-            }
-        } else if (warp < 12) {
-            // =========================== output group ===========================
-            // Thread = row of the O accumulator: bf16, staged in the operand layout, one TMA tile store per panel.
-            // The last, partial chunk of a reverse-index row is written row by row (its slots end where the next
-            // row's begin).
-            const int otid = tid - 8 * 32;
-            int hh = 0, chunk = chunk0;
+            cbase += static_cast<uint32_t>(ud.chunk1 - ud.chunk0);
+        }
+    } else if (warp >= 8) {
+        reg_inc<kFwdRegsOutput>();
+        // =========================== output group ===========================
+        // Thread = row of the O accumulator: bf16, staged in the operand layout, one TMA tile store per panel.
+        // The last, partial chunk of a reverse-index row is written row by row (its slots end where the next
+        // row's begin).
+        const int otid = tid - 8 * 32;
+        UnitDesc ud;
+        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
+            const int64_t slot_base = ud.e0 - edge_base;   // slot of the first row of the reverse-index row
+            int hh = 0, chunk = ud.chunk0;
             for (int t = 0; t < ntiles && !bad; ++t) {
                 if (hh != P.mpp) {
-                    const int nrows = min(kBlock, n - chunk * kBlock);
+                    const int nrows = min(kBlock, ud.n - chunk * kBlock);
                     const int64_t slot0 = slot_base + static_cast<int64_t>(chunk) * kBlock;
                     const bool full = nrows == kBlock;
                     const uint32_t to = tmem_o0 + (mt & 1) * 128;
@@ -496,10 +460,103 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 }
             }
         }
-        cbase += static_cast<uint32_t>(chunk1 - chunk0);
-        ++nsub;
+        if (otid == 0) tma_store_wait_all();
+    } else {
+        reg_inc<kFwdRegsSoftmax>();
+        // =========================== softmax groups ===========================
+        const uint32_t wg = static_cast<uint32_t>(warp >> 2);
+        const uint32_t ts = tmem_s0 + wg * 128;
+        const float2 sc2 = make_float2(P.scale_log2e, P.scale_log2e);
+        UnitDesc ud;
+        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
+            const int64_t slot_base = ud.e0 - edge_base;
+            int hh = 0, chunk = ud.chunk0;
+            for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
+                if ((gt & 1) == wg) {
+                    const bool is_proxy = hh == P.mpp;
+                    const int nrows = min(kBlock, ud.n - chunk * kBlock);
+                    wait(BAR(sm->s_full[wg]), (gt >> 1) & 1);
+                    if (bad) break;
+                    tc_fence_after_sync();
+                    // only the first chunk of a reverse-index row can hold rows of the key block itself
+                    const bool masked = (chunk == 0);
+                    const int limit = masked ? sm->limits[(cbase + chunk - ud.chunk0) & (kLimitRing - 1)][row] : 127;
+                    float m = 0.f, l = 0.f;
+                    // The body is instantiated per (masked, proxy) combination: the common tile (neither) must not pay
+                    // for predicated-off mask arithmetic in its inner loops, which are bound by instruction issue.
+                    auto softmax_tile = [&](auto masked_c, auto proxy_c) __attribute__((always_inline)) {
+                        constexpr bool kMasked = decltype(masked_c)::value;
+                        constexpr bool kProxy = decltype(proxy_c)::value;
+                        // Two passes over the 128 logits of the row (maximum, then exponentials), software-pipelined over
+                        // 32-column pieces: the TMEM load of the next piece is in flight while this one is worked on
+                        // (tcgen05.wait::ld waits for every load issued so far, hence the order wait, issue, compute).
+                        uint32_t buf[2][32];
+                        float mloc = -INFINITY;
+                        tmem_ld32(tmem_addr(ts, quarter, 0), buf[0]);
+#pragma unroll
+                        for (int c = 0; c < 128; c += 32) {
+                            const int cur = (c >> 5) & 1;
+                            tmem_ld_wait();
+                            tmem_ld32(tmem_addr(ts, quarter, (c + 32) & 127), buf[cur ^ 1]);   // (the last one fetches piece 0 again, for pass 2)
+                            if (kMasked) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) mloc = (c + i <= limit) ? fmaxf(mloc, __uint_as_float(buf[cur][i])) : mloc;
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 2)
+                                    mloc = fmax3(mloc, __uint_as_float(buf[cur][i]), __uint_as_float(buf[cur][i + 1]));
+                            }
+                        }
+                        m = mloc * P.scale_log2e;   // raw logits: scale > 0, so the maximum commutes with it
+                        const float2 nm2 = make_float2(-m, -m);
+                        float2 l2 = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int c = 0; c < 128; c += 32) {
+                            const int cur = (c >> 5) & 1;
+                            tmem_ld_wait();
+                            if (c + 32 < 128) tmem_ld32(tmem_addr(ts, quarter, c + 32), buf[cur ^ 1]);
+                            uint32_t pk[16];
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const float2 a = f2_fma(f2_from_bits(buf[cur][i], buf[cur][i + 1]), sc2, nm2);
+                                float p0 = fast_exp2(a.x);
+                                float p1 = fast_exp2(a.y);
+                                if (kMasked) {
+                                    p0 = (c + i <= limit) ? p0 : 0.f;
+                                    p1 = (c + i + 1 <= limit) ? p1 : 0.f;
+                                }
+                                l2 = f2_add(l2, make_float2(p0, p1));
+                                if (!kProxy) pk[i >> 1] = pack_bf16(p0, p1);
+                            }
+                            // P (bf16, two keys per column) over S columns this thread has already consumed
+                            if (!kProxy) tmem_st16(tmem_addr(ts, quarter, c >> 1), pk);
+                        }
+                        l = l2.x + l2.y;
+                    };
+                    if (masked) {
+                        if (is_proxy) softmax_tile(std::true_type{}, std::true_type{});
+                        else softmax_tile(std::true_type{}, std::false_type{});
+                    } else {
+                        if (is_proxy) softmax_tile(std::false_type{}, std::true_type{});
+                        else softmax_tile(std::false_type{}, std::false_type{});
+                    }
+                    if (!is_proxy) tmem_st_wait();
+                    tc_fence_before_sync();
+                    warp_arrive(BAR(sm->p_full[wg]));
+                    if (row < nrows) {
+                        const int64_t slot = slot_base + static_cast<int64_t>(chunk) * kBlock + row;
+                        reinterpret_cast<float2*>(P.stat_part)[slot * lse_stride + hh] = make_float2(m, l);
+                    }
+                }
+                if (++hh == hpc) {
+                    hh = 0;
+                    ++chunk;
+                }
+            }
+            cbase += static_cast<uint32_t>(ud.chunk1 - ud.chunk0);
+        }
     }
-    if (tid == 8 * 32) tma_store_wait_all();
 #ifdef FMSA_TRACE
     if (blockIdx.x == 0 && lane == 0) {
         trace_acc[0] = static_cast<unsigned long long>(clock64() - trace_t0);
@@ -840,6 +897,6 @@ extern "C" int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_par
 
 #ifdef FMSA_TRACE
 extern "C" int fmsa_debug_fwd_trace(unsigned long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, fmsa::g_fwd_trace, sizeof(unsigned long long) * 16 * 8) == cudaSuccess ? 0 : -4;
+    return cudaMemcpyFromSymbol(host_out, fmsa::g_fwd_trace, sizeof(unsigned long long) * 24 * 8) == cudaSuccess ? 0 : -4;
 }
 #endif
