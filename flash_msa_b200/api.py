@@ -113,7 +113,6 @@ class _SparseAttentionFunction(torch.autograd.Function):
         ctx.set_materialize_grads(False)
         ctx.scale = float(scale)
         ctx.top_k_blocks = top_k_blocks
-        ctx.block_indices = block_indices      # kept for inspection by tests (not a saved tensor)
         return out, kl_loss
 
     @staticmethod

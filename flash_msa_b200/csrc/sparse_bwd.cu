@@ -53,6 +53,8 @@ struct BwdParams {
     const int32_t* col_q;
     __nv_bfloat16* dq_part;    // [(edge - edge_base) * mpp + head][128]: per-edge dQ contributions (unscaled)
     __nv_bfloat16* dqp_part;   // [(edge - edge_base)][128]: per-edge dQp contributions (unscaled)
+    int64_t part_slots;        // slots per plane of the two buffers above
+    int split;                 // 1: every contribution is stored as a bf16 pair (value, rounding remainder) in two planes
     // fp32, zero-initialised: [B,Hpkv,S,128], [B,Hkv,S,128] x2
     float *dkp_acc, *dk_acc, *dv_acc;
     int32_t* counter;
@@ -528,40 +530,57 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                 bad = group_or(1, bad);
                 if (bad) break;
                 tc_fence_after_sync();
-                __nv_bfloat16* grow = is_proxy ? P.dqp_part + (slot0 + row) * kHeadDim
-                                               : P.dq_part + ((slot0 + row) * P.mpp + hh) * kHeadDim;
+                // With `split` the row leaves twice: rounded to bf16, and the remainder of that rounding (a second plane of
+                // the partial buffers, `part_slots` slots further on), so that the sum over many edges keeps fp32-like accuracy.
+                const int nparts = P.split ? 2 : 1;
+                for (int part = 0; part < nparts; ++part) {
+                    if (part > 0 && full) named_barrier_sync(1, 128);   // the staging tile's first store has read it
+                    const int64_t pslot0 = slot0 + part * P.part_slots;
+                    __nv_bfloat16* grow = is_proxy ? P.dqp_part + (pslot0 + row) * kHeadDim
+                                                   : P.dq_part + ((pslot0 + row) * P.mpp + hh) * kHeadDim;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_addr(r0, quarter, c), v);
-                    tmem_ld_wait();
-                    uint32_t pk[16];
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_addr(r0, quarter, c), v);
+                        tmem_ld_wait();
+                        uint32_t pk[16];
+                        if (part == 0) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                    if (full) {
-                        // the dS^T tile is free (dQ has been computed): it stages the rows for one TMA tile store
+                            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        } else {
 #pragma unroll
-                        for (int k8 = 0; k8 < 4; ++k8)
-                            st_shared_v4(tile_ds + swz_offset(row, (c >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2],
-                                         pk[4 * k8 + 3]);
-                    } else if (row < nrows) {
+                            for (int i = 0; i < 16; ++i) {
+                                const float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
+                                pk[i] = pack_bf16(x0 - bf16_round(x0), x1 - bf16_round(x1));
+                            }
+                        }
+                        if (full) {
+                            // the dS^T tile is free (dQ has been computed): it stages the rows for one TMA tile store
 #pragma unroll
-                        for (int k8 = 0; k8 < 4; ++k8)
-                            *reinterpret_cast<uint4*>(grow + c + 8 * k8) =
-                                make_uint4(pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
+                            for (int k8 = 0; k8 < 4; ++k8)
+                                st_shared_v4(tile_ds + swz_offset(row, (c >> 3) + k8), pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2],
+                                             pk[4 * k8 + 3]);
+                        } else if (row < nrows) {
+#pragma unroll
+                            for (int k8 = 0; k8 < 4; ++k8)
+                                *reinterpret_cast<uint4*>(grow + c + 8 * k8) =
+                                    make_uint4(pk[4 * k8], pk[4 * k8 + 1], pk[4 * k8 + 2], pk[4 * k8 + 3]);
+                        }
                     }
-                }
-                tc_fence_before_sync();
-                warp_arrive(BAR(sm->r0_free));
-                if (full) {
-                    fence_async_smem();
-                    named_barrier_sync(1, 128);
-                    if (otid == 0) {
-                        const void* tm = is_proxy ? static_cast<const void*>(&tmap_dqp) : static_cast<const void*>(&tmap_dq);
-                        tma_store_3d(tm, tile_ds, 0, is_proxy ? 0 : hh, static_cast<int>(slot0));
-                        tma_store_3d(tm, tile_ds + kPanelBytes, 64, is_proxy ? 0 : hh, static_cast<int>(slot0));
-                        tma_store_commit();
-                        tma_store_wait_read();
+                    if (part == nparts - 1) {
+                        tc_fence_before_sync();
+                        warp_arrive(BAR(sm->r0_free));
+                    }
+                    if (full) {
+                        fence_async_smem();
+                        named_barrier_sync(1, 128);
+                        if (otid == 0) {
+                            const void* tm = is_proxy ? static_cast<const void*>(&tmap_dqp) : static_cast<const void*>(&tmap_dq);
+                            tma_store_3d(tm, tile_ds, 0, is_proxy ? 0 : hh, static_cast<int>(pslot0));
+                            tma_store_3d(tm, tile_ds + kPanelBytes, 64, is_proxy ? 0 : hh, static_cast<int>(pslot0));
+                            tma_store_commit();
+                            tma_store_wait_read();
+                        }
                     }
                 }
                 if (otid == 0) mbar_arrive(BAR(sm->ds_free));
@@ -747,6 +766,8 @@ struct BwdCombineParams {
     float scale, kl_out_scale; // factors the backward kernel left out of its partial rows
     int S, NB, Hq, Hp, mpp, ppk, Kb;
     int g_begin, G, dense;
+    int split;              // the partial buffers hold a second plane (rounding remainders) part_slots slots further on
+    int64_t part_slots;
 };
 
 __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams P) {
@@ -778,14 +799,17 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams
             for (int i = 0; i < cnt; ++i) {
                 const int64_t si = __shfl_sync(0xffffffffu, sl, i);
                 if (si < 0) continue;
-                const __nv_bfloat16* src = proxy ? P.dqp_part + si * kHeadDim : P.dq_part + (si * P.mpp + hh) * kHeadDim;
-                const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
-                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                a0 += __low2float(lo);
-                a1 += __high2float(lo);
-                a2 += __low2float(hi);
-                a3 += __high2float(hi);
+                for (int part = 0; part <= P.split; ++part) {
+                    const int64_t sp = si + part * P.part_slots;
+                    const __nv_bfloat16* src = proxy ? P.dqp_part + sp * kHeadDim : P.dq_part + (sp * P.mpp + hh) * kHeadDim;
+                    const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
+                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                    a0 += __low2float(lo);
+                    a1 += __high2float(lo);
+                    a2 += __low2float(hi);
+                    a3 += __high2float(hi);
+                }
             }
         }
         uint2 o;
@@ -834,29 +858,32 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
         for (int i = 0; i < cnt; ++i) {
             const int64_t si = __shfl_sync(0xffffffffu, sl, i);
             if (si < 0) continue;
-            const __nv_bfloat16* rec = P.dq_part + si * P.mpp * kHeadDim;
+            for (int part = 0; part <= P.split; ++part) {
+                const int64_t sp = si + part * P.part_slots;
+                const __nv_bfloat16* rec = P.dq_part + sp * P.mpp * kHeadDim;
 #pragma unroll
-            for (int k = 0; k < KITER; ++k) {
-                const int ck = k * 32 + lane;
-                if (ck < nchunk) {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
-                    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+                for (int k = 0; k < KITER; ++k) {
+                    const int ck = k * 32 + lane;
+                    if (ck < nchunk) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
+                        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&u[e]);
-                        acc[k][2 * e] += __low2float(v2);
-                        acc[k][2 * e + 1] += __high2float(v2);
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&u[e]);
+                            acc[k][2 * e] += __low2float(v2);
+                            acc[k][2 * e + 1] += __high2float(v2);
+                        }
                     }
                 }
-            }
-            if (P.dqp) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(P.dqp_part + si * kHeadDim + lane * 4);
-                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                pa0 += __low2float(lo);
-                pa1 += __high2float(lo);
-                pa2 += __low2float(hi);
-                pa3 += __high2float(hi);
+                if (P.dqp) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(P.dqp_part + sp * kHeadDim + lane * 4);
+                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                    pa0 += __low2float(lo);
+                    pa1 += __high2float(lo);
+                    pa2 += __low2float(hi);
+                    pa3 += __high2float(hi);
+                }
             }
         }
     }
@@ -956,8 +983,8 @@ extern "C" int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const fl
 extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
                                const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out,
                                const float* lse, const float* lse_proxy, const float* delta, const int32_t* row_ptr,
-                               const int32_t* col_q, void* dq_part, void* dqp_part, int64_t part_slots, float* dkp_acc,
-                               float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
+                               const int32_t* col_q, void* dq_part, void* dqp_part, int64_t part_slots, int32_t split,
+                               float* dkp_acc, float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
                                int32_t dense, float* kl_value, int32_t* counter, int32_t* status, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(problem_ok(pb));
@@ -982,7 +1009,7 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     FMSA_REQUIRE(gather_compatible(q->ptr, q->stride_b, q->stride_h, q->stride_s));
     FMSA_REQUIRE(gather_compatible(d_out->ptr, d_out->stride_b, d_out->stride_h, d_out->stride_s));
     if (with_kl) FMSA_REQUIRE(gather_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
-    FMSA_REQUIRE(part_slots > 0 && part_slots < 0x7fffffffLL);
+    FMSA_REQUIRE(part_slots > 0 && part_slots * (split ? 2 : 1) < 0x7fffffffLL);
     const fmsa_tensor* qpx = with_kl ? q_proxy : q;
     const fmsa_tensor* kpx = with_kl ? k_proxy : k;
     const int h_qpx = with_kl ? pb->Hp : pb->Hq, h_kpx = with_kl ? pb->Hpkv : pb->Hkv;
@@ -995,8 +1022,9 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
         !make_tmap_bhsd(&tk, k->ptr, pb->B, pb->Hkv, pb->S, k->stride_b, k->stride_h, k->stride_s, 128) ||
         !make_tmap_bhsd(&tv, v->ptr, pb->B, pb->Hkv, pb->S, v->stride_b, v->stride_h, v->stride_s, 128) ||
         !make_tmap_bhsd(&tkp, kpx->ptr, pb->B, h_kpx, pb->S, kpx->stride_b, kpx->stride_h, kpx->stride_s, 128) ||
-        !make_tmap_partials_swz(&tdq, dq_part, static_cast<uint64_t>(part_slots), static_cast<uint64_t>(pb->Hq / pb->Hp)) ||
-        !make_tmap_partials_swz(&tdqp, with_kl ? dqp_part : dq_part, static_cast<uint64_t>(part_slots), 1))
+        !make_tmap_partials_swz(&tdq, dq_part, static_cast<uint64_t>(part_slots) * (split ? 2 : 1),
+                                static_cast<uint64_t>(pb->Hq / pb->Hp)) ||
+        !make_tmap_partials_swz(&tdqp, with_kl ? dqp_part : dq_part, static_cast<uint64_t>(part_slots) * (split ? 2 : 1), 1))
         return FMSA_ERR_CUDA;
 
     BwdParams P;
@@ -1008,6 +1036,7 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.lse = lse; P.lse_proxy = lse_proxy; P.delta = delta;
     P.row_ptr = row_ptr; P.col_q = col_q;
     P.dq_part = static_cast<__nv_bfloat16*>(dq_part); P.dqp_part = static_cast<__nv_bfloat16*>(dqp_part);
+    P.part_slots = part_slots; P.split = split ? 1 : 0;
     P.dkp_acc = dkp_acc; P.dk_acc = dk_acc; P.dv_acc = dv_acc;
     P.counter = counter; P.status = status;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hkv = pb->Hkv; P.Hp = pb->Hp; P.Hpkv = pb->Hpkv;
@@ -1030,18 +1059,20 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
 }
 
 extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part,
-                                       const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
-                                       const float* grad_kl, int32_t g_begin, int32_t g_count, int32_t dense,
-                                       void* stream) {
+                                       int64_t part_slots, int32_t split, const int32_t* edge_pos, const int32_t* row_ptr,
+                                       void* dq, void* dq_proxy, const float* grad_kl, int32_t g_begin, int32_t g_count,
+                                       int32_t dense, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(problem_ok(pb));
     FMSA_REQUIRE(dq_part && dq);
     FMSA_REQUIRE(dense || (edge_pos && row_ptr));
     FMSA_REQUIRE(!dq_proxy || dqp_part);
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
+    FMSA_REQUIRE(!split || part_slots > 0);
     BwdCombineParams P;
     P.dq_part = static_cast<const __nv_bfloat16*>(dq_part); P.dqp_part = static_cast<const __nv_bfloat16*>(dqp_part);
     P.edge_pos = edge_pos; P.row_ptr = row_ptr;
+    P.split = split ? 1 : 0; P.part_slots = part_slots;
     P.dq = static_cast<__nv_bfloat16*>(dq); P.dqp = static_cast<__nv_bfloat16*>(dq_proxy); P.grad_kl = grad_kl;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hp = pb->Hp; P.mpp = pb->Hq / pb->Hp; P.ppk = pb->Hp / pb->Hkv;
     P.Kb = pb->top_k_blocks; P.g_begin = g_begin; P.G = g_count; P.dense = dense ? 1 : 0;

@@ -483,11 +483,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     const bool masked = (chunk == 0);
                     const int limit = masked ? sm->limits[(cbase + chunk - ud.chunk0) & (kLimitRing - 1)][row] : 127;
                     float m = 0.f, l = 0.f;
-                    // The body is instantiated per (masked, proxy) combination: the common tile (neither) must not pay
-                    // for predicated-off mask arithmetic in its inner loops, which are bound by instruction issue.
-                    auto softmax_tile = [&](auto masked_c, auto proxy_c) __attribute__((always_inline)) {
-                        constexpr bool kMasked = decltype(masked_c)::value;
-                        constexpr bool kProxy = decltype(proxy_c)::value;
+                    {
+                        const bool kMasked = masked, kProxy = is_proxy;
                         // Two passes over the 128 logits of the row (maximum, then exponentials), software-pipelined over
                         // 32-column pieces: the TMEM load of the next piece is in flight while this one is worked on
                         // (tcgen05.wait::ld waits for every load issued so far, hence the order wait, issue, compute).
@@ -533,13 +530,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                             if (!kProxy) tmem_st16(tmem_addr(ts, quarter, c >> 1), pk);
                         }
                         l = l2.x + l2.y;
-                    };
-                    if (masked) {
-                        if (is_proxy) softmax_tile(std::true_type{}, std::true_type{});
-                        else softmax_tile(std::true_type{}, std::false_type{});
-                    } else {
-                        if (is_proxy) softmax_tile(std::false_type{}, std::true_type{});
-                        else softmax_tile(std::false_type{}, std::false_type{});
                     }
                     if (!is_proxy) tmem_st_wait();
                     tc_fence_before_sync();

@@ -239,6 +239,8 @@ def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_bloc
 # Upper bound on the bytes of forward partials held at once; larger problems run in several passes
 # over (batch, KV head) groups.
 MAX_PARTIAL_BYTES = 8 << 30
+# Rows with more edges than this store their dQ partial rows as (value, rounding remainder) pairs.
+SPLIT_PARTIALS_ABOVE = 32
 
 
 def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, with_proxy=True, status=None):
@@ -328,11 +330,17 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
 
     groups = b * hkv
     per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
-    bytes_per_slot = (mpp + (1 if with_kl else 0)) * d * 2
+    # A query row's dQ is the sum of one bf16 partial row per selected block.  Beyond ~32 blocks the rounding of the
+    # partial rows starts to show against the reference's fp32 accumulation, so each partial is then stored as a
+    # (value, rounding remainder) pair in two planes.
+    edges_per_row = (s // BLOCK_SIZE) if dense else rix.top_k_blocks
+    split = 1 if edges_per_row > SPLIT_PARTIALS_ABOVE else 0
+    planes = 2 if split else 1
+    bytes_per_slot = (mpp + (1 if with_kl else 0)) * d * 2 * planes
     gstep = max(1, min(groups, MAX_PARTIAL_BYTES // max(1, per_group * bytes_per_slot)))
     slots = per_group * gstep
-    dq_part = torch.empty(slots * mpp * d, dtype=q.dtype, device=dev)
-    dqp_part = torch.empty(slots * d, dtype=q.dtype, device=dev) if with_kl else None
+    dq_part = torch.empty(planes * slots * mpp * d, dtype=q.dtype, device=dev)
+    dqp_part = torch.empty(planes * slots * d, dtype=q.dtype, device=dev) if with_kl else None
     row_ptr = 0 if dense else rix.row_ptr.data_ptr()
     col_q = 0 if dense else rix.col_q.data_ptr()
     edge_pos = 0 if dense else rix.edge_pos.data_ptr()
@@ -342,13 +350,13 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
             _launch("fmsa_sparse_bwd", 1, lib.fmsa_sparse_bwd(
                 ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
                 _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(), row_ptr, col_q,
-                dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, dkp_acc.data_ptr() if with_kl else 0,
+                dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split, dkp_acc.data_ptr() if with_kl else 0,
                 dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), g0, gc, int(with_kl), int(dense),
                 kl_value.data_ptr() if (with_kl and kl_value is not None) else 0, counter.data_ptr(),
                 status.data_ptr(), st), dev)
         with _Timed("bwd_combine", dev):
             _launch("fmsa_sparse_bwd_combine", 1, lib.fmsa_sparse_bwd_combine(
-                ctypes_byref(pb), dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, edge_pos, row_ptr,
+                ctypes_byref(pb), dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split, edge_pos, row_ptr,
                 dq.data_ptr(), dqp.data_ptr() if with_kl else 0, gk.data_ptr() if with_kl else 0, g0, gc, int(dense), st), dev)
 
     dkv = torch.empty(2, b, hkv, s, d, dtype=q.dtype, device=dev)

@@ -105,8 +105,9 @@ int fmsa_reverse_index(const int32_t* block_indices, int32_t* row_ptr, int32_t* 
  *  - Problems whose scratch need (fmsa_reverse_index_workspace_bytes) exceeds
  *    FMSA_STATIC_SCRATCH_BYTES are refused with FMSA_ERR_WORKSPACE; nothing is launched.
  *  - The call allocates and frees nothing.  Its first call on a device looks the array's device
- *    address up once (cudaGetSymbolAddress, with that device current); make that first call before
- *    any stream capture begins.
+ *    address up once (cudaGetSymbolAddress, with that device current) and keeps it; make that first call
+ *    before any stream capture begins.  The kept address does not survive cudaDeviceReset: a process that
+ *    resets a device must not call this entry point on it afterwards.
  *  - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
  *    (different streams without an ordering) race and give wrong results.  Calls ordered on one
  *    stream are safe; nothing needs clearing between them. */
@@ -162,8 +163,13 @@ int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int3
  *   d_out      (B,Hq,S,128) view of the upstream gradient
  *   lse, delta fp32 [B,Hq,S];  lse_proxy fp32 [B,Hp,S]
  *   dq_part    bf16 [slots, Hq/Hp, 128], dqp_part bf16 [slots, 128]: per-edge contributions to dQ and
- *              dQp (slots >= fmsa_fwd_partial_slots); fmsa_sparse_bwd_combine sums them per row.
+ *              dQp (part_slots = slots >= fmsa_fwd_partial_slots); fmsa_sparse_bwd_combine sums them per row.
  *              Both are unscaled; the combine applies scale and scale/(B*Hp*S).
+ *   split      0: one bf16 value per element, as above.  1: both buffers hold TWO planes of part_slots slots
+ *              (so twice the size): plane 0 the contribution rounded to bf16, plane 1 the remainder of that
+ *              rounding, and the combine adds both.  The sum over the edges of a row then keeps fp32-like
+ *              accuracy however many blocks a row selects (the reference accumulates in fp32 atomics,
+ *              flash_msa/msa_backward_cutedsl.py:738-836); use it when a row has more than ~32 edges.
  *   dkp_acc fp32 [B,Hpkv,S,128], dk_acc, dv_acc fp32 [B,Hkv,S,128]: ZEROED by the caller,
  *              accumulated with atomics (long reverse-index rows are split over several CTAs),
  *              unscaled; cast to the activation dtype with fmsa_cast_scaled (which applies the factors).
@@ -179,8 +185,8 @@ int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int3
 int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
                     const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out, const float* lse,
                     const float* lse_proxy, const float* delta, const int32_t* row_ptr, const int32_t* col_q,
-                    void* dq_part, void* dqp_part, int64_t part_slots, float* dkp_acc, float* dk_acc, float* dv_acc,
-                    int32_t g_begin, int32_t g_count, int32_t with_kl, int32_t dense, float* kl_value,
+                    void* dq_part, void* dqp_part, int64_t part_slots, int32_t split, float* dkp_acc, float* dk_acc,
+                    float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl, int32_t dense, float* kl_value,
                     int32_t* counter, int32_t* status, void* stream);
 
 /* Sums the per-edge contributions of every query row:
@@ -188,8 +194,8 @@ int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_ten
  *   scalar, the upstream gradient of kl_loss: flash_msa/flash_msa.py:122-125; NULL = 1).
  * Takes the place of the reference's fp32 atomic accumulation + cast
  * (flash_msa/msa_backward_cutedsl.py:738-836, 1075-1081). */
-int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part,
-                            const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
+int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part, int64_t part_slots,
+                            int32_t split, const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
                             const float* grad_kl, int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
 
 /* dst[i] = bf16(src[i] * const_scale * f), f = *scale_ptr (a device scalar, e.g. the upstream

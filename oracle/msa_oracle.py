@@ -432,6 +432,79 @@ def row_reference(q_proxy, k_proxy, q, k, v, d_out, scale, b, p, qpos, block_row
             "dq_proxy": dqp, "block_scores": blk}
 
 
+def key_block_reference(q_proxy, k_proxy, q, k, v, d_out, scale, b, kvh, j, block_indices, grad_kl=1.0,
+                        rounded=False, row_chunk=128):
+    """The column-wise twin of ``row_reference``: the gradients that belong to ONE key block j of KV head
+    kvh of batch b, summed over every query row that selected it (all proxy heads of the KV group, all their
+    main heads): dv [128,D], dk [128,D] and dk_proxy {proxy-K head: [128,D]}.  Closed forms of the reference
+    kernel (flash_msa/msa_backward_cutedsl.py:512-551 for dV, dK; :709-733 for dKp), with each row's softmax
+    statistics recomputed from its own selected blocks (``block_indices`` [B,Hp,S,Kb]).  Rows are processed
+    ``row_chunk`` at a time against the gathered keys of their own selected blocks, so this also runs at
+    sequence lengths where the full eager model does not fit.  ``rounded=True`` rounds P, dS, dSp and out to
+    bf16 at the points where the reference kernels do: the error yardstick."""
+    bsz, hq, s, d = q.shape
+    hkv, hp, hpkv = k.shape[1], q_proxy.shape[1], k_proxy.shape[1]
+    mpp, ppk, pg = hq // hp, hp // hkv, hp // hpkv
+    nb = s // BLOCK
+    kb = block_indices.shape[-1]
+    f32 = torch.float32
+    dev = q.device
+    rnd = (lambda t: t.to(torch.bfloat16).to(f32)) if rounded else (lambda t: t)
+    gk = 0.0 if grad_kl is None else float(grad_kl)
+    dv = torch.zeros(BLOCK, d, dtype=f32, device=dev)
+    dk = torch.zeros(BLOCK, d, dtype=f32, device=dev)
+    dkp = {}
+    inblk = torch.arange(BLOCK, device=dev)
+    for p in range(kvh * ppk, (kvh + 1) * ppk):
+        kph = p // pg
+        idx_p = block_indices[b, p].to(dev).long()                  # [S, Kb]
+        qblk = torch.arange(s, device=dev) // BLOCK
+        rows_all = torch.nonzero(((idx_p == j).any(-1)) & (qblk >= j)).flatten()
+        acc_kp = dkp.setdefault(kph, torch.zeros(BLOCK, d, dtype=f32, device=dev))
+        for r0 in range(0, rows_all.numel(), row_chunk):
+            rows = rows_all[r0:r0 + row_chunk]
+            nr = rows.numel()
+            sel = idx_p[rows]                                        # [R, Kb]
+            tok = sel[:, :, None] * BLOCK + inblk[None, None, :]     # [R, Kb, 128]
+            valid = ((sel >= 0) & (sel < nb))[:, :, None] & (tok <= rows[:, None, None])
+            tokc = tok.clamp(0, s - 1).view(nr, kb * BLOCK)
+            valid = valid.view(nr, kb * BLOCK)
+            jpos = (sel == j).float().argmax(1)                      # slot of block j in each row's list
+            ar = torch.arange(nr, device=dev)
+            pick = lambda t: t.view(nr, kb, BLOCK)[ar, jpos]         # [R, 128]: the part that belongs to block j
+            mj = pick(valid)
+            kp_sel = k_proxy[b, kph][tokc].to(f32)                   # [R, T, D]
+            sp = torch.einsum("rd,rtd->rt", q_proxy[b, p, rows].to(f32), kp_sel) * scale
+            del kp_sel
+            sp = sp.masked_fill(~valid, float("-inf"))
+            p_px = pick(torch.exp(sp - torch.logsumexp(sp, 1, keepdim=True)))
+            del sp
+            k_sel = k[b, kvh][tokc].to(f32)
+            v_sel = v[b, kvh][tokc].to(f32)
+            v_j = v[b, kvh, j * BLOCK:(j + 1) * BLOCK].to(f32)
+            teacher = torch.zeros(nr, BLOCK, dtype=f32, device=dev)
+            for i in range(mpp):
+                h = p * mpp + i
+                qh = q[b, h, rows].to(f32)
+                sc = torch.einsum("rd,rtd->rt", qh, k_sel) * scale
+                sc = sc.masked_fill(~valid, float("-inf"))
+                pr = torch.exp(sc - torch.logsumexp(sc, 1, keepdim=True))
+                del sc
+                o = torch.einsum("rt,rtd->rd", rnd(pr), v_sel)
+                do = d_out[b, rows, h * d:(h + 1) * d].to(f32)
+                delta = (rnd(o) * do).sum(1, keepdim=True)
+                pj = pick(pr)
+                del pr
+                dsj = rnd(pj * (do @ v_j.t() - delta))
+                dv += rnd(pj).t() @ do
+                dk += (dsj.t() @ qh) * scale
+                teacher += pj
+            del k_sel, v_sel
+            dsp = rnd(torch.where(mj, p_px - teacher / mpp, torch.zeros_like(p_px))) * (gk / float(bsz * hp * s))
+            acc_kp += (dsp.t() @ q_proxy[b, p, rows].to(f32)) * scale
+    return {"dv": rnd(dv), "dk": rnd(dk), "dk_proxy": {kk: rnd(t) for kk, t in dkp.items()}}
+
+
 # ----------------------------------------------------------------------------
 # synthetic workloads (shapes and value distributions of the benchmark configs)
 # ----------------------------------------------------------------------------

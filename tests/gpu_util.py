@@ -34,4 +34,35 @@ def yardstick_check(name, got, ref32, ref16, floor):
 def yardstick_ratio(got, ref32, ref16):
     """Kernel error divided by the yardstick error plus 1e-3 of the largest reference element (rows whose
     gradient is exactly zero have a zero yardstick error).  For reporting."""
-    return max_err(got, ref32) / (max_err(ref16, ref32) + 1e-3 * ref32.abs().max().item() + 1e-12)
+    return max_err(got, ref32) / (max_err(ref16, ref32) + 1e-3 * ref32.abs().max().item() + 1e-6)
+
+
+def kernel_selection(q_proxy, k_proxy, kb):
+    """The block selection the forward makes for these inputs (the select kernels are deterministic, so
+    calling them again reproduces what `flash_msa_func` used)."""
+    from flash_msa_b200 import ops
+    return ops.select_blocks(q_proxy, k_proxy, scale=SCALE, num_blocks=q_proxy.shape[2] // 128, top_k_blocks=kb)
+
+
+_REPORT = {}
+
+
+def report(section, values):
+    """Collects parity figures (error / yardstick ratios, near-tie and flip counts) of the GPU tests into one
+    JSON file: $FMSA_PARITY_REPORT, or gpurun_out/parity_report.json under the repository root."""
+    import json
+    import os
+    _REPORT[section] = values
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.environ.get("FMSA_PARITY_REPORT") or os.path.join(root, "gpurun_out", "parity_report.json")
+    try:
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        old = {}
+        if os.path.exists(path):
+            with open(path) as f:
+                old = json.load(f)
+        old.update(_REPORT)
+        with open(path, "w") as f:
+            json.dump(old, f, indent=1, sort_keys=True)
+    except OSError:
+        pass

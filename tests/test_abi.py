@@ -14,7 +14,7 @@ def test_library_builds_and_exports_declared_symbols():
     assert "fmsa_select_topk" in names and "fmsa_reverse_index" in names
     for name in names:
         assert hasattr(lib, name), name
-    assert lib.fmsa_abi_version() == 3          # 3: fmsa_pipeline_selftest
+    assert lib.fmsa_abi_version() == 4          # 4: split partial rows in fmsa_sparse_bwd / fmsa_sparse_bwd_combine
 
 
 def test_argument_errors_do_not_launch():

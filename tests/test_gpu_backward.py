@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import msa_oracle as O
-from tests.gpu_util import SCALE, bf16_inputs, max_err, yardstick_check
+from tests.gpu_util import SCALE, bf16_inputs, kernel_selection, max_err, yardstick_check
 
 pytestmark = pytest.mark.gpu
 NAMES = ["dq_proxy", "dk_proxy", "dq", "dk", "dv"]
@@ -52,7 +52,7 @@ def test_sparse_backward(fm, name, grad_kl):
         pytest.skip("grad_kl variants covered on the small shapes")
     qp, kp, q, k, v, do = bf16_inputs(cfg, layout="bshd" if name == "c1" else "bhsd")
     out, grads, node = _run_kernel(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, grad_kl)
-    idx = node.block_indices
+    idx = kernel_selection(qp, kp, cfg["kb"])
     r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, grad_kl, block_indices=idx)
     _, _, g16 = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE, block_indices=idx),
                                          (qp, kp, q, k, v), do, grad_kl)
@@ -116,7 +116,7 @@ def test_kl_value(fm, name):
         _, _, node = _run_kernel(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, 1.0)
         got = fm.last_kl_value()
         assert got is not None and got.shape == () and got.dtype == torch.float32
-        ref = O.sparse_forward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, block_indices=node.block_indices)["kl"]
+        ref = O.sparse_forward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, block_indices=kernel_selection(qp, kp, cfg["kb"]))["kl"]
         assert abs(got.item() - ref.item()) <= 2e-2 * abs(ref.item()) + 1e-4, (got.item(), ref.item())
         _run_kernel(fm.flash_msa_warmup_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, 1.0)
         got_w = fm.last_kl_value()

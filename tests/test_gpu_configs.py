@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import msa_oracle as O
-from tests.gpu_util import SCALE, bf16_inputs, max_err, yardstick_check, yardstick_ratio
+from tests.gpu_util import SCALE, bf16_inputs, kernel_selection, max_err, report, yardstick_check, yardstick_ratio
 
 pytestmark = pytest.mark.gpu
 NAMES = ["dq_proxy", "dk_proxy", "dq", "dk", "dv"]
@@ -30,17 +30,23 @@ def _grads(fn, tensors, do, top_k, grad_kl=1.0):
     return out, [t.grad for t in leaves], out.grad_fn
 
 
-def _check_against_oracle(fm, cfg, skew):
+def _check_against_oracle(fm, cfg, skew, tag):
     qp, kp, q, k, v, do = bf16_inputs(cfg, skew=skew)
-    out, grads, node = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128)
-    idx = node.block_indices
+    out, grads, _ = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128)
+    idx = kernel_selection(qp, kp, cfg["kb"])
     r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 1.0, block_indices=idx)
     r16 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 1.0, block_indices=idx,
                                     dtype=torch.bfloat16)
     # selection: bit-exact on the kernel's own scores is covered elsewhere; here only near-tie flips are allowed
     idx_o, sc = O.select_blocks(qp, kp, SCALE, cfg["kb"])
     flips = (idx.sort(-1).values != idx_o.sort(-1).values).any(-1).sum().item()
-    assert flips <= O.near_tie_report(sc, cfg["kb"], 1e-3)["near_ties"] + 2, flips
+    near = O.near_tie_report(sc, cfg["kb"], 1e-3)["near_ties"]
+    rep = {"config": cfg, "selection_flips": int(flips), "near_ties": int(near), "max_abs_err": {}, "err_over_yardstick": {}}
+    for n, got in zip(["out"] + NAMES, [out] + list(grads)):
+        rep["max_abs_err"][n] = max_err(got, r32[n])
+        rep["err_over_yardstick"][n] = yardstick_ratio(got, r32[n], r16[n])
+    report(tag, rep)
+    assert flips <= near + 2, flips
     yardstick_check("out", out, r32["out"], r16["out"], 2e-3 * r32["out"].abs().max().item())
     for n, got in zip(NAMES, grads):
         ref = r32[n]
@@ -51,13 +57,32 @@ def test_skewed_selection_shape(fm):
     """Reduced-size version of the skewed workload: Hq/Hp = 6, Hp/Hpkv = 2, 24 selected blocks (> 16 and > 32 is
     covered by the top-k unit tests), block-mean keys, x4 proxy queries, sink blocks."""
     cfg = dict(b=1, s=4096, hq=12, hkv=1, hp=2, hpkv=1, kb=24, seed=9)
-    _check_against_oracle(fm, cfg, skew=True)
+    _check_against_oracle(fm, cfg, skew=True, tag="c4_distribution_s4096")
 
 
 def test_config2_full_size_slice(fm):
     """One (batch, KV-head group) slice of B=2 S=8192 Hq=32 Hkv=8 Hp=8 top_k=16 blocks at full sequence length."""
     cfg = dict(b=1, s=8192, hq=4, hkv=1, hp=1, hpkv=1, kb=16, seed=0)
-    _check_against_oracle(fm, cfg, skew=False)
+    _check_against_oracle(fm, cfg, skew=False, tag="c2_slice")
+
+
+def test_config3_full_size_slice(fm):
+    """One (batch, KV-head group) slice of the warmup configuration (B=4 S=4096 Hq=32 Hkv=8 Hp=8) at full sequence
+    length: dense causal main attention + full-sequence proxy KL, forward and all five gradients against the
+    restatement of flash_msa/tests/testing_model_warmup.py:63-104."""
+    cfg = dict(b=1, s=4096, hq=4, hkv=1, hp=1, hpkv=1, kb=1, seed=3)
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    out, grads, _ = _grads(fm.flash_msa_warmup_func, (qp, kp, q, k, v), do, 0)
+    r32 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 1.0)
+    r16 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 1.0, dtype=torch.bfloat16)
+    rep = {"config": cfg, "max_abs_err": {}, "err_over_yardstick": {}}
+    for n, got in zip(["out"] + NAMES, [out] + list(grads)):
+        rep["max_abs_err"][n] = max_err(got, r32[n])
+        rep["err_over_yardstick"][n] = yardstick_ratio(got, r32[n], r16[n])
+    report("c3_slice", rep)
+    yardstick_check("out", out, r32["out"], r16["out"], 2e-3 * r32["out"].abs().max().item())
+    for n, got in zip(NAMES, grads):
+        yardstick_check(n, got, r32[n], r16[n], 2e-3 * r32[n].abs().max().item())
 
 
 def test_config2_full_size_properties(fm):
@@ -66,14 +91,14 @@ def test_config2_full_size_properties(fm):
     out1, g1, node1 = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do, 2048, grad_kl=1.0)
     out2, g2, node2 = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do * 2, 2048, grad_kl=2.0)
     # selection and forward are deterministic
-    assert torch.equal(node1.block_indices, node2.block_indices)
+    idx = kernel_selection(qp, kp, cfg["kb"])
+    assert torch.equal(idx, kernel_selection(qp, kp, cfg["kb"]))
     assert torch.equal(out1, out2)
     # the backward is linear in (dO, grad_kl): doubling both doubles every gradient (up to bf16 rounding)
     for n, a, c in zip(NAMES, g1, g2):
         scale = a.float().abs().max().item()
         assert max_err(c.float(), 2 * a.float()) <= 2e-2 * scale, n
     # every row selects its own block first and only causally valid blocks, each at most once
-    idx = node1.block_indices
     s = cfg["s"]
     qblk = (torch.arange(s, device=idx.device) // 128).view(1, 1, s, 1)
     assert torch.equal(idx[..., :1], qblk.expand(idx.shape[0], idx.shape[1], s, 1).to(idx.dtype))
@@ -99,17 +124,18 @@ LONG = {
 def test_long_context_sampled_rows(fm, name):
     """The sequence lengths of configs 5 and 4 on one of their KV groups: reverse-index rows of > 100
     chunks, sub-unit splitting and the work ring at full length.  The eager model needs 17 GB per head at
-    S = 65536, so parity is checked on sampled query positions with the one-row oracle: selection (stable
-    top-k of independently computed scores, flips only at near-ties), out, dQ, dQp against fp32 with the
-    bf16-rounded restatement as the yardstick."""
+    S = 65536, so parity is checked on samples with the one-row and one-key-block restatements: selection
+    (stable top-k of independently computed scores, flips only at near-ties), out, dQ, dQp on sampled query
+    positions; dK, dV, dKp on sampled key blocks (block 0, the longest reverse-index row, the last block) -
+    all against fp32 with the bf16-rounded restatement as the yardstick (at most twice its error)."""
     cfg, skew = LONG[name]
     qp, kp, q, k, v, do = bf16_inputs(cfg, skew=skew)
-    out, grads, node = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, grad_kl=1.0)
-    idx = node.block_indices
+    out, grads, _ = _grads(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, grad_kl=1.0)
+    idx = kernel_selection(qp, kp, cfg["kb"])
     nb, mpp = cfg["s"] // 128, cfg["hq"] // cfg["hp"]
-    dqp, dq = grads[0], grads[2]
+    dqp, dkp, dq, dk, dv = grads
     flips = near = 0
-    worst = {"out": 0.0, "dq": 0.0, "dq_proxy": 0.0}
+    worst = {"out": 0.0, "dq": 0.0, "dq_proxy": 0.0, "dk": 0.0, "dv": 0.0, "dk_proxy": 0.0}
     for p in range(cfg["hp"]):
         for qpos in (0, 127, 128, 4321, cfg["s"] // 2 + 232, cfg["s"] - 1):
             row = idx[0, p, qpos]
@@ -130,15 +156,34 @@ def test_long_context_sampled_rows(fm, name):
             heads = slice(p * mpp, (p + 1) * mpp)
             o = out[0, qpos].view(cfg["hq"], 128)[heads]
             worst["out"] = max(worst["out"], yardstick_ratio(o, r32["out"], r16["out"]))
-            yardstick_check("out", o, r32["out"], r16["out"], 2e-3 * r32["out"].abs().max().item())
-            # dQ and dQp are sums of per-edge contributions that the kernel rounds to bf16 one by one (up to Kb
-            # of them per row); the floor is one bf16 ulp of the row's largest element
             worst["dq"] = max(worst["dq"], yardstick_ratio(dq[0, heads, qpos], r32["dq"], r16["dq"]))
             worst["dq_proxy"] = max(worst["dq_proxy"], yardstick_ratio(dqp[0, p, qpos], r32["dq_proxy"], r16["dq_proxy"]))
-            yardstick_check("dq", dq[0, heads, qpos], r32["dq"], r16["dq"], 2 ** -8 * r32["dq"].abs().max().item() + 1e-6)
+            yardstick_check("out", o, r32["out"], r16["out"], 2e-3 * r32["out"].abs().max().item())
+            yardstick_check("dq", dq[0, heads, qpos], r32["dq"], r16["dq"], 2e-3 * r32["dq"].abs().max().item() + 1e-6)
             yardstick_check("dq_proxy", dqp[0, p, qpos], r32["dq_proxy"], r16["dq_proxy"],
-                            2 ** -8 * r32["dq_proxy"].abs().max().item() + 1e-9)
-    print(f"long-context {name}: selection flips {flips} (near-ties {near}); worst kernel/yardstick error ratio {worst}")
+                            2e-3 * r32["dq_proxy"].abs().max().item() + 1e-9)
+    # key blocks: the first one, the one with the longest reverse-index row (a sink block in the skewed workload;
+    # > 100 chunks of 128 rows), the last one
+    counts = torch.zeros(nb + 1, dtype=torch.long, device=idx.device)
+    counts.scatter_add_(0, idx[0].reshape(-1).long().clamp(0, nb), torch.ones(idx[0].numel(), dtype=torch.long, device=idx.device))
+    longest = int(counts[1:nb].argmax().item()) + 1
+    chunks = {}
+    for j in sorted({0, longest, nb - 1}):
+        chunks[j] = int((counts[j].item() / cfg["hp"] + 127) // 128)
+        r32 = O.key_block_reference(qp, kp, q, k, v, do, SCALE, 0, 0, j, idx, 1.0)
+        r16 = O.key_block_reference(qp, kp, q, k, v, do, SCALE, 0, 0, j, idx, 1.0, rounded=True)
+        sl = slice(j * 128, (j + 1) * 128)
+        for n, got in (("dk", dk[0, 0, sl]), ("dv", dv[0, 0, sl])):
+            worst[n] = max(worst[n], yardstick_ratio(got, r32[n], r16[n]))
+            yardstick_check(f"{n}[block {j}]", got, r32[n], r16[n], 2e-3 * r32[n].abs().max().item() + 1e-6)
+        for kph, ref in r32["dk_proxy"].items():
+            worst["dk_proxy"] = max(worst["dk_proxy"], yardstick_ratio(dkp[0, kph, sl], ref, r16["dk_proxy"][kph]))
+            yardstick_check(f"dk_proxy[block {j}]", dkp[0, kph, sl], ref, r16["dk_proxy"][kph], 2e-3 * ref.abs().max().item() + 1e-9)
+    assert max(chunks.values()) > 100, chunks
+    report(name, {"config": cfg, "selection_flips_sampled_rows": flips, "near_ties_sampled_rows": near,
+                  "key_blocks_checked": chunks, "err_over_yardstick": worst})
+    print(f"long-context {name}: selection flips {flips} (near-ties {near}); key blocks (chunks per proxy head) {chunks}; "
+          f"worst kernel/yardstick error ratio {worst}")
     assert flips <= near, (flips, near)
 
 

@@ -146,3 +146,19 @@ def test_row_reference_matches_full_oracle():
         assert (sc - rr["block_scores"]).abs().max() < 2e-6
         kl_rows += rr["kl"].item()
     assert kl_rows > 0.0
+
+
+def test_key_block_reference_matches_the_full_restatement():
+    """The per-key-block restatement (used at sequence lengths where the eager model does not fit) gives the
+    dK, dV and dKp slices of the full closed-form oracle."""
+    qp, kp, q, k, v, do = O.make_inputs(2, 768, 8, 2, 4, 2, seed=3)
+    scale, kb = 128 ** -0.5, 3
+    idx, _ = O.select_blocks(qp, kp, scale, kb)
+    full = O.sparse_forward_backward(qp, kp, q, k, v, kb * 128, scale, do, 0.7, block_indices=idx)
+    for b, kvh, j in [(0, 0, 0), (1, 1, 2), (0, 1, 5), (1, 0, 3)]:
+        r = O.key_block_reference(qp, kp, q, k, v, do, scale, b, kvh, j, idx, 0.7, row_chunk=100)
+        sl = slice(j * 128, (j + 1) * 128)
+        assert (r["dv"] - full["dv"][b, kvh, sl]).abs().max().item() <= 1e-5
+        assert (r["dk"] - full["dk"][b, kvh, sl]).abs().max().item() <= 1e-5
+        for kph, t in r["dk_proxy"].items():
+            assert (t - full["dk_proxy"][b, kph, sl]).abs().max().item() <= 1e-9

@@ -37,6 +37,32 @@ def test_static_scratch_reverse_index_matches_workspace_variant():
         assert torch.equal(got.edge_pos, want.edge_pos)
 
 
+def test_static_scratch_calls_allocate_nothing():
+    """What the entry point is for: after the first call on the device (which looks the scratch array's address
+    up) further calls on caller-owned, preallocated tensors neither allocate through torch nor change the
+    amount of free device memory."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from flash_msa_b200 import ops
+    b, hp, s, kb = 2, 4, 4096, 8
+    nb = s // 128
+    idx = _indices(b, hp, s, kb, 5)
+    row_ptr = torch.empty(b * hp * nb + 1, dtype=torch.int32, device="cuda")
+    col_q = torch.empty(b * hp * s * kb, dtype=torch.int32, device="cuda")
+    edge_pos = torch.empty(b, hp, s, kb, dtype=torch.int32, device="cuda")
+    ops.build_reverse_index_static(idx, row_ptr, col_q, edge_pos)       # warm call: symbol address looked up here
+    torch.cuda.synchronize()
+    want = ops.build_reverse_index(idx)
+    torch.cuda.synchronize()
+    free0, alloc0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(3):
+        ops.build_reverse_index_static(idx, row_ptr, col_q, edge_pos)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert torch.equal(row_ptr, want.row_ptr) and torch.equal(edge_pos, want.edge_pos)
+
+
 def test_static_scratch_rejects_oversized_problems():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
