@@ -48,10 +48,6 @@ WORKLOADS = {
                desc="long-context sparse MSA, B=1 S=65536 Hq=64 Hkv=8 Hp=16 Hpkv=8 top_k=32 blocks, sharded by KV group"),
 }
 SCALE = 128 ** -0.5
-# DRAM bytes per launch of the dominant kernel (sparse backward at c2): dram__bytes_read.sum +
-# dram__bytes_write.sum of the ncu capture summarised in profiles/sparse_bwd_kernel_c2q.md (a quarter-size
-# case), scaled by 4 to the full launch.
-BWD_TRAFFIC_BYTES_C2 = 4 * (285.179904e6 + 618.938624e6)
 
 
 def measured_peaks():
@@ -168,14 +164,25 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # CPU arm (reference algorithm on the host cores)
 # --------------------------------------------------------------------------------------------
-def cpu_slice_step(cfg, tensors):
+def cpu_eager_fn(cfg, slice_cfg):
+    """(callable, kind): the reference project's own eager model when its copy under oracle/_ref imports here
+    ("reference"), else the oracle's line-by-line restatement of it ("port")."""
+    from oracle import make_ref
+    from oracle import msa_oracle as O
+    models = make_ref.reference_eager()
+    if models is not None:
+        cls = models[1] if cfg["dense"] else models[0]
+        m = cls(slice_cfg["hq"], slice_cfg["hkv"], 128, slice_cfg["hp"], slice_cfg["hpkv"], max(cfg["kb"], 1) * 128, False)
+        return (lambda *t: m._attention_eager(*t)), "reference"
+    if cfg["dense"]:
+        return (lambda *t: O.eager_warmup(*t, SCALE)), "port"
+    return (lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE)), "port"
+
+
+def cpu_slice_step(fn, tensors):
     """One fwd+bwd of the reference's eager algorithm on one (batch, KV group) slice."""
     from oracle import msa_oracle as O
     qp, kp, q, k, v, do = tensors
-    if cfg["dense"]:
-        fn = lambda *t: O.eager_warmup(*t, SCALE)
-    else:
-        fn = lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE)
     O.eager_forward_backward(fn, (qp, kp, q, k, v), do, 1.0)
 
 
@@ -187,24 +194,26 @@ def cpu_slice(cfg, seed=0):
     pkv = max(1, cfg["hpkv"] // cfg["hkv"])
     tensors = O.make_inputs(1, cfg["s"], g, 1, ppk, min(pkv, ppk), seed=seed)
     slices = cfg["b"] * cfg["hkv"]
-    sl = dict(cfg, b=1, hq=g)
-    return tensors, slices, flops(sl)
+    sl = dict(cfg, b=1, hq=g, hkv=1, hp=ppk, hpkv=min(pkv, ppk))
+    return tensors, slices, flops(sl), sl
 
 
 def run_cpu_baseline(cfg, steps, warmup):
     torch.set_num_threads(os.cpu_count() or 1)
-    tensors, slices, f_slice = cpu_slice(cfg)
+    tensors, slices, f_slice, sl = cpu_slice(cfg)
+    fn, kind = cpu_eager_fn(cfg, sl)
     for _ in range(warmup):
-        cpu_slice_step(cfg, tensors)
+        cpu_slice_step(fn, tensors)
     times = []
     for _ in range(steps):
         t0 = time.perf_counter()
-        cpu_slice_step(cfg, tensors)
+        cpu_slice_step(fn, tensors)
         times.append(time.perf_counter() - t0)
     t = sum(times) / len(times)
-    return {"value": f_slice / t / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+    what = "the reference's own eager model" if kind == "reference" else "fp32 eager restatement"
+    return {"value": f_slice / t / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
             "sample": f"1 of {slices} (batch, KV-head group) slices of the workload per step "
-                      f"(S={cfg['s']}, {cfg['hq'] // cfg['hkv']} main heads), fp32 eager restatement, {steps} step(s)",
+                      f"(S={cfg['s']}, {cfg['hq'] // cfg['hkv']} main heads), {what}, fp32, {steps} step(s)",
             "s_per_slice": t, "slices": slices}
 
 
@@ -219,7 +228,7 @@ def reference_arm(args, cfg):
         "impl": "reference", "metric": "sparse_attn_fwd_bwd_tflops", "value": base["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_slice * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg["desc"], "l2": "inputs larger than L2"},
+        "config": config_of(cfg, local_problem(args.workload, 0, max(1, args.gpus))[1]),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tokens_per_s": cfg["s"] / (per_slice * slices / cfg["b"]) if slices else None,
@@ -269,8 +278,278 @@ def micro_select(args):
 
 
 # --------------------------------------------------------------------------------------------
+# the reference's own GPU kernels beside ours (best effort: they are JIT-built at first use)
+# --------------------------------------------------------------------------------------------
+def ref_kernels(args):
+    """Imports the reference's kernel wrappers from oracle/_ref (written by oracle/make_ref.py) and runs the three
+    that need no FlashAttention backend - select_blocks (flash_msa/msa_select_cutedsl.py:481-538),
+    build_reverse_index_cuda (flash_msa/reverse_index_cuda.py:139-187) and run_fused_backward
+    (flash_msa/msa_backward_cutedsl.py:1083-1114) - beside fmsa_select_*, fmsa_reverse_index and fmsa_sparse_bwd on
+    the same inputs, with the max-abs error of both backward kernels against the fp32 oracle.  Whatever fails to
+    import, build or run is reported with its exception text instead.  Prints one JSON line."""
+    import traceback
+    from oracle import msa_oracle as O
+    out = {"ref_kernels": {}, "shapes": []}
+    refdir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(os.path.join(refdir, "flash_msa")):
+        print(json.dumps({"ref_kernels": {"unavailable": "oracle/_ref is absent (run oracle/make_ref.py where the reference tree is)"}}))
+        return
+    sys.path.insert(0, refdir)
+    dev = torch.device("cuda", 0)
+    from flash_msa_b200 import ops
+
+    def attempt(name, fn):
+        try:
+            return fn()
+        except Exception as e:      # noqa: BLE001 - the exception text IS the result
+            out["ref_kernels"][name] = {"error": f"{type(e).__name__}: {str(e)[:400]}",
+                                        "where": traceback.format_exc().strip().splitlines()[-3:][0][:200]}
+            return None
+
+    def timed(fn, n=5):
+        fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in ev:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in ev)
+
+    # one attempt to import an FA4 backend under the name the reference's forward uses
+    attempt("flash_attn_backend", lambda: __import__("vllm.vllm_flash_attn.cute.interface"))
+    if "flash_attn_backend" not in out["ref_kernels"]:
+        out["ref_kernels"]["flash_attn_backend"] = {"import": "vllm.vllm_flash_attn.cute.interface imports; not wired into the reference forward"}
+
+    shapes = [dict(b=1, s=2048, hq=16, hkv=2, hp=4, hpkv=1, kb=4, tag="reference default (tests/test_eager_match.py)"),
+              dict(WORKLOADS["c2q"], tag="quarter of c2")]
+    for cfg in shapes:
+        tag = cfg["tag"]
+        res = {}
+        qp, kp, q, k, v, do = [t.to(dev) for t in O.make_inputs(cfg["b"], cfg["s"], cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"],
+                                                                seed=0, dtype=torch.bfloat16)]
+        nb, kb, mpp = cfg["s"] // 128, cfg["kb"], cfg["hq"] // cfg["hp"]
+        idx = ops.select_blocks(qp, kp, scale=SCALE, num_blocks=nb, top_k_blocks=kb)
+        res["ours_select_ms"] = timed(lambda: ops.select_blocks(qp, kp, scale=SCALE, num_blocks=nb, top_k_blocks=kb))
+        res["ours_reverse_index_ms"] = timed(lambda: ops.build_reverse_index(idx))
+
+        def ref_select():
+            from flash_msa.msa_select_cutedsl import select_blocks
+            r = select_blocks(qp, kp, scale=SCALE, num_blocks=nb, top_k_blocks=kb)
+            res["ref_select_ms"] = timed(lambda: select_blocks(qp, kp, scale=SCALE, num_blocks=nb, top_k_blocks=kb))
+            same = (r.sort(-1).values == idx.sort(-1).values).all(-1).float().mean().item()
+            res["rows_with_same_selection"] = same      # the reference rounds scores to bf16 first: ties differ
+            return r
+        attempt(f"select_blocks [{tag}]", ref_select)
+
+        meta = {}
+
+        def ref_rix():
+            from flash_msa.reverse_index_cuda import build_reverse_index_cuda
+            qc = 128 // mpp
+            meta["tm"], meta["tq"] = build_reverse_index_cuda(idx, query_chunk=qc)
+            res["ref_reverse_index_ms"] = timed(lambda: build_reverse_index_cuda(idx, query_chunk=qc))
+        attempt(f"build_reverse_index_cuda [{tag}]", ref_rix)
+
+        # backward: both kernels get the same forward results (ours), the oracle is the judge
+        rix = ops.build_reverse_index(idx)
+        o, lse, lse_p = ops.attention_forward(q, k, v, qp, kp, SCALE, rix)
+        gk = torch.ones((), device=dev)
+        ours = ops.attention_backward(q, k, v, qp, kp, o, do, lse, lse_p, SCALE, rix, gk)
+        res["ours_backward_ms"] = timed(lambda: ops.attention_backward(q, k, v, qp, kp, o, do, lse, lse_p, SCALE, rix, gk))
+        names = ["dq_proxy", "dk_proxy", "dq", "dk", "dv"]
+        want = None
+        if cfg["s"] <= 2048:
+            want = O.sparse_forward_backward(qp, kp, q, k, v, kb * 128, SCALE, do, 1.0, block_indices=idx)
+            res["ours_max_abs_err"] = {n: (g_.float() - want[n]).abs().max().item() for n, g_ in zip(names, ours)}
+
+        def ref_bwd():
+            from flash_msa.msa_backward_cutedsl import run_fused_backward
+            go = do.view(cfg["b"], cfg["s"], cfg["hq"], 128).transpose(1, 2).contiguous()
+            om = o.view(cfg["b"], cfg["s"], cfg["hq"], 128).transpose(1, 2).contiguous()
+            delta = (om.float() * go.float()).sum(-1)
+            call = lambda: run_fused_backward(qp, kp, q, k, v, go, lse, lse_p, delta, meta["tm"], meta["tq"], scale=SCALE,
+                                              grad_kl_scale=1.0 / (cfg["b"] * cfg["hp"] * cfg["s"]))
+            grads = call()
+            res["ref_backward_ms"] = timed(call)
+            if want is not None:
+                res["ref_max_abs_err"] = {n: (g_.float() - want[n]).abs().max().item() for n, g_ in zip(names, grads)}
+        if "tm" in meta:
+            attempt(f"run_fused_backward [{tag}]", ref_bwd)
+        out["shapes"].append({"shape": {k_: v_ for k_, v_ in cfg.items() if k_ not in ("desc", "tag", "dense")}, "tag": tag, **res})
+    print(json.dumps(out))
+
+
+# --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
+SHARDING_NOTE = "(batch, KV-head group), no collective on the kernel path"
+L2_NOTE = "inputs larger than L2 (no flush needed)"
+
+
+def config_of(cfg, local):
+    """The `config` object of the JSON line; both arms emit the same one for the same workload."""
+    return {"workload": cfg["desc"], "sharding": SHARDING_NOTE, "l2": L2_NOTE, "per_rank": local}
+
+
+def local_problem(name, rank, world):
+    """Per-rank problem and scaling mode of a workload: config 5 is one global problem split by KV group (strong
+    scaling); every other workload is replicated, one full problem per rank (weak scaling)."""
+    from flash_msa_b200.sharding import shard_workload
+    cfg = dict(WORKLOADS[name])
+    if name == "c5":
+        return cfg, shard_workload(cfg, rank, world), "strong"
+    return cfg, dict(cfg), "weak"
+
+
+def bwd_traffic_bytes(workload):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary (profiles/traffic_c2q.json: a
+    capture of the quarter-size case; traffic is proportional to the (batch, KV group) units processed)."""
+    path = os.path.join(ROOT, "profiles", "traffic_c2q.json")
+    if workload != "c2" or not os.path.exists(path):
+        return None
+    with open(path) as f:
+        t = json.load(f)
+    return float(t["scale_to_c2"]) * (float(t["dram_bytes_read"]) + float(t["dram_bytes_write"]))
+
+
+class GpuContext:
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (flash_msa_b200 has no CPU path)")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def sync_all(self):
+        torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms):
+        if self.dist is None:
+            return ms
+        t = torch.tensor([ms], device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks):
+    """W warm-up steps, then K timed fwd+bwd steps of one workload on this rank's share of it (CUDA events on the
+    launching stream, barrier + synchronize on both sides, max over ranks)."""
+    import flash_msa_b200
+    from flash_msa_b200 import ops
+    from oracle.msa_oracle import make_inputs
+
+    cfg, local, scaling = local_problem(name, ctx.rank, ctx.world)
+    dev = ctx.dev
+    fn = flash_msa_b200.flash_msa_warmup_func if cfg["dense"] else flash_msa_b200.flash_msa_func
+    top_k = cfg["kb"] * 128
+    host = make_inputs(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], seed=ctx.rank,
+                       dtype=torch.bfloat16)
+    host = [t.pin_memory() for t in host]
+    qp, kp, q, k, v, do = [t.to(dev) for t in host]
+    ones = torch.ones((), device=dev)
+
+    def step():
+        leaves = [t.detach().requires_grad_(True) for t in (qp, kp, q, k, v)]
+        out, kl = fn(*leaves, top_k, SCALE)
+        torch.autograd.backward([out, kl], [do, ones])
+
+    for _ in range(warmup):
+        step()
+    ctx.sync_all()
+    sampler = ClockSampler(ctx.local_rank) if (sample_clocks and ctx.rank == 0) else None
+    if sampler:
+        sampler.start()
+    torch.cuda.reset_peak_memory_stats(dev)
+    ops.KERNEL_EVENTS = []
+    launches0 = ops.LAUNCHES
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx.sync_all()
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    ctx.sync_all()
+    elapsed_ms = ctx.max_over_ranks(start.elapsed_time(end))
+    res = {"cfg": cfg, "local": local, "scaling": scaling, "steps": steps, "ms_per_step": elapsed_ms / steps,
+           "launches": ops.LAUNCHES - launches0, "clocks": sampler.stop() if sampler else None,
+           "peak_mem_gib": torch.cuda.max_memory_allocated(dev) / 2 ** 30}
+    events, ops.KERNEL_EVENTS = ops.KERNEL_EVENTS, None
+    per_kernel = {}
+    for kname, s_, e_ in events:
+        per_kernel.setdefault(kname, []).append(s_.elapsed_time(e_))
+    res["per_kernel"] = per_kernel
+    step_total = sum(sum(v_) for v_ in per_kernel.values()) / steps
+    res["kernels"] = {n: {"ms_per_step": sum(v_) / steps, "share": (sum(v_) / steps) / step_total if step_total else None}
+                      for n, v_ in sorted(per_kernel.items())}
+
+    # ---- end to end: host buffers, copies inside the timed region ----
+    if with_e2e:
+        # the repo's host-buffer call: pinned host tensors in, pinned host tensors out, copies and kernels
+        # pipelined over (batch, KV-group) chunks on three streams (flash_msa_b200/host.py)
+        from flash_msa_b200.host import HostStep
+        hs = HostStep(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], top_k, SCALE,
+                      dense=cfg["dense"], device=dev)
+        hs.run(*host, grad_kl=1.0)
+        hs.synchronize()
+        ctx.sync_all()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(2, min(steps, 5))
+        s2.record()
+        for _ in range(n_e2e):
+            hs.run(*host, grad_kl=1.0)
+        # the step ends when the last result has reached host memory
+        torch.cuda.current_stream().wait_stream(hs.s_out)
+        torch.cuda.current_stream().wait_stream(hs.s_cmp)
+        e2.record()
+        ctx.sync_all()
+        e2e_ms = ctx.max_over_ranks(s2.elapsed_time(e2))
+        h2d, d2h = hs.bytes_per_step()
+        # Copy-only floor: the same bytes as one contiguous pinned copy per tensor in each direction, both
+        # directions at once, every rank at the same time.  What the host link gives whatever the kernels do.
+        outs_dev = [torch.empty_like(t, device=dev) for t in hs.host_out]
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        dev_in = [qp, kp, q, k, v, do]
+
+        def copies():
+            with torch.cuda.stream(s_in):
+                for d_, h_ in zip(dev_in, host):
+                    d_.copy_(h_, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                for h_, d_ in zip(hs.host_out, outs_dev):
+                    h_.copy_(d_, non_blocking=True)
+
+        copies()
+        ctx.sync_all()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(3):
+            copies()
+        torch.cuda.current_stream().wait_stream(s_in)
+        torch.cuda.current_stream().wait_stream(s_out)
+        c1.record()
+        ctx.sync_all()
+        floor_ms = ctx.max_over_ranks(c0.elapsed_time(c1)) / 3
+        total_f = flops(cfg) * (ctx.world if scaling == "weak" else 1)
+        res["e2e"] = {"value": total_f * n_e2e / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                      "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e, "copy_floor_ms": floor_ms}
+        del hs, outs_dev
+    del qp, kp, q, k, v, do, host
+    torch.cuda.empty_cache()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -280,10 +559,15 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-strong-c5", action="store_true", help="skip the config-5 strong-scaling measurement of the default run")
     ap.add_argument("--micro-select", action="store_true", help="time the top-k and reverse-index kernels at config-5 size")
+    ap.add_argument("--ref-kernels", action="store_true", help="try the reference's own GPU kernels beside ours (needs oracle/_ref)")
     args = ap.parse_args()
     if args.micro_select:
         micro_select(args)
+        return
+    if args.ref_kernels:
+        ref_kernels(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
     cfg = dict(WORKLOADS[args.workload])
@@ -292,157 +576,64 @@ def main():
         reference_arm(args, cfg)
         return
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (flash_msa_b200 has no CPU path)")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+    ctx = GpuContext()
+    main_res = time_workload(ctx, args.workload, args.steps, args.warmup, with_e2e=not args.no_e2e, sample_clocks=True)
+    # Config 5 (long context, one global problem split by KV group) next to the headline: the strong-scaling curve
+    # comes from running this same command at 1, 2, 4 and 8 GPUs.
+    strong = None
+    if args.workload == "c2" and not args.no_strong_c5 and WORKLOADS["c5"]["hkv"] % ctx.world == 0:
+        strong = time_workload(ctx, "c5", max(2, min(args.steps, 5)), 2, with_e2e=False, sample_clocks=False)
 
-    import flash_msa_b200
-    from flash_msa_b200 import ops
-    from flash_msa_b200.sharding import shard_workload
-    from oracle.msa_oracle import make_inputs
-
-    # strong-scaling workload (c5): one global problem split by KV group; others: one full problem per rank
-    local = shard_workload(cfg, rank, world) if args.workload == "c5" else dict(cfg)
-    scaling = "strong" if args.workload == "c5" else "weak"
-    fn = flash_msa_b200.flash_msa_warmup_func if cfg["dense"] else flash_msa_b200.flash_msa_func
-    top_k = cfg["kb"] * 128
-
-    host = make_inputs(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], seed=rank,
-                       dtype=torch.bfloat16)
-    host = [t.pin_memory() for t in host]
-    devt = [t.to(dev) for t in host]
-    qp, kp, q, k, v, do = devt
-    ones = torch.ones((), device=dev)
-
-    def step():
-        leaves = [t.detach().requires_grad_(True) for t in (qp, kp, q, k, v)]
-        out, kl = fn(*leaves, top_k, SCALE)
-        torch.autograd.backward([out, kl], [do, ones])
-        return out, [t.grad for t in leaves]
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    sync_all()
-
-    # ---- timed region: device-resident inputs ----
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    ops.KERNEL_EVENTS = []
-    launches0 = ops.LAUNCHES
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    start.record()
-    for _ in range(args.steps):
-        step()
-    end.record()
-    sync_all()
-    elapsed_ms = start.elapsed_time(end)
-    launches = ops.LAUNCHES - launches0
-    events = ops.KERNEL_EVENTS
-    ops.KERNEL_EVENTS = None
-    clocks = sampler.stop() if rank == 0 else None
-    per_kernel = {}
-    for name, s, e in events:
-        per_kernel.setdefault(name, []).append(s.elapsed_time(e))
-    if dist is not None:
-        t = torch.tensor([elapsed_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-
-    # ---- end to end: host buffers, copies inside the timed region ----
-    e2e = None
-    if not args.no_e2e:
-        # the repo's host-buffer call: pinned host tensors in, pinned host tensors out, copies and kernels
-        # pipelined over (batch, KV-group) chunks on three streams (flash_msa_b200/host.py)
-        from flash_msa_b200.host import HostStep
-        hs = HostStep(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], top_k, SCALE,
-                      dense=cfg["dense"], device=dev)
-
-        def e2e_step():
-            return hs.run(*host, grad_kl=1.0)
-
-        e2e_step()
-        hs.synchronize()
-        sync_all()
-        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_e2e = max(2, min(args.steps, 5))
-        s2.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        # the step ends when the last result has reached host memory
-        torch.cuda.current_stream().wait_stream(hs.s_out)
-        torch.cuda.current_stream().wait_stream(hs.s_cmp)
-        e2.record()
-        sync_all()
-        e2e_ms = s2.elapsed_time(e2)
-        if dist is not None:
-            t = torch.tensor([e2e_ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-        h2d, d2h = hs.bytes_per_step()
-        total_f = flops(cfg) * (world if scaling == "weak" else 1)
-        e2e = {"value": total_f * n_e2e / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e}
-
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+    if ctx.rank != 0:
+        if ctx.dist is not None:
+            ctx.dist.destroy_process_group()
         return
 
+    world = ctx.world
+    cfg, local, scaling = main_res["cfg"], main_res["local"], main_res["scaling"]
     peaks = measured_peaks()
     total_flops = flops(cfg) * (world if scaling == "weak" else 1)
-    ms_per_step = elapsed_ms / args.steps
+    ms_per_step = main_res["ms_per_step"]
     value = total_flops / (ms_per_step * 1e-3) / 1e12
     tokens = cfg["b"] * cfg["s"] * (world if scaling == "weak" else 1)
 
     # dominant kernel: the fused backward.  Algorithmic FLOPs per launch = 5 products over the
     # selected pairs of this rank's problem.
-    bwd_times = per_kernel.get("attn_bwd", [float("nan")])
-    bwd_ms_step = sum(bwd_times) / args.steps            # all launches of one step (large problems run in passes)
-    bwd_launches = len(bwd_times) / args.steps
+    bwd_times = main_res["per_kernel"].get("attn_bwd", [float("nan")])
+    bwd_ms_step = sum(bwd_times) / main_res["steps"]     # all launches of one step (large problems run in passes)
+    bwd_launches = len(bwd_times) / main_res["steps"]
     bwd_flops = flops(local) * 5.0 / 7.0
     achieved = bwd_flops / (bwd_ms_step * 1e-3) / 1e12
-    traffic = BWD_TRAFFIC_BYTES_C2 if (args.workload == "c2" and bwd_launches == 1) else None
+    traffic = bwd_traffic_bytes(args.workload) if bwd_launches == 1 else None
     roofline = {"kernel": "sparse_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": traffic,
                 "peak_source": f"{peaks['source']} (burst cuBLAS bf16)", "ms_per_launch": bwd_ms_step / bwd_launches,
                 "launches_per_step": bwd_launches}
-    step_total = sum(sum(v) for v in per_kernel.values()) / args.steps
-    breakdown = {n: {"ms_per_step": sum(v) / args.steps, "share": (sum(v) / args.steps) / step_total if step_total else None}
-                 for n, v in sorted(per_kernel.items())}
 
     line = {
         "metric": "sparse_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": cfg["desc"], "sharding": "(batch, KV-head group), no collective on the kernel path",
-                   "l2": "inputs larger than L2 (no flush needed)", "per_rank": local},
+        "config": config_of(cfg, local),
         "tokens_per_s": tokens / (ms_per_step * 1e-3),
         "frac_of_peak": value / (peaks["bf16_tflops"] * world),
-        "roofline": roofline, "kernels": breakdown, "clocks": clocks, "gpu_launches": launches,
+        "roofline": roofline, "kernels": main_res["kernels"], "clocks": main_res["clocks"],
+        "gpu_launches": main_res["launches"], "peak_mem_gib": main_res["peak_mem_gib"],
     }
-    if e2e is not None:
-        line["e2e"] = e2e
+    if "e2e" in main_res:
+        line["e2e"] = main_res["e2e"]
+    if strong is not None:
+        c5 = strong["cfg"]
+        t5 = strong["ms_per_step"] * 1e-3
+        line["strong_c5"] = {"workload": c5["desc"], "n_gpus": world, "scaling": "strong", "steps": strong["steps"],
+                             "ms_per_step": strong["ms_per_step"], "tokens_per_s": c5["b"] * c5["s"] / t5,
+                             "tflops": flops(c5) / t5 / 1e12, "per_rank": strong["local"], "kernels": strong["kernels"],
+                             "peak_mem_gib": strong["peak_mem_gib"]}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = {k_: v_ for k_, v_ in run_cpu_baseline(cfg, 1, 1).items() if k_ not in ("s_per_slice", "slices")}
     print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    if ctx.dist is not None:
+        ctx.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -826,7 +826,7 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams
 }
 
 // Wide variant for Hq/Hp <= 8: one sweep over the contiguous mpp*256-byte record of each edge.
-template <int KITER>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (latency bound)
+template <int KITER, bool SPLIT>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (latency bound)
 __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_kernel(const BwdCombineParams P) {
     const int lane = threadIdx.x & 31;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -858,7 +858,8 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
         for (int i = 0; i < cnt; ++i) {
             const int64_t si = __shfl_sync(0xffffffffu, sl, i);
             if (si < 0) continue;
-            for (int part = 0; part <= P.split; ++part) {
+#pragma unroll
+            for (int part = 0; part < (SPLIT ? 2 : 1); ++part) {
                 const int64_t sp = si + part * P.part_slots;
                 const __nv_bfloat16* rec = P.dq_part + sp * P.mpp * kHeadDim;
 #pragma unroll
@@ -1083,16 +1084,19 @@ extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_pa
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
     const dim3 cg(static_cast<unsigned>(grid));
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
-    if (P.mpp <= 2)
-        bwd_combine_wide_kernel<1><<<cg, 256, 0, cst>>>(P);
-    else if (P.mpp <= 4)
-        bwd_combine_wide_kernel<2><<<cg, 256, 0, cst>>>(P);
-    else if (P.mpp <= 6)
-        bwd_combine_wide_kernel<3><<<cg, 256, 0, cst>>>(P);
-    else if (P.mpp <= 8)
-        bwd_combine_wide_kernel<4><<<cg, 256, 0, cst>>>(P);
-    else
-        bwd_combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    if (P.mpp > 8) {
+        bwd_combine_kernel<<<static_cast<unsigned>(grid), 256, 0, cst>>>(P);
+    } else if (P.split) {
+        if (P.mpp <= 2) bwd_combine_wide_kernel<1, true><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 4) bwd_combine_wide_kernel<2, true><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 6) bwd_combine_wide_kernel<3, true><<<cg, 256, 0, cst>>>(P);
+        else bwd_combine_wide_kernel<4, true><<<cg, 256, 0, cst>>>(P);
+    } else {
+        if (P.mpp <= 2) bwd_combine_wide_kernel<1, false><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 4) bwd_combine_wide_kernel<2, false><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 6) bwd_combine_wide_kernel<3, false><<<cg, 256, 0, cst>>>(P);
+        else bwd_combine_wide_kernel<4, false><<<cg, 256, 0, cst>>>(P);
+    }
     return check_launch();
 }
 
