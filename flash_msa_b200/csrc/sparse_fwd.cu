@@ -72,8 +72,8 @@ constexpr int kLimitRing = 8;
 struct FwdCtrl {
     uint64_t k_full, k_empty, v_full, v_empty, kp_full, kp_empty;
     uint64_t q_full[kFwdQStages], q_empty[kFwdQStages];
-    uint64_t s_full[2], p_full[2], s_free[2];
-    uint64_t o_full[2], o_empty[2];
+    uint64_t s_full[3], p_full[3], s_free[3];
+    uint64_t o_full, o_empty;
     uint64_t unit_full[kUnitRing];
     UnitDesc units[kUnitRing];
     uint8_t limits[kLimitRing][128];   // per chunk in flight: last visible key of each row (127 = all)
@@ -81,8 +81,8 @@ struct FwdCtrl {
     int32_t abort_flag;
 };
 
-// Roles (warp index): 0-3 softmax group A (tiles with an even running index, S accumulator 0), 4-7 softmax group B
-// (odd tiles, S accumulator 1), 8-11 output group, 12-19 row gather, 20 K/V loads, 21 MMA issue (22, 23 only take
+// Roles (warp index): 0-3 softmax group A (tiles with an even running index), 4-7 softmax group B
+// (odd tiles), 8-11 output group, 12-19 row gather, 20 K/V loads, 21 MMA issue (22, 23 only take
 // part in the block-wide steps).  A TMA row gather costs the issuing warp ~65 cycles whatever its size, so the 64
 // gathers of a tile are spread over eight warps.
 constexpr int kFwdGatherWarps = 8;
@@ -104,10 +104,13 @@ static_assert(kFwdSmemBytes <= 232448, "shared memory budget of one CTA");
 // head, then the proxy head.  Hand-offs (all mbarriers, one arrival per warp or per tcgen05.commit):
 //   gather warps  q_full[stage] (TMA bytes)  <- q_empty[stage] (commit after S)
 //   K/V warp      k_full/v_full/kp_full      <- k_empty/kp_empty (commit after the last S of a sub-unit), v_empty
-//   MMA warp      S(t+1) before P V(t); s_full[t&1], o_full[mt&1]; s_free[t&1] when tile t no longer needs its S columns
-//   softmax       p_full[t&1] when P is in TMEM (or, for a proxy tile, when S has been read)
-//   output group  o_empty[mt&1] when the O accumulator has been read
-// TMEM: S[2] at columns 0 and 128 (P overwrites the first 64 columns of its S), O[2] at 256 and 384.
+//   MMA warp      S runs two tiles ahead of P V; s_full[t%3], o_full; s_free[t%3] when tile t no longer needs its S columns
+//   softmax       p_full[t%3] when P is in TMEM (or, for a proxy tile, when S has been read)
+//   output group  o_empty when the O accumulator has been read
+// TMEM: three S accumulators at columns 0, 128 and 256 (tile t uses number t%3; P overwrites the first 64 columns of
+// its S), one O accumulator at 384.  With three S accumulators the product S(t+2) does not have to wait for P V(t),
+// so a softmax group finds its next S finished when it comes back for it; the price is a single O accumulator, i.e.
+// P V(t+1) waits until O(t) has been read out, which takes far less time than a softmax.
 // The register file is re-divided between the warpgroups (setmaxnreg): the softmax and output groups get what the
 // gather and issue warps do not need.
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -140,13 +143,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             mbar_init(BAR(sm->q_full[i]), kFwdGatherWarps);
             mbar_init(BAR(sm->q_empty[i]), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 3; ++i) {
             mbar_init(BAR(sm->s_full[i]), 1);
             mbar_init(BAR(sm->p_full[i]), 4);
             mbar_init(BAR(sm->s_free[i]), 1);
-            mbar_init(BAR(sm->o_full[i]), 1);
-            mbar_init(BAR(sm->o_empty[i]), 4);
         }
+        mbar_init(BAR(sm->o_full), 1);
+        mbar_init(BAR(sm->o_empty), 4);
         for (int i = 0; i < kUnitRing; ++i) mbar_init(BAR(sm->unit_full[i]), 1);
         sm->abort_flag = 0;
         fence_mbar_init();
@@ -165,7 +168,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm->tmem_slot;
-    const uint32_t tmem_s0 = tmem, tmem_o0 = tmem + 256;
+    const uint32_t tmem_s0 = tmem, tmem_o0 = tmem + 384;
 
     const int hpc = P.mpp + (P.with_proxy ? 1 : 0);   // tiles per chunk
     const int lse_stride = P.mpp + 1;
@@ -214,6 +217,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     uint32_t cbase = 0;  // chunks of the sub-units seen so far: the row limits of chunk c of a sub-unit live in ring
                          // entry (cbase + c - chunk0) % kLimitRing
     uint32_t qs = 0, qph = 0;   // gather warps / MMA warp: Q stage of tile gt and the phase bit of its barriers
+    uint32_t sb = 0, sph = 0;   // MMA warp / softmax groups: S accumulator of tile gt (gt % 3) and the phase bit of its barriers
 
     // Next sub-unit of the common sequence (false: no more work, or the CTA is giving up).  The first gather warp draws
     // the work and publishes the decoded sub-unit; it passes over sub-units that lie beyond the end of their row, so
@@ -267,56 +271,67 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                 const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
                 wait(BAR(sm->k_full), nsub & 1, 5);
                 bool kp_ready = false, v_ready = false;
-                uint32_t gts = gt;   // running index of the next S to issue
-                int hs = 0;          // its head
+                uint32_t gts = gt;            // running index of the next S to issue, its accumulator and phase bit
+                uint32_t ssb = sb, ssph = sph;
+                int hs = 0;                   // its head
+                int s_issued = 0;
                 auto next_s = [&]() {
+                    if (s_issued == ntiles) return;
                     const bool proxy = hs == P.mpp;
                     if (proxy && !kp_ready) {
                         wait(BAR(sm->kp_full), nsub & 1, 5);
                         kp_ready = true;
                     }
                     wait(BAR(sm->q_full[qs]), qph, 1);
-                    if (gts >= 2) wait(BAR(sm->s_free[gts & 1]), ((gts >> 1) - 1) & 1, 2);
+                    if (gts >= 3) wait(BAR(sm->s_free[ssb]), ssph ^ 1, 2);
                     tc_fence_after_sync();
                     if (!bad) {
-                        umma_tile_128<false, false>(tmem_s0 + (gts & 1) * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k,
-                                                    false, elect);
-                        umma_commit(BAR(sm->s_full[gts & 1]), elect);
+                        umma_tile_128<false, false>(tmem_s0 + ssb * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k, false,
+                                                    elect);
+                        umma_commit(BAR(sm->s_full[ssb]), elect);
                         umma_commit(BAR(sm->q_empty[qs]), elect);
                     }
                     if (++qs == kFwdQStages) {
                         qs = 0;
                         qph ^= 1;
                     }
+                    if (++ssb == 3) {
+                        ssb = 0;
+                        ssph ^= 1;
+                    }
                     ++gts;
                     if (++hs == hpc) hs = 0;
+                    if (++s_issued == ntiles && !bad) {
+                        umma_commit(BAR(sm->k_empty), elect);    // every S of this sub-unit has been issued
+                        umma_commit(BAR(sm->kp_empty), elect);
+                    }
                 };
+                next_s();
                 next_s();
                 int hh = 0;
                 for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
                     const bool is_proxy = hh == P.mpp;
-                    if (t + 1 < ntiles) {
-                        next_s();   // S of the next tile first: the softmax groups never starve
-                    } else if (!bad) {
-                        umma_commit(BAR(sm->k_empty), elect);    // every S of this sub-unit has been issued
-                        umma_commit(BAR(sm->kp_empty), elect);
-                    }
-                    wait(BAR(sm->p_full[gt & 1]), (gt >> 1) & 1, 3);
+                    next_s();   // S runs two tiles ahead: the softmax groups never starve
+                    wait(BAR(sm->p_full[sb]), sph, 3);
                     if (!is_proxy) {
                         if (!v_ready) {
                             wait(BAR(sm->v_full), nsub & 1, 5);
                             v_ready = true;
                         }
-                        if (mt >= 2) wait(BAR(sm->o_empty[mt & 1]), ((mt >> 1) - 1) & 1, 4);
+                        if (mt >= 1) wait(BAR(sm->o_empty), (mt - 1) & 1, 4);
                         tc_fence_after_sync();
                         if (!bad) {
-                            const uint32_t ts = tmem_s0 + (gt & 1) * 128;
-                            umma_tile_128_ts<true>(tmem_o0 + (mt & 1) * 128, ts, ts + 32, tile_v, false, elect);   // O = P V_j
-                            umma_commit(BAR(sm->o_full[mt & 1]), elect);
+                            const uint32_t ts = tmem_s0 + sb * 128;
+                            umma_tile_128_ts<true>(tmem_o0, ts, ts + 32, tile_v, false, elect);   // O = P V_j
+                            umma_commit(BAR(sm->o_full), elect);
                         }
                         ++mt;
                     }
-                    if (!bad) umma_commit(BAR(sm->s_free[gt & 1]), elect);
+                    if (!bad) umma_commit(BAR(sm->s_free[sb]), elect);
+                    if (++sb == 3) {
+                        sb = 0;
+                        sph ^= 1;
+                    }
                     if (++hh == hpc) hh = 0;
                 }
                 if (!bad) umma_commit(BAR(sm->v_empty), elect);
@@ -414,9 +429,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     const int nrows = min(kBlock, ud.n - chunk * kBlock);
                     const int64_t slot0 = slot_base + static_cast<int64_t>(chunk) * kBlock;
                     const bool full = nrows == kBlock;
-                    const uint32_t to = tmem_o0 + (mt & 1) * 128;
+                    const uint32_t to = tmem_o0;
                     if (otid == 0) tma_store_wait_read();   // the staging tile's previous store has read it
-                    wait(BAR(sm->o_full[mt & 1]), (mt >> 1) & 1);
+                    wait(BAR(sm->o_full), mt & 1);
                     bad = group_or(1, bad);
                     if (bad) break;
                     tc_fence_after_sync();
@@ -442,7 +457,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         }
                     }
                     tc_fence_before_sync();
-                    warp_arrive(BAR(sm->o_empty[mt & 1]));
+                    warp_arrive(BAR(sm->o_empty));
                     if (full) {
                         fence_async_smem();
                         named_barrier_sync(1, 128);
@@ -465,7 +480,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         reg_inc<kFwdRegsSoftmax>();
         // =========================== softmax groups ===========================
         const uint32_t wg = static_cast<uint32_t>(warp >> 2);
-        const uint32_t ts = tmem_s0 + wg * 128;
         const float2 sc2 = make_float2(P.scale_log2e, P.scale_log2e);
         UnitDesc ud;
         for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
@@ -474,9 +488,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             int hh = 0, chunk = ud.chunk0;
             for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
                 if ((gt & 1) == wg) {
+                    const uint32_t ts = tmem_s0 + sb * 128;
                     const bool is_proxy = hh == P.mpp;
                     const int nrows = min(kBlock, ud.n - chunk * kBlock);
-                    wait(BAR(sm->s_full[wg]), (gt >> 1) & 1);
+                    wait(BAR(sm->s_full[sb]), sph);
                     if (bad) break;
                     tc_fence_after_sync();
                     // only the first chunk of a reverse-index row can hold rows of the key block itself
@@ -533,11 +548,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     }
                     if (!is_proxy) tmem_st_wait();
                     tc_fence_before_sync();
-                    warp_arrive(BAR(sm->p_full[wg]));
+                    warp_arrive(BAR(sm->p_full[sb]));
                     if (row < nrows) {
                         const int64_t slot = slot_base + static_cast<int64_t>(chunk) * kBlock + row;
                         reinterpret_cast<float2*>(P.stat_part)[slot * lse_stride + hh] = make_float2(m, l);
                     }
+                }
+                if (++sb == 3) {
+                    sb = 0;
+                    sph ^= 1;
                 }
                 if (++hh == hpc) {
                     hh = 0;
