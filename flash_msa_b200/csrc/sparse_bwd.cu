@@ -78,7 +78,7 @@ struct BwdUnit {
 constexpr int kBwdUnitRing = 8;
 
 // Per-tile facts about the 128 gathered query rows (= TMEM columns), staged for the compute groups.
-struct BwdRowStats {
+struct alignas(16) BwdRowStats {   // (filled and read with 16-byte vector accesses)
     float neg_lse[128];    // -lse * log2(e); -inf for a dead row, whose probabilities then come out as 0
     float neg_delta[128];  // -delta
     uint8_t limit[128];    // last visible key of the row inside this key block (127 = all)

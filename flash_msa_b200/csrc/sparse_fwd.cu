@@ -76,7 +76,7 @@ struct FwdCtrl {
     uint64_t o_full, o_empty;
     uint64_t unit_full[kUnitRing];
     UnitDesc units[kUnitRing];
-    uint8_t limits[kLimitRing][128];   // per chunk in flight: last visible key of each row (127 = all)
+    alignas(16) uint8_t limits[kLimitRing][128];   // per chunk in flight: last visible key of each row (127 = all)
     uint32_t tmem_slot;
     int32_t abort_flag;
 };
