@@ -107,7 +107,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
 static __device__ __forceinline__ bool mbar_wait_poll_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
-        if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+        // a burst of parked tries between two looks at the clock and the abort flag: the waiting roles of a
+        // warp-specialised kernel should cost the working ones as few issue slots as possible
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i)
+            if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
         if (*abort_flag) return false;
         if (global_timer_ns() - t0 > kWaitLimitNs) {
             *abort_flag = 1;
