@@ -78,7 +78,7 @@ def _declare(lib):
     lib.fmsa_bwd_delta.restype = c_int
     lib.fmsa_bwd_delta.argtypes = [P, T, P, c_int32, c_int32, c_int32, P]
     lib.fmsa_sparse_bwd.restype = c_int
-    lib.fmsa_sparse_bwd.argtypes = [PB, T, T, T, T, T, T, P, P, P, P, P, P, P, c_int64, c_int32, P, P, P, P, P, c_int32, c_int32,
+    lib.fmsa_sparse_bwd.argtypes = [PB, T, T, T, T, T, T, P, P, P, P, P, P, P, c_int64, c_int32, P, P, P, c_int32, c_int32,
                                     c_int32, c_int32, P, P, P, P]
     lib.fmsa_sparse_bwd_combine.restype = c_int
     lib.fmsa_sparse_bwd_combine.argtypes = [PB, P, P, c_int64, c_int32, P, P, P, P, P, c_int32, c_int32, c_int32, P]

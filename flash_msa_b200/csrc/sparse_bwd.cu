@@ -54,8 +54,6 @@ struct BwdParams {
     __nv_bfloat16* dq_part;    // [(edge - edge_base) * mpp + head][128]: per-edge dQ contributions (unscaled)
     __nv_bfloat16* dqp_part;   // [(edge - edge_base)][128]: per-edge dQp contributions (unscaled)
     int64_t part_slots;        // slots per plane of the two buffers above
-    float *dq_acc, *dqp_acc;   // reduce mode (non-null dq_acc): fp32, zero-initialised [B,Hq,S,128] and [B,Hp,S,128]; dQ and dQp
-                               // are added to them with vector reductions instead of leaving as partial rows
     int split;                 // 1: every contribution is stored as a bf16 pair (value, rounding remainder) in two planes
     // fp32, zero-initialised: [B,Hpkv,S,128], [B,Hkv,S,128] x2
     float *dkp_acc, *dk_acc, *dv_acc;
@@ -198,7 +196,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     const uint32_t r0 = tmem, r1 = tmem + 128, r2 = tmem + 256, r3 = tmem + 384;
 
     const int hpc = P.mpp + (P.with_kl ? 1 : 0);   // tiles per chunk
-    const bool reduce_dq = P.dq_acc != nullptr;
     const int64_t edge_base = P.dense ? dense_edge_base(static_cast<int64_t>(P.g_begin) * P.ppk, P.S, P.NB)
                                       : static_cast<int64_t>(P.row_ptr[static_cast<int64_t>(P.g_begin) * P.ppk * P.NB]);
     volatile int* abort_flag = &sm->abort_flag;
@@ -245,9 +242,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
     // work and publishes the decoded sub-unit; it passes over sub-units that lie beyond the end of their row, so
     // every published entry has work (or is the end marker).  The roles are at most a few tiles apart, fewer than the
     // ring has entries.
-    auto next_unit = [&](uint32_t draw, BwdUnit& ud) -> bool {
+    auto next_unit = [&](uint32_t draw, BwdUnit& ud, auto may_draw) -> bool {
         const uint32_t uslot = draw & (kBwdUnitRing - 1);
-        if (warp == 12 && lane == 0) {
+        if (decltype(may_draw)::value && warp == 12 && lane == 0) {
             BwdUnit nu;
             nu.chunk1 = -1;
             for (;;) {
@@ -300,7 +297,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         if (warp == 17) {
             // =========================== MMA issue ===========================
             BwdUnit ud;
-            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
                 const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
                 wait(BAR(sm->k_full), nsub & 1, 6);
                 wait(BAR(sm->v_full), nsub & 1, 6);
@@ -339,16 +336,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                             umma_commit(BAR(sm->do_empty[s]), elect);
                             umma_tile_128_ts<true>(r3, r1, r1 + 64, tq, t != 0, elect);     // dK += dS^T Q_g
                             umma_commit(BAR(sm->q_empty[s]), elect);
-                            if (reduce_dq) umma_tile_128<true, true>(r0, tile_k, tile_ds, false, elect);   // dQ^T = K_j^T dS^T (lane = head dim)
-                            else umma_tile_128<true, true>(r0, tile_ds, tile_k, false, elect);          // dQ = dS K_j (lane = query)
+                            umma_tile_128<true, true>(r0, tile_ds, tile_k, false, elect);   // dQ = dS K_j
                             umma_commit(BAR(sm->dq_full), elect);
                         }
                     } else {
                         if (!bad) {
                             umma_tile_128<true, false>(r1, tq, tile_ds, false, elect);      // dKp^T = Qp_g^T dSp  (lane = head dim)
                             umma_commit(BAR(sm->dkp_full), elect);
-                            if (reduce_dq) umma_tile_128<true, true>(r0, tdo, tile_ds, false, elect);   // dQp^T = Kp_j^T dSp^T
-                            else umma_tile_128<true, true>(r0, tile_ds, tdo, false, elect);          // dQp = dSp Kp_j
+                            umma_tile_128<true, true>(r0, tile_ds, tdo, false, elect);      // dQp = dSp Kp_j
                             umma_commit(BAR(sm->dq_full), elect);
                             umma_commit(BAR(sm->q_empty[s]), elect);
                             umma_commit(BAR(sm->do_empty[s]), elect);
@@ -366,7 +361,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         } else if (warp == 16) {
             // =========================== K / V loads, row statistics ===========================
             BwdUnit ud;
-            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
                 const int64_t bp = static_cast<int64_t>(ud.b) * P.Hp + ud.p;
                 if (nsub > 0) wait(BAR(sm->kv_empty), (nsub - 1) & 1, 1);
                 if (!bad && lane == 0) {
@@ -425,7 +420,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
         const int quad = (lane >> 1) & 7, panel = lane & 1;
         const bool q_lane = lane >= 16;
         BwdUnit ud;
-        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+        for (uint32_t draw = 0; next_unit(draw, ud, std::true_type{}); ++draw, ++nsub) {
             const int64_t q_base = static_cast<int64_t>(ud.b) * P.q_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.q_row_h;
             const int64_t do_base = static_cast<int64_t>(ud.b) * P.do_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.do_row_h;
             const int64_t qp_base = static_cast<int64_t>(ud.b) * P.qp_row_b + static_cast<int64_t>(ud.p) * P.qp_row_h;
@@ -499,7 +494,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
             }
         };
         BwdUnit ud;
-        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+        for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
             const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
             const int64_t slot_base = ud.e0 - edge_base;
             const int kph = ud.p / P.pg;
@@ -535,52 +530,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                 bad = group_or(1, bad);
                 if (bad) break;
                 tc_fence_after_sync();
-                if (reduce_dq) {
-                    if (otid == 0) mbar_arrive(BAR(sm->ds_free));   // dQ has been computed: the dS^T tile is reusable
-                    // dQ^T (dQp^T): lane = head-dimension index, column = gathered query row.  The 32 lanes of a warp add
-                    // to 32 consecutive floats of one accumulator row per instruction (the row's query position is
-                    // read once per column, the same for every lane).  Two 32-column pieces are held at a time so that
-                    // the accumulator is handed back to the issuer as early as the registers allow.
-                    float* base = is_proxy ? P.dqp_acc + (static_cast<int64_t>(ud.b) * P.Hp + ud.p) * P.S * kHeadDim + row
-                                           : P.dq_acc + (static_cast<int64_t>(ud.b) * P.Hq + ud.p * P.mpp + hh) * P.S * kHeadDim + row;
-                    const int32_t* qrow = P.col_q + ud.e0 + static_cast<int64_t>(chunk) * kBlock;
-                    const int q_dense0 = ud.j * kBlock + chunk * kBlock;
-                    // lane l fetches the query position of column c + l (one coalesced load per piece); the positions
-                    // then go round the warp by shuffle, so that no reduction waits for a load of its own
-                    auto piece_rows = [&](int c) -> int {
-                        const int col = c + lane;
-                        if (col >= nrows) return -1;
-                        const int qid = P.dense ? (q_dense0 + col) : __ldg(qrow + col);
-                        return static_cast<unsigned>(qid) < static_cast<unsigned>(P.S) ? qid : -1;
-                    };
-                    auto add_piece = [&](const uint32_t (&v)[32], int qmine) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int qid = __shfl_sync(0xffffffffu, qmine, i);
-                            if (qid >= 0) atomicAdd(base + static_cast<int64_t>(qid) * kHeadDim, __uint_as_float(v[i]));
-                        }
-                    };
-                    const int q0 = piece_rows(0), q1 = piece_rows(32), q2 = piece_rows(64), q3 = piece_rows(96);
-                    uint32_t va[32], vb[32];
-                    tmem_ld32(tmem_addr(r0, quarter, 0), va);
-                    tmem_ld32(tmem_addr(r0, quarter, 32), vb);
-                    tmem_ld_wait();
-                    add_piece(va, q0);
-                    tmem_ld32(tmem_addr(r0, quarter, 64), va);
-                    add_piece(vb, q1);
-                    tmem_ld_wait();
-                    tmem_ld32(tmem_addr(r0, quarter, 96), vb);
-                    tmem_ld_wait();
-                    tc_fence_before_sync();
-                    warp_arrive(BAR(sm->r0_free));
-                    add_piece(va, q2);
-                    add_piece(vb, q3);
-                    if (++hh == hpc) {
-                        hh = 0;
-                        ++chunk;
-                    }
-                    continue;
-                }
                 // With `split` the row leaves twice: rounded to bf16, and the remainder of that rounding (a second plane of
                 // the partial buffers, `part_slots` slots further on), so that the sum over many edges keeps fp32-like accuracy.
                 const int nparts = P.split ? 2 : 1;
@@ -670,7 +619,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
 #pragma unroll
         for (int i = 0; i < 32; ++i) teacher[i] = __floats2half2_rn(0.f, 0.f);
         BwdUnit ud;
-        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+        for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
             const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
             int hh = 0, chunk = ud.chunk0;
             for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
@@ -1036,19 +985,18 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
                                const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out,
                                const float* lse, const float* lse_proxy, const float* delta, const int32_t* row_ptr,
                                const int32_t* col_q, void* dq_part, void* dqp_part, int64_t part_slots, int32_t split,
-                               float* dq_acc, float* dqp_acc, float* dkp_acc, float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
+                               float* dkp_acc, float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
                                int32_t dense, float* kl_value, int32_t* counter, int32_t* status, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(problem_ok(pb));
     FMSA_REQUIRE(q && k && v && d_out && q->ptr && k->ptr && v->ptr && d_out->ptr);
-    FMSA_REQUIRE(lse && delta && (dq_part || dq_acc) && dk_acc && dv_acc && counter && status);
+    FMSA_REQUIRE(lse && delta && dq_part && dk_acc && dv_acc && counter && status);
     FMSA_REQUIRE(dense || (row_ptr && col_q));
-    FMSA_REQUIRE(!with_kl || (q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && lse_proxy && dkp_acc &&
-                              (dq_acc ? dqp_acc != nullptr : dqp_part != nullptr)));
+    FMSA_REQUIRE(!with_kl || (q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && lse_proxy && dqp_part && dkp_acc));
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
     FMSA_REQUIRE(dense || (pb->top_k_blocks >= 1 && pb->top_k_blocks <= pb->S / kBlock));
     FMSA_REQUIRE(pb->scale > 0.f);
-    if (!dq_acc && part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
+    if (part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
     FMSA_REQUIRE(tma_compatible(k->ptr, k->stride_b, k->stride_h, k->stride_s));
     FMSA_REQUIRE(tma_compatible(v->ptr, v->stride_b, v->stride_h, v->stride_s));
     FMSA_REQUIRE(tma_compatible(q->ptr, q->stride_b, q->stride_h, q->stride_s));
@@ -1058,14 +1006,6 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
         FMSA_REQUIRE(tma_compatible(k_proxy->ptr, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s));
     }
     FMSA_REQUIRE(aligned16(dk_acc) && aligned16(dv_acc) && (!with_kl || aligned16(dkp_acc)));
-    if (dq_acc) {
-        FMSA_REQUIRE(aligned16(dq_acc) && (!with_kl || aligned16(dqp_acc)));
-        // the tile-store maps are not used in this mode; give them something valid to describe
-        dq_part = dq_acc;
-        dqp_part = dq_acc;
-        part_slots = 128;
-        split = 0;
-    }
     FMSA_REQUIRE(aligned16(dq_part) && (!with_kl || aligned16(dqp_part)));
     FMSA_REQUIRE(gather_compatible(q->ptr, q->stride_b, q->stride_h, q->stride_s));
     FMSA_REQUIRE(gather_compatible(d_out->ptr, d_out->stride_b, d_out->stride_h, d_out->stride_s));
@@ -1098,7 +1038,6 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.row_ptr = row_ptr; P.col_q = col_q;
     P.dq_part = static_cast<__nv_bfloat16*>(dq_part); P.dqp_part = static_cast<__nv_bfloat16*>(dqp_part);
     P.part_slots = part_slots; P.split = split ? 1 : 0;
-    P.dq_acc = dq_acc; P.dqp_acc = dq_acc ? dqp_acc : nullptr;
     P.dkp_acc = dkp_acc; P.dk_acc = dk_acc; P.dv_acc = dv_acc;
     P.counter = counter; P.status = status;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hkv = pb->Hkv; P.Hp = pb->Hp; P.Hpkv = pb->Hpkv;

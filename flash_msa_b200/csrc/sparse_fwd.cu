@@ -91,7 +91,7 @@ constexpr int kFwdThreads = 24 * 32;
 // launched with 80 registers per thread; an increase can only be served from what the other warpgroups of the
 // same CTA gave up, so the six warpgroups must not ask for more than 6 x 80 in total (a warpgroup that asks for
 // registers nobody released waits forever).
-constexpr int kFwdRegsLaunch = 80, kFwdRegsSoftmax = 112, kFwdRegsOutput = 96, kFwdRegsGather = 48, kFwdRegsMisc = 56;
+constexpr int kFwdRegsLaunch = 80, kFwdRegsSoftmax = 128, kFwdRegsOutput = 80, kFwdRegsGather = 48, kFwdRegsMisc = 48;
 static_assert(2 * kFwdRegsSoftmax + kFwdRegsOutput + 2 * kFwdRegsGather + kFwdRegsMisc <= 6 * kFwdRegsLaunch,
               "register re-division must balance");
 static_assert(kFwdRegsLaunch == (65536 / kFwdThreads) / 8 * 8, "registers per thread at launch");
@@ -223,9 +223,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     // the work and publishes the decoded sub-unit; it passes over sub-units that lie beyond the end of their row, so
     // every published entry has work (or is the end marker).  The roles are at most a handful of tiles apart (Q stages
     // + S and O accumulators), far fewer than the ring has entries.
-    auto next_unit = [&](uint32_t draw, UnitDesc& ud) -> bool {
+    auto next_unit = [&](uint32_t draw, UnitDesc& ud, auto may_draw) -> bool {
         const uint32_t uslot = draw & (kUnitRing - 1);
-        if (warp == 12 && lane == 0) {
+        if (decltype(may_draw)::value && warp == 12 && lane == 0) {
             UnitDesc nu;
             nu.chunk1 = -1;
             for (;;) {
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         if (warp == 21) {
             // =========================== MMA issue ===========================
             UnitDesc ud;
-            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
                 const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
                 wait(BAR(sm->k_full), nsub & 1, 5);
                 bool kp_ready = false, v_ready = false;
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         } else if (warp == 20) {
             // =========================== K / V / Kp loads ===========================
             UnitDesc ud;
-            for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+            for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
                 if (nsub > 0) wait(BAR(sm->k_empty), (nsub - 1) & 1);
                 if (!bad && lane == 0) {
                     mbar_arrive_expect_tx(BAR(sm->k_full), kTileBytes);
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         const int g = warp - 12;
         const int quad = (lane >> 1) & 3, panel = lane & 1;
         UnitDesc ud;
-        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+        for (uint32_t draw = 0; next_unit(draw, ud, std::true_type{}); ++draw, ++nsub) {
             const int64_t q_base = static_cast<int64_t>(ud.b) * P.q_row_b + static_cast<int64_t>(ud.p) * P.mpp * P.q_row_h;
             const int64_t qp_base = static_cast<int64_t>(ud.b) * P.qp_row_b + static_cast<int64_t>(ud.p) * P.qp_row_h;
             for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
@@ -420,7 +420,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         // row's begin).
         const int otid = tid - 8 * 32;
         UnitDesc ud;
-        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+        for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
             const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
             const int64_t slot_base = ud.e0 - edge_base;   // slot of the first row of the reverse-index row
             int hh = 0, chunk = ud.chunk0;
@@ -482,7 +482,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
         const uint32_t wg = static_cast<uint32_t>(warp >> 2);
         const float2 sc2 = make_float2(P.scale_log2e, P.scale_log2e);
         UnitDesc ud;
-        for (uint32_t draw = 0; next_unit(draw, ud); ++draw, ++nsub) {
+        for (uint32_t draw = 0; next_unit(draw, ud, std::false_type{}); ++draw, ++nsub) {
             const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
             const int64_t slot_base = ud.e0 - edge_base;
             int hh = 0, chunk = ud.chunk0;
@@ -503,46 +503,59 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         // Two passes over the 128 logits of the row (maximum, then exponentials), software-pipelined over
                         // 32-column pieces: the TMEM load of the next piece is in flight while this one is worked on
                         // (tcgen05.wait::ld waits for every load issued so far, hence the order wait, issue, compute).
-                        uint32_t buf[2][32];
+                        // The loops run over PAIRS of pieces and are not unrolled further: the softmax code of a tile has
+                        // to stay small enough for the instruction cache, which five roles share.
+                        uint32_t ba[32], bb[32];
                         float mloc = -INFINITY;
-                        tmem_ld32(tmem_addr(ts, quarter, 0), buf[0]);
-#pragma unroll
-                        for (int c = 0; c < 128; c += 32) {
-                            const int cur = (c >> 5) & 1;
-                            tmem_ld_wait();
-                            tmem_ld32(tmem_addr(ts, quarter, (c + 32) & 127), buf[cur ^ 1]);   // (the last one fetches piece 0 again, for pass 2)
+                        auto piece_max = [&](const uint32_t (&v)[32], int c) __attribute__((always_inline)) {
                             if (kMasked) {
+                                const int lc = limit - c;
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) mloc = (c + i <= limit) ? fmaxf(mloc, __uint_as_float(buf[cur][i])) : mloc;
+                                for (int i = 0; i < 32; ++i) mloc = (i <= lc) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
                             } else {
 #pragma unroll
-                                for (int i = 0; i < 32; i += 2)
-                                    mloc = fmax3(mloc, __uint_as_float(buf[cur][i]), __uint_as_float(buf[cur][i + 1]));
+                                for (int i = 0; i < 32; i += 2) mloc = fmax3(mloc, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
                             }
+                        };
+                        tmem_ld32(tmem_addr(ts, quarter, 0), ba);
+#pragma unroll 1
+                        for (int c = 0; c < 128; c += 64) {
+                            tmem_ld_wait();
+                            tmem_ld32(tmem_addr(ts, quarter, c + 32), bb);
+                            piece_max(ba, c);
+                            tmem_ld_wait();
+                            tmem_ld32(tmem_addr(ts, quarter, (c + 64) & 127), ba);   // (the last one fetches piece 0 again, for pass 2)
+                            piece_max(bb, c + 32);
                         }
                         m = mloc * P.scale_log2e;   // raw logits: scale > 0, so the maximum commutes with it
                         const float2 nm2 = make_float2(-m, -m);
                         float2 l2 = make_float2(0.f, 0.f);
-#pragma unroll
-                        for (int c = 0; c < 128; c += 32) {
-                            const int cur = (c >> 5) & 1;
-                            tmem_ld_wait();
-                            if (c + 32 < 128) tmem_ld32(tmem_addr(ts, quarter, c + 32), buf[cur ^ 1]);
+                        auto piece_exp = [&](const uint32_t (&v)[32], int c) __attribute__((always_inline)) {
                             uint32_t pk[16];
+                            const int lc = limit - c;
 #pragma unroll
                             for (int i = 0; i < 32; i += 2) {
-                                const float2 a = f2_fma(f2_from_bits(buf[cur][i], buf[cur][i + 1]), sc2, nm2);
+                                const float2 a = f2_fma(f2_from_bits(v[i], v[i + 1]), sc2, nm2);
                                 float p0 = fast_exp2(a.x);
                                 float p1 = fast_exp2(a.y);
                                 if (kMasked) {
-                                    p0 = (c + i <= limit) ? p0 : 0.f;
-                                    p1 = (c + i + 1 <= limit) ? p1 : 0.f;
+                                    p0 = (i <= lc) ? p0 : 0.f;
+                                    p1 = (i + 1 <= lc) ? p1 : 0.f;
                                 }
                                 l2 = f2_add(l2, make_float2(p0, p1));
-                                if (!kProxy) pk[i >> 1] = pack_bf16(p0, p1);
+                                pk[i >> 1] = pack_bf16(p0, p1);
                             }
                             // P (bf16, two keys per column) over S columns this thread has already consumed
                             if (!kProxy) tmem_st16(tmem_addr(ts, quarter, c >> 1), pk);
+                        };
+#pragma unroll 1
+                        for (int c = 0; c < 128; c += 64) {
+                            tmem_ld_wait();
+                            tmem_ld32(tmem_addr(ts, quarter, c + 32), bb);
+                            piece_exp(ba, c);
+                            tmem_ld_wait();
+                            if (c == 0) tmem_ld32(tmem_addr(ts, quarter, 64), ba);
+                            piece_exp(bb, c + 32);
                         }
                         l = l2.x + l2.y;
                     }

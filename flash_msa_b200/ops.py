@@ -242,8 +242,6 @@ def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_bloc
 MAX_PARTIAL_BYTES = 8 << 30
 # Rows with more edges than this store their dQ partial rows as (value, rounding remainder) pairs.
 SPLIT_PARTIALS_ABOVE = 32
-# True: the backward adds dQ and dQp to fp32 accumulators with vector reductions (no partial rows, no combine pass).
-DQ_REDUCE = os.environ.get("FLASH_MSA_B200_DQ_REDUCE", "0") == "1"
 
 
 def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, with_proxy=True, status=None):
@@ -339,53 +337,35 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
         _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(acc.data_ptr(), dst.data_ptr(), acc.numel(), scale_ptr,
                                                           float(const_scale), st), dev)
 
-    if DQ_REDUCE:
-        # dQ and dQp accumulate in fp32 with vector reductions, like dK, dV and dKp (and like the reference)
-        dq_acc = torch.zeros(b, hq, s, d, dtype=torch.float32, device=dev)
-        dqp_acc = torch.zeros(b, hp, s, d, dtype=torch.float32, device=dev) if with_kl else None
+    # dQ and dQp leave the kernel as per-edge partial rows; a combine pass sums them per query row
+    dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
+    if with_kl:
+        dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
+    per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
+    # A query row's dQ is the sum of one bf16 partial row per selected block.  Beyond ~32 blocks the rounding of the
+    # partial rows starts to show against the reference's fp32 accumulation, so each partial is then stored as a
+    # (value, rounding remainder) pair in two planes.
+    edges_per_row = (s // BLOCK_SIZE) if dense else rix.top_k_blocks
+    split = 1 if edges_per_row > SPLIT_PARTIALS_ABOVE else 0
+    planes = 2 if split else 1
+    bytes_per_slot = (mpp + (1 if with_kl else 0)) * d * 2 * planes
+    gstep = max(1, min(groups, MAX_PARTIAL_BYTES // max(1, per_group * bytes_per_slot)))
+    slots = per_group * gstep
+    dq_part = torch.empty(planes * slots * mpp * d, dtype=q.dtype, device=dev)
+    dqp_part = torch.empty(planes * slots * d, dtype=q.dtype, device=dev) if with_kl else None
+    for g0 in range(0, groups, gstep):
+        gc = min(gstep, groups - g0)
         with _Timed("attn_bwd", dev):
             _launch("fmsa_sparse_bwd", 1, lib.fmsa_sparse_bwd(
                 ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
                 _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(), row_ptr, col_q,
-                0, 0, 0, 0, dq_acc.data_ptr(), dqp_acc.data_ptr() if with_kl else 0, dkp_acc.data_ptr() if with_kl else 0,
-                dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), 0, groups, int(with_kl), int(dense), klv, counter.data_ptr(),
-                status.data_ptr(), st), dev)
-        dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
-        with _Timed("cast", dev):
-            cast(dq_acc, dq, 0, scale)
-            if with_kl:
-                dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
-                cast(dqp_acc, dqp, gk.data_ptr(), kl_norm)
-    else:
-        # dQ and dQp leave the kernel as per-edge partial rows; a combine pass sums them per query row
-        dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
-        if with_kl:
-            dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
-        per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
-        # A query row's dQ is the sum of one bf16 partial row per selected block.  Beyond ~32 blocks the rounding of the
-        # partial rows starts to show against the reference's fp32 accumulation, so each partial is then stored as a
-        # (value, rounding remainder) pair in two planes.
-        edges_per_row = (s // BLOCK_SIZE) if dense else rix.top_k_blocks
-        split = 1 if edges_per_row > SPLIT_PARTIALS_ABOVE else 0
-        planes = 2 if split else 1
-        bytes_per_slot = (mpp + (1 if with_kl else 0)) * d * 2 * planes
-        gstep = max(1, min(groups, MAX_PARTIAL_BYTES // max(1, per_group * bytes_per_slot)))
-        slots = per_group * gstep
-        dq_part = torch.empty(planes * slots * mpp * d, dtype=q.dtype, device=dev)
-        dqp_part = torch.empty(planes * slots * d, dtype=q.dtype, device=dev) if with_kl else None
-        for g0 in range(0, groups, gstep):
-            gc = min(gstep, groups - g0)
-            with _Timed("attn_bwd", dev):
-                _launch("fmsa_sparse_bwd", 1, lib.fmsa_sparse_bwd(
-                    ctypes_byref(pb), _tensor_arg(q), _tensor_arg(k), _tensor_arg(v), _tensor_arg(qp), _tensor_arg(kp),
-                    _tensor_arg(go), lse.data_ptr(), lse_proxy.data_ptr() if with_kl else 0, delta.data_ptr(), row_ptr, col_q,
-                    dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split, 0, 0,
-                    dkp_acc.data_ptr() if with_kl else 0, dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), g0, gc, int(with_kl),
-                    int(dense), klv, counter.data_ptr(), status.data_ptr(), st), dev)
-            with _Timed("bwd_combine", dev):
-                _launch("fmsa_sparse_bwd_combine", 1, lib.fmsa_sparse_bwd_combine(
-                    ctypes_byref(pb), dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split, edge_pos, row_ptr,
-                    dq.data_ptr(), dqp.data_ptr() if with_kl else 0, gk.data_ptr() if with_kl else 0, g0, gc, int(dense), st), dev)
+                dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split,
+                dkp_acc.data_ptr() if with_kl else 0, dkv_acc[0].data_ptr(), dkv_acc[1].data_ptr(), g0, gc, int(with_kl),
+                int(dense), klv, counter.data_ptr(), status.data_ptr(), st), dev)
+        with _Timed("bwd_combine", dev):
+            _launch("fmsa_sparse_bwd_combine", 1, lib.fmsa_sparse_bwd_combine(
+                ctypes_byref(pb), dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split, edge_pos, row_ptr,
+                dq.data_ptr(), dqp.data_ptr() if with_kl else 0, gk.data_ptr() if with_kl else 0, g0, gc, int(dense), st), dev)
 
     dkv = torch.empty(2, b, hkv, s, d, dtype=q.dtype, device=dev)
     with _Timed("cast", dev):

@@ -170,11 +170,6 @@ int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int3
  *              rounding, and the combine adds both.  The sum over the edges of a row then keeps fp32-like
  *              accuracy however many blocks a row selects (the reference accumulates in fp32 atomics,
  *              flash_msa/msa_backward_cutedsl.py:738-836); use it when a row has more than ~32 edges.
- *   dq_acc     NULL, or fp32 [B,Hq,S,128] (with dqp_acc fp32 [B,Hp,S,128] when with_kl), ZEROED by the caller: dQ and
- *              dQp are then added to these accumulators with vector reductions, exactly as the reference accumulates
- *              them (flash_msa/msa_backward_cutedsl.py:738-836), dq_part / dqp_part / part_slots / split are
- *              ignored and no combine pass is needed; cast with fmsa_cast_scaled (dq_acc needs scale, dqp_acc
- *              needs scale/(B*Hp*S) times the upstream kl gradient).
  *   dkp_acc fp32 [B,Hpkv,S,128], dk_acc, dv_acc fp32 [B,Hkv,S,128]: ZEROED by the caller,
  *              accumulated with atomics (long reverse-index rows are split over several CTAs),
  *              unscaled; cast to the activation dtype with fmsa_cast_scaled (which applies the factors).
@@ -190,9 +185,9 @@ int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int3
 int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_tensor* k, const fmsa_tensor* v,
                     const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, const fmsa_tensor* d_out, const float* lse,
                     const float* lse_proxy, const float* delta, const int32_t* row_ptr, const int32_t* col_q,
-                    void* dq_part, void* dqp_part, int64_t part_slots, int32_t split, float* dq_acc, float* dqp_acc,
-                    float* dkp_acc, float* dk_acc, float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl,
-                    int32_t dense, float* kl_value, int32_t* counter, int32_t* status, void* stream);
+                    void* dq_part, void* dqp_part, int64_t part_slots, int32_t split, float* dkp_acc, float* dk_acc,
+                    float* dv_acc, int32_t g_begin, int32_t g_count, int32_t with_kl, int32_t dense, float* kl_value,
+                    int32_t* counter, int32_t* status, void* stream);
 
 /* Sums the per-edge contributions of every query row:
  *   dq bf16 [B,Hq,S,128];  dq_proxy bf16 [B,Hp,S,128] (or NULL), multiplied by *grad_kl (device

@@ -129,20 +129,3 @@ def test_kl_value(fm, name):
     finally:
         api.COMPUTE_KL_VALUE = False
 
-
-def test_reduction_mode_matches_partial_row_mode(fm):
-    """The backward can add dQ and dQp to fp32 accumulators with vector reductions instead of writing per-edge
-    partial rows for a combine pass (less memory, slower): both modes must agree to bf16 rounding."""
-    from flash_msa_b200 import ops
-    cfg = CFGS["c1"]
-    qp, kp, q, k, v, do = bf16_inputs(cfg)
-    saved = ops.DQ_REDUCE
-    try:
-        res = {}
-        for mode in (False, True):
-            ops.DQ_REDUCE = mode
-            _, res[mode], _ = _run_kernel(fm.flash_msa_func, (qp, kp, q, k, v), do, cfg["kb"] * 128, 1.0)
-    finally:
-        ops.DQ_REDUCE = saved
-    for n, a, b in zip(NAMES, res[False], res[True]):
-        assert max_err(a, b) <= 2 ** -7 * a.float().abs().max().item() + 1e-9, n
