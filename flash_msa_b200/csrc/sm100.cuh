@@ -105,15 +105,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
 // when one of its waits ran out.  Every other waiter sees it within one parking period and gives up as well,
 // so the whole CTA leaves its loops together instead of each role waiting out its own limit in turn.
 static __device__ __forceinline__ bool mbar_wait_poll_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    const uint64_t t0 = global_timer_ns();
+    // Kept as small as possible: this loop is inlined at every wait site of the warp-specialised kernels, whose
+    // code has to fit the instruction cache.  The clock and the abort flag are looked at once per 64 parked tries
+    // (a parked try returns after kParkNs at the latest), the time limit is counted in such rounds.
+    uint32_t tries = 0;
+    uint64_t t0 = 0;
     for (;;) {
-        // a burst of parked tries between two looks at the clock and the abort flag: the waiting roles of a
-        // warp-specialised kernel should cost the working ones as few issue slots as possible
-#pragma unroll 1
-        for (int i = 0; i < 16; ++i)
-            if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+        if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+        if ((++tries & 63u) != 0) continue;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > kWaitLimitNs) {
             *abort_flag = 1;
             return false;
         }
