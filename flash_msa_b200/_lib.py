@@ -13,6 +13,7 @@ LIB_PATH = os.environ.get("FLASH_MSA_B200_LIB") or os.path.join(PKG_DIR, "libfla
 HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "flash_msa_b200.h")
 
 FMSA_OK = 0
+FMSA_DTYPE_BF16, FMSA_DTYPE_FP16 = 0, 1
 _ERRORS = {
     -1: (ValueError, "invalid argument (shape, alignment or null pointer)"),
     -2: (NotImplementedError, "request outside the implemented envelope"),
@@ -68,7 +69,7 @@ def _declare(lib):
     T = ctypes.POINTER(FmsaTensor)
     PB = ctypes.POINTER(FmsaProblem)
     lib.fmsa_select_scores.restype = c_int
-    lib.fmsa_select_scores.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P]
+    lib.fmsa_select_scores.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, P, P]
     lib.fmsa_fwd_partial_slots.restype = c_int64
     lib.fmsa_fwd_partial_slots.argtypes = [PB, c_int32, c_int32]
     lib.fmsa_sparse_fwd.restype = c_int
@@ -76,14 +77,14 @@ def _declare(lib):
     lib.fmsa_sparse_fwd_combine.restype = c_int
     lib.fmsa_sparse_fwd_combine.argtypes = [PB, P, P, P, P, P, P, P, c_int32, c_int32, c_int32, P]
     lib.fmsa_bwd_delta.restype = c_int
-    lib.fmsa_bwd_delta.argtypes = [P, T, P, c_int32, c_int32, c_int32, P]
+    lib.fmsa_bwd_delta.argtypes = [P, T, P, c_int32, c_int32, c_int32, c_int32, P]
     lib.fmsa_sparse_bwd.restype = c_int
     lib.fmsa_sparse_bwd.argtypes = [PB, T, T, T, T, T, T, P, P, P, P, P, P, P, c_int64, c_int32, P, P, P, c_int32, c_int32,
                                     c_int32, c_int32, P, P, P, P]
     lib.fmsa_sparse_bwd_combine.restype = c_int
     lib.fmsa_sparse_bwd_combine.argtypes = [PB, P, P, c_int64, c_int32, P, P, P, P, P, c_int32, c_int32, c_int32, P]
     lib.fmsa_cast_scaled.restype = c_int
-    lib.fmsa_cast_scaled.argtypes = [P, P, c_int64, P, c_float, P]
+    lib.fmsa_cast_scaled.argtypes = [P, P, c_int64, P, c_float, c_int32, P]
     lib.fmsa_copy2d_async.restype = c_int
     lib.fmsa_copy2d_async.argtypes = [P, ctypes.c_size_t, P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, P]
 
@@ -91,7 +92,7 @@ def _declare(lib):
 class FmsaProblem(ctypes.Structure):
     """Mirror of ``fmsa_problem``."""
     _fields_ = [("B", c_int32), ("S", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("Hp", c_int32),
-                ("Hpkv", c_int32), ("top_k_blocks", c_int32), ("scale", c_float)]
+                ("Hpkv", c_int32), ("top_k_blocks", c_int32), ("scale", c_float), ("dtype", c_int32)]
 
 
 def check(status: int, what: str) -> None:

@@ -39,8 +39,8 @@ def _validate_inputs(q_proxy, k_proxy, q, k, v, top_k, sparse: bool):
     if n_proxy_heads < n_kv_heads or n_proxy_heads % n_kv_heads != 0:
         raise NotImplementedError("n_proxy_heads must be a multiple of n_kv_heads")
     dts = {t.dtype for t in (q_proxy, k_proxy, q, k, v)}
-    if len(dts) != 1 or q.dtype != torch.bfloat16:
-        raise TypeError(f"flash_msa_b200 supports bf16 activations of one dtype, got {sorted(map(str, dts))}")
+    if len(dts) != 1 or q.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"flash_msa_b200 supports bf16 or fp16 activations of one dtype, got {sorted(map(str, dts))}")
     num_blocks = s // BLOCK_SIZE
     if not sparse:
         return num_blocks, 0

@@ -19,7 +19,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // flash_msa/flash_msa.py:44-53 and flash_msa/warmup/flash_msa_warmup.py:34-43).
 inline bool problem_ok(const fmsa_problem* pb) {
     return pb && pb->B > 0 && pb->S > 0 && pb->S % 128 == 0 && pb->Hq > 0 && pb->Hkv > 0 && pb->Hp > 0 && pb->Hpkv > 0 &&
-           pb->Hq % pb->Hkv == 0 && pb->Hq % pb->Hp == 0 && pb->Hp % pb->Hpkv == 0 && pb->Hp % pb->Hkv == 0;
+           pb->Hq % pb->Hkv == 0 && pb->Hq % pb->Hp == 0 && pb->Hp % pb->Hpkv == 0 && pb->Hp % pb->Hkv == 0 &&
+           (pb->dtype == FMSA_DTYPE_BF16 || pb->dtype == FMSA_DTYPE_FP16);
 }
 
 // Per-device facts that never change are looked up once (the launchers run on the critical path of every step).

@@ -26,6 +26,7 @@ struct ScoreSmem {
     float stage[128][kScoreStageCols + 1];
 };
 
+template <bool FP16>
 __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                             const __grid_constant__ CUtensorMap tmap_k,
                                                             float* __restrict__ block_scores, int Hp, int pg, int S,
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
                 if (ok && j >= 2) ok = mbar_wait(smem_u32(&sm->s_empty[st]), ((j >> 1) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after_sync();
-                umma_tile_128<false, false>(tmem + st * 128, tile_q, tile_k0 + st * kTileBytes, false);
+                umma_tile_128<false, false, FP16>(tmem + st * 128, tile_q, tile_k0 + st * kTileBytes, false);
                 umma_commit(smem_u32(&sm->k_empty[st]));
                 umma_commit(smem_u32(&sm->s_full[st]));
             }
@@ -140,11 +141,12 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
 }  // namespace fmsa
 
 extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores,
-                                  int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t* status,
-                                  void* stream) {
+                                  int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype,
+                                  int32_t* status, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && block_scores && status);
     FMSA_REQUIRE(B > 0 && Hp > 0 && Hpkv > 0 && Hp % Hpkv == 0 && S > 0 && S % kBlock == 0);
+    FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
     FMSA_REQUIRE(static_cast<int64_t>(B) * Hp <= 65535);
     FMSA_REQUIRE(tma_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
     FMSA_REQUIRE(tma_compatible(k_proxy->ptr, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s));
@@ -154,11 +156,13 @@ extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor*
         return FMSA_ERR_CUDA;
     const int NB = S / kBlock;
     const size_t smem = 3 * kTileBytes + 1024 + sizeof(ScoreSmem);
-    if (cudaFuncSetAttribute(select_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
-        cudaSuccess)
-        return FMSA_ERR_CUDA;
+    const bool fp16 = dtype == FMSA_DTYPE_FP16;
+    const void* kfn = fp16 ? reinterpret_cast<const void*>(select_scores_kernel<true>)
+                           : reinterpret_cast<const void*>(select_scores_kernel<false>);
+    if (!ensure_smem_attr(kfn, smem)) return FMSA_ERR_CUDA;
     const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(B * Hp));
-    select_scores_kernel<<<grid, 192, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB,
-                                                                                scale, status);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (fp16) select_scores_kernel<true><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, status);
+    else select_scores_kernel<false><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, status);
     return check_launch();
 }

@@ -13,6 +13,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -169,10 +170,11 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 // ---------------------------------------------------------------------------------------------
 // tcgen05.mma (kind::f16: bf16 x bf16 -> fp32 in TMEM), M = 128, one CTA
 // ---------------------------------------------------------------------------------------------
-// Instruction descriptor: D fp32, A/B bf16, M = 128, N = n; a_mn / b_mn select MN-major operands.
-__host__ __device__ constexpr uint32_t umma_idesc(int n, bool a_mn, bool b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+// Instruction descriptor: D fp32, A/B bf16 (or fp16: format code 0 instead of 1), M = 128, N = n; a_mn / b_mn
+// select MN-major operands.
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool a_mn, bool b_mn, bool fp16 = false) {
+    return (1u << 4) | ((fp16 ? 0u : 1u) << 7) | ((fp16 ? 0u : 1u) << 10) | ((a_mn ? 1u : 0u) << 15) |
+           ((b_mn ? 1u : 0u) << 16) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1.
@@ -230,10 +232,10 @@ __host__ __device__ constexpr uint32_t umma_kstep(bool mn_major, int ks) {
 }
 // The eight instructions sit in ONE asm block (two predicate set-ups and two 64-bit adds per step with
 // immediate step sizes), so the issuing warp spends as few issue slots per MMA as possible.
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FP16 = false>
 __device__ __forceinline__ void umma_tile_128(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, bool accumulate,
                                               uint32_t elect = 1u) {
-    constexpr uint32_t idesc = umma_idesc(128, A_MN, B_MN);
+    constexpr uint32_t idesc = umma_idesc(128, A_MN, B_MN, FP16);
     const uint64_t a0 = A_MN ? desc_mnmajor(a_tile, 0) : desc_kmajor(a_tile, 0);
     const uint64_t b0 = B_MN ? desc_mnmajor(b_tile, 0) : desc_kmajor(b_tile, 0);
 #define FMSA_UMMA_STEP(AI, BI)                                                  \
@@ -325,10 +327,10 @@ __device__ __forceinline__ void tmem_st_wait() {
 // be split: `a_lo` is the TMEM address of reduction elements 0..63 (32 columns), `a_hi` that of
 // elements 64..127.  B is a shared-memory tile as in umma_tile_128.
 // ---------------------------------------------------------------------------------------------
-template <bool B_MN>
+template <bool B_MN, bool FP16 = false>
 __device__ __forceinline__ void umma_tile_128_ts(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_tile,
                                                  bool accumulate, uint32_t elect = 1u) {
-    constexpr uint32_t idesc = umma_idesc(128, false, B_MN);
+    constexpr uint32_t idesc = umma_idesc(128, false, B_MN, FP16);
     const uint64_t b0 = B_MN ? desc_mnmajor(b_tile, 0) : desc_kmajor(b_tile, 0);
 #define FMSA_UMMA_TS_STEP(AREG, AOFF, BI)                                       \
     "add.u32 a, " #AREG ", " #AOFF ";\n"                                        \
@@ -518,6 +520,31 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// The same for the activation type of a kernel instantiation: bf16 (FP16 = false) or fp16.  A packed pair sits in
+// one 32-bit word, the first element in the low half.
+template <bool FP16>
+__device__ __forceinline__ uint32_t pack_act(float lo, float hi) {
+    if (FP16) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    return pack_bf16(lo, hi);
+}
+template <bool FP16>
+__device__ __forceinline__ float act_round(float x) {
+    return FP16 ? __half2float(__float2half_rn(x)) : bf16_round(x);
+}
+template <bool FP16>
+__device__ __forceinline__ float act_lo(uint32_t w) {
+    if (FP16) return __low2float(*reinterpret_cast<const __half2*>(&w));
+    return __low2float(*reinterpret_cast<const __nv_bfloat162*>(&w));   // (a conversion the compiler can fold into the consumer; a shift is not)
+}
+template <bool FP16>
+__device__ __forceinline__ float act_hi(uint32_t w) {
+    if (FP16) return __high2float(*reinterpret_cast<const __half2*>(&w));
+    return __high2float(*reinterpret_cast<const __nv_bfloat162*>(&w));
+}
 
 // Stores 16 accumulator values of a TRANSPOSED tile (this lane = head-dimension index d, value i =
 // output row row0+i) as bf16: the 32 lanes of a warp write 64 contiguous bytes of one output row per

@@ -125,6 +125,7 @@ constexpr int kStatusBadSmem = 3;   // the dynamic shared memory window does not
 // st_full <- st_empty (row statistics); sdp_full (S^T and dP^T of a tile), pds_full (P^T, dS^T written), dq_full,
 // r0_free (dQ read out), ds_free (the dS^T tile, which doubles as the staging tile of the dQ store, is reusable),
 // dkp_full / r1_free (proxy tile), acc_full / acc_free (dV, dK flushed at the end of a sub-unit).
+template <bool FP16>
 __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                     const __grid_constant__ CUtensorMap tmap_do,
                                                                     const __grid_constant__ CUtensorMap tmap_qp,
@@ -309,13 +310,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     if (!proxy) {
                         if (g >= 1 && prev_proxy) wait(BAR(sm->r1_free), (pt - 1) & 1, 4);   // dKp has been read out of R1
                         tc_fence_after_sync();
-                        if (!bad) umma_tile_128<false, false>(r1, tile_v, tdo, false, elect);   // dP^T = V_j dO_g^T
+                        if (!bad) umma_tile_128<false, false, FP16>(r1, tile_v, tdo, false, elect);   // dP^T = V_j dO_g^T
                     }
                     wait(BAR(sm->q_full[s]), ph, 2);
                     if (g >= 1) wait(BAR(sm->r0_free), (g - 1) & 1, 3);                       // dQ / dQp has been read out of R0
                     tc_fence_after_sync();
                     if (!bad) {
-                        umma_tile_128<false, false>(r0, proxy ? tdo : tile_k, tq, false, elect);   // S^T = K_j Q_g^T  (Sp^T = Kp_j Qp_g^T)
+                        umma_tile_128<false, false, FP16>(r0, proxy ? tdo : tile_k, tq, false, elect);   // S^T = K_j Q_g^T  (Sp^T = Kp_j Qp_g^T)
                         umma_commit(BAR(sm->sdp_full), elect);
                     }
                 };
@@ -332,18 +333,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     if (!is_proxy) {
                         if (t == 0 && nsub > 0) wait(BAR(sm->acc_free), (nsub - 1) & 1, 6);   // dV, dK of the previous sub-unit flushed
                         if (!bad) {
-                            umma_tile_128_ts<true>(r2, r0, r0 + 64, tdo, t != 0, elect);    // dV += P^T dO_g
+                            umma_tile_128_ts<true, FP16>(r2, r0, r0 + 64, tdo, t != 0, elect);    // dV += P^T dO_g
                             umma_commit(BAR(sm->do_empty[s]), elect);
-                            umma_tile_128_ts<true>(r3, r1, r1 + 64, tq, t != 0, elect);     // dK += dS^T Q_g
+                            umma_tile_128_ts<true, FP16>(r3, r1, r1 + 64, tq, t != 0, elect);     // dK += dS^T Q_g
                             umma_commit(BAR(sm->q_empty[s]), elect);
-                            umma_tile_128<true, true>(r0, tile_ds, tile_k, false, elect);   // dQ = dS K_j
+                            umma_tile_128<true, true, FP16>(r0, tile_ds, tile_k, false, elect);   // dQ = dS K_j
                             umma_commit(BAR(sm->dq_full), elect);
                         }
                     } else {
                         if (!bad) {
-                            umma_tile_128<true, false>(r1, tq, tile_ds, false, elect);      // dKp^T = Qp_g^T dSp  (lane = head dim)
+                            umma_tile_128<true, false, FP16>(r1, tq, tile_ds, false, elect);      // dKp^T = Qp_g^T dSp  (lane = head dim)
                             umma_commit(BAR(sm->dkp_full), elect);
-                            umma_tile_128<true, true>(r0, tile_ds, tdo, false, elect);      // dQp = dSp Kp_j
+                            umma_tile_128<true, true, FP16>(r0, tile_ds, tdo, false, elect);      // dQp = dSp Kp_j
                             umma_commit(BAR(sm->dq_full), elect);
                             umma_commit(BAR(sm->q_empty[s]), elect);
                             umma_commit(BAR(sm->do_empty[s]), elect);
@@ -546,12 +547,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                         uint32_t pk[16];
                         if (part == 0) {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                            for (int i = 0; i < 16; ++i) pk[i] = pack_act<FP16>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
                         } else {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 const float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
-                                pk[i] = pack_bf16(x0 - bf16_round(x0), x1 - bf16_round(x1));
+                                pk[i] = pack_act<FP16>(x0 - act_round<FP16>(x0), x1 - act_round<FP16>(x1));
                             }
                         }
                         if (full) {
@@ -673,13 +674,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                                 // dS = P o (dP - delta)
                                 const float2 nd2 = *reinterpret_cast<const float2*>(&st->neg_delta[cbase + c + i]);
                                 const float2 d = f2_mul(make_float2(p0, p1), f2_add(f2_from_bits(dv[cur][i], dv[cur][i + 1]), nd2));
-                                pk[i >> 1] = pack_bf16(p0, p1);
-                                dk[i >> 1] = pack_bf16(d.x, d.y);
+                                pk[i >> 1] = pack_act<FP16>(p0, p1);
+                                dk[i >> 1] = pack_act<FP16>(d.x, d.y);
                                 if (with_kl) teacher[ti] = __hadd2(teacher[ti], __floats2half2_rn(p0, p1));
                             } else {
                                 const float2 tt = __half22float2(teacher[ti]);
                                 const float t0 = tt.x * inv_mpp, t1 = tt.y * inv_mpp;
-                                dk[i >> 1] = pack_bf16(p0 - t0, p1 - t1);
+                                dk[i >> 1] = pack_act<FP16>(p0 - t0, p1 - t1);
                                 if (P.kl_value) {   // KL(teacher || proxy) = sum t (ln t - ln p); t = 0 contributes nothing
                                     kl_acc += (t0 > 0.f) ? t0 * (fast_log2(t0) - a.x) : 0.f;
                                     kl_acc += (t1 > 0.f) ? t1 * (fast_log2(t1) - a.y) : 0.f;
@@ -770,6 +771,7 @@ struct BwdCombineParams {
     int64_t part_slots;
 };
 
+template <bool FP16>
 __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams P) {
     const int lane = threadIdx.x & 31;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -803,30 +805,30 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams
                     const int64_t sp = si + part * P.part_slots;
                     const __nv_bfloat16* src = proxy ? P.dqp_part + sp * kHeadDim : P.dq_part + (sp * P.mpp + hh) * kHeadDim;
                     const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
-                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                    a0 += __low2float(lo);
-                    a1 += __high2float(lo);
-                    a2 += __low2float(hi);
-                    a3 += __high2float(hi);
+                    const uint32_t lo = raw.x;
+                    const uint32_t hi = raw.y;
+                    a0 += act_lo<FP16>(lo);
+                    a1 += act_hi<FP16>(lo);
+                    a2 += act_lo<FP16>(hi);
+                    a3 += act_hi<FP16>(hi);
                 }
             }
         }
         uint2 o;
         if (proxy) {
-            o.x = pack_bf16(a0 * gk, a1 * gk);
-            o.y = pack_bf16(a2 * gk, a3 * gk);
+            o.x = pack_act<FP16>(a0 * gk, a1 * gk);
+            o.y = pack_act<FP16>(a2 * gk, a3 * gk);
             *reinterpret_cast<uint2*>(P.dqp + (bp * P.S + q) * kHeadDim + lane * 4) = o;
         } else {
-            o.x = pack_bf16(a0 * P.scale, a1 * P.scale);
-            o.y = pack_bf16(a2 * P.scale, a3 * P.scale);
+            o.x = pack_act<FP16>(a0 * P.scale, a1 * P.scale);
+            o.y = pack_act<FP16>(a2 * P.scale, a3 * P.scale);
             *reinterpret_cast<uint2*>(P.dq + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q) * kHeadDim + lane * 4) = o;
         }
     }
 }
 
 // Wide variant for Hq/Hp <= 8: one sweep over the contiguous mpp*256-byte record of each edge.
-template <int KITER, bool SPLIT>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (latency bound)
+template <int KITER, bool SPLIT, bool FP16>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (latency bound)
 __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_kernel(const BwdCombineParams P) {
     const int lane = threadIdx.x & 31;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -870,20 +872,20 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
                         const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&u[e]);
-                            acc[k][2 * e] += __low2float(v2);
-                            acc[k][2 * e + 1] += __high2float(v2);
+                            const uint32_t v2 = u[e];
+                            acc[k][2 * e] += act_lo<FP16>(v2);
+                            acc[k][2 * e + 1] += act_hi<FP16>(v2);
                         }
                     }
                 }
                 if (P.dqp) {
                     const uint2 raw = *reinterpret_cast<const uint2*>(P.dqp_part + sp * kHeadDim + lane * 4);
-                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                    pa0 += __low2float(lo);
-                    pa1 += __high2float(lo);
-                    pa2 += __low2float(hi);
-                    pa3 += __high2float(hi);
+                    const uint32_t lo = raw.x;
+                    const uint32_t hi = raw.y;
+                    pa0 += act_lo<FP16>(lo);
+                    pa1 += act_hi<FP16>(lo);
+                    pa2 += act_lo<FP16>(hi);
+                    pa3 += act_hi<FP16>(hi);
                 }
             }
         }
@@ -894,18 +896,18 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
         if (ck < nchunk) {
             const int hh = ck >> 4, col = (ck & 15) * 8;
             uint4 o;
-            o.x = pack_bf16(acc[k][0] * P.scale, acc[k][1] * P.scale);
-            o.y = pack_bf16(acc[k][2] * P.scale, acc[k][3] * P.scale);
-            o.z = pack_bf16(acc[k][4] * P.scale, acc[k][5] * P.scale);
-            o.w = pack_bf16(acc[k][6] * P.scale, acc[k][7] * P.scale);
+            o.x = pack_act<FP16>(acc[k][0] * P.scale, acc[k][1] * P.scale);
+            o.y = pack_act<FP16>(acc[k][2] * P.scale, acc[k][3] * P.scale);
+            o.z = pack_act<FP16>(acc[k][4] * P.scale, acc[k][5] * P.scale);
+            o.w = pack_act<FP16>(acc[k][6] * P.scale, acc[k][7] * P.scale);
             *reinterpret_cast<uint4*>(P.dq + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q) * kHeadDim + col) = o;
         }
     }
     if (P.dqp) {
         const float gk = (P.grad_kl ? *P.grad_kl : 1.f) * P.kl_out_scale;
         uint2 o;
-        o.x = pack_bf16(pa0 * gk, pa1 * gk);
-        o.y = pack_bf16(pa2 * gk, pa3 * gk);
+        o.x = pack_act<FP16>(pa0 * gk, pa1 * gk);
+        o.y = pack_act<FP16>(pa2 * gk, pa3 * gk);
         *reinterpret_cast<uint2*>(P.dqp + (bp * P.S + q) * kHeadDim + lane * 4) = o;
     }
 }
@@ -913,6 +915,7 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
 // -------------------------------------------------------------------------------------------
 // delta[b,h,q] = sum_d out[b,q,h,d] * dout[b,q,h,d]   (flash_msa/flash_msa.py:99)
 // -------------------------------------------------------------------------------------------
+template <bool FP16>
 __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                                                     int64_t do_sb, int64_t do_ss, int64_t do_sh, float* __restrict__ delta,
                                                     int B, int S, int Hq) {
@@ -925,10 +928,9 @@ __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restr
     const int b = static_cast<int>(bq / S);
     const uint2 a = *reinterpret_cast<const uint2*>(out + w * kHeadDim + lane * 4);
     const uint2 d = *reinterpret_cast<const uint2*>(dout + b * do_sb + q * do_ss + h * do_sh + lane * 4);
-    const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(&a.x), a1 = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
-    const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&d.x), d1 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
-    float s = __low2float(a0) * __low2float(d0) + __high2float(a0) * __high2float(d0) + __low2float(a1) * __low2float(d1) +
-              __high2float(a1) * __high2float(d1);
+    const uint32_t a0 = a.x, a1 = a.y, d0 = d.x, d1 = d.y;
+    float s = act_lo<FP16>(a0) * act_lo<FP16>(d0) + act_hi<FP16>(a0) * act_hi<FP16>(d0) + act_lo<FP16>(a1) * act_lo<FP16>(d1) +
+              act_hi<FP16>(a1) * act_hi<FP16>(d1);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (lane == 0) delta[(static_cast<int64_t>(b) * Hq + h) * S + q] = s;
@@ -936,6 +938,7 @@ __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restr
 
 // dst = bf16(src * const_scale * factor), factor = *scale_ptr when given (the upstream kl gradient lives on the
 // device: flash_msa/flash_msa.py:122-125) else 1.
+template <bool FP16>
 __global__ void __launch_bounds__(256) cast_scaled_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n4,
                                                           const float* __restrict__ scale_ptr, float const_scale) {
     const float f = (scale_ptr ? *scale_ptr : 1.f) * const_scale;
@@ -943,8 +946,8 @@ __global__ void __launch_bounds__(256) cast_scaled_kernel(const float* __restric
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 v = reinterpret_cast<const float4*>(src)[i];
         uint2 o;
-        o.x = pack_bf16(v.x * f, v.y * f);
-        o.y = pack_bf16(v.z * f, v.w * f);
+        o.x = pack_act<FP16>(v.x * f, v.y * f);
+        o.y = pack_act<FP16>(v.z * f, v.w * f);
         reinterpret_cast<uint2*>(dst)[i] = o;
     }
 }
@@ -953,31 +956,42 @@ __global__ void __launch_bounds__(256) cast_scaled_kernel(const float* __restric
 }  // namespace fmsa
 
 extern "C" int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int32_t B, int32_t S, int32_t Hq,
-                              void* stream) {
+                              int32_t dtype, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(out && d_out && d_out->ptr && delta && B > 0 && S > 0 && Hq > 0);
+    FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
     FMSA_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7u) == 0 && (reinterpret_cast<uintptr_t>(d_out->ptr) & 7u) == 0);
     FMSA_REQUIRE(d_out->stride_b % 4 == 0 && d_out->stride_h % 4 == 0 && d_out->stride_s % 4 == 0);
     const int64_t rows = static_cast<int64_t>(B) * S * Hq;
     const int64_t grid = (rows + 7) / 8;
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
-    delta_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    if (dtype == FMSA_DTYPE_FP16)
+        delta_kernel<true><<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out->ptr), d_out->stride_b, d_out->stride_s,
+        d_out->stride_h, delta, B, S, Hq);
+    else
+        delta_kernel<false><<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out->ptr), d_out->stride_b, d_out->stride_s,
         d_out->stride_h, delta, B, S, Hq);
     return check_launch();
 }
 
 extern "C" int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale,
-                                void* stream) {
+                                int32_t dtype, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(src && dst && n >= 0 && n % 4 == 0);
+    FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
     FMSA_REQUIRE(aligned16(src) && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0);
     if (n == 0) return FMSA_OK;
     const int64_t n4 = n / 4;
     int64_t grid = (n4 + 255) / 256;
     if (grid > 148 * 16) grid = 148 * 16;
-    cast_scaled_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        src, static_cast<__nv_bfloat16*>(dst), n4, scale_ptr, const_scale);
+    if (dtype == FMSA_DTYPE_FP16)
+        cast_scaled_kernel<true><<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            src, static_cast<__nv_bfloat16*>(dst), n4, scale_ptr, const_scale);
+    else
+        cast_scaled_kernel<false><<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            src, static_cast<__nv_bfloat16*>(dst), n4, scale_ptr, const_scale);
     return check_launch();
 }
 
@@ -1050,12 +1064,15 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int sms = device_sm_count();
-    if (sms <= 0 || !ensure_smem_attr(reinterpret_cast<const void*>(sparse_bwd_kernel), kBwdSmemBytes)) return FMSA_ERR_CUDA;
+    const bool fp16 = pb->dtype == FMSA_DTYPE_FP16;
+    const void* kfn = fp16 ? reinterpret_cast<const void*>(sparse_bwd_kernel<true>) : reinterpret_cast<const void*>(sparse_bwd_kernel<false>);
+    if (sms <= 0 || !ensure_smem_attr(kfn, kBwdSmemBytes)) return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    sparse_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
+    if (fp16) sparse_bwd_kernel<true><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
+    else sparse_bwd_kernel<false><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
     return check_launch();
 }
 
@@ -1084,19 +1101,30 @@ extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_pa
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
     const dim3 cg(static_cast<unsigned>(grid));
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
+    const bool fp16 = pb->dtype == FMSA_DTYPE_FP16;
+#define FMSA_BWD_COMBINE(K)                                                                          \
+    do {                                                                                             \
+        if (fp16) {                                                                                  \
+            if (P.split) bwd_combine_wide_kernel<K, true, true><<<cg, 256, 0, cst>>>(P);             \
+            else bwd_combine_wide_kernel<K, false, true><<<cg, 256, 0, cst>>>(P);                    \
+        } else {                                                                                     \
+            if (P.split) bwd_combine_wide_kernel<K, true, false><<<cg, 256, 0, cst>>>(P);            \
+            else bwd_combine_wide_kernel<K, false, false><<<cg, 256, 0, cst>>>(P);                   \
+        }                                                                                            \
+    } while (0)
     if (P.mpp > 8) {
-        bwd_combine_kernel<<<static_cast<unsigned>(grid), 256, 0, cst>>>(P);
-    } else if (P.split) {
-        if (P.mpp <= 2) bwd_combine_wide_kernel<1, true><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 4) bwd_combine_wide_kernel<2, true><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 6) bwd_combine_wide_kernel<3, true><<<cg, 256, 0, cst>>>(P);
-        else bwd_combine_wide_kernel<4, true><<<cg, 256, 0, cst>>>(P);
+        if (fp16) bwd_combine_kernel<true><<<cg, 256, 0, cst>>>(P);
+        else bwd_combine_kernel<false><<<cg, 256, 0, cst>>>(P);
+    } else if (P.mpp <= 2) {
+        FMSA_BWD_COMBINE(1);
+    } else if (P.mpp <= 4) {
+        FMSA_BWD_COMBINE(2);
+    } else if (P.mpp <= 6) {
+        FMSA_BWD_COMBINE(3);
     } else {
-        if (P.mpp <= 2) bwd_combine_wide_kernel<1, false><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 4) bwd_combine_wide_kernel<2, false><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 6) bwd_combine_wide_kernel<3, false><<<cg, 256, 0, cst>>>(P);
-        else bwd_combine_wide_kernel<4, false><<<cg, 256, 0, cst>>>(P);
+        FMSA_BWD_COMBINE(4);
     }
+#undef FMSA_BWD_COMBINE
     return check_launch();
 }
 

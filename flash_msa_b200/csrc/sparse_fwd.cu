@@ -113,6 +113,7 @@ static_assert(kFwdSmemBytes <= 232448, "shared memory budget of one CTA");
 // P V(t+1) waits until O(t) has been read out, which takes far less time than a softmax.
 // The register file is re-divided between the warpgroups (setmaxnreg): the softmax and output groups get what the
 // gather and issue warps do not need.
+template <bool FP16>
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                     const __grid_constant__ CUtensorMap tmap_qp,
                                                                     const __grid_constant__ CUtensorMap tmap_k,
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     if (gts >= 3) wait(BAR(sm->s_free[ssb]), ssph ^ 1, 2);
                     tc_fence_after_sync();
                     if (!bad) {
-                        umma_tile_128<false, false>(tmem_s0 + ssb * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k, false,
+                        umma_tile_128<false, false, FP16>(tmem_s0 + ssb * 128, tile_q0 + qs * kTileBytes, proxy ? tile_kp : tile_k, false,
                                                     elect);
                         umma_commit(BAR(sm->s_full[ssb]), elect);
                         umma_commit(BAR(sm->q_empty[qs]), elect);
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         tc_fence_after_sync();
                         if (!bad) {
                             const uint32_t ts = tmem_s0 + sb * 128;
-                            umma_tile_128_ts<true>(tmem_o0, ts, ts + 32, tile_v, false, elect);   // O = P V_j
+                            umma_tile_128_ts<true, FP16>(tmem_o0, ts, ts + 32, tile_v, false, elect);   // O = P V_j
                             umma_commit(BAR(sm->o_full), elect);
                         }
                         ++mt;
@@ -443,7 +444,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         tmem_ld_wait();
                         uint32_t pk[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        for (int i = 0; i < 16; ++i) pk[i] = pack_act<FP16>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
                         if (full) {
 #pragma unroll
                             for (int k8 = 0; k8 < 4; ++k8)
@@ -543,7 +544,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                                     p1 = (i + 1 <= lc) ? p1 : 0.f;
                                 }
                                 l2 = f2_add(l2, make_float2(p0, p1));
-                                pk[i >> 1] = pack_bf16(p0, p1);
+                                pk[i >> 1] = pack_act<FP16>(p0, p1);
                             }
                             // P (bf16, two keys per column) over S columns this thread has already consumed
                             if (!kProxy) tmem_st16(tmem_addr(ts, quarter, c >> 1), pk);
@@ -611,6 +612,7 @@ struct CombineParams {
     int g_begin, G, dense;
 };
 
+template <bool FP16>
 __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
     const int lane = threadIdx.x & 31;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -676,17 +678,17 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
                 const float wi = __shfl_sync(0xffffffffu, wgt, i);
                 if (si < 0) continue;
                 const uint2 raw = *reinterpret_cast<const uint2*>(P.o_part + (si * P.mpp + hh) * kHeadDim + lane * 4);
-                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                a0 += wi * __low2float(lo);
-                a1 += wi * __high2float(lo);
-                a2 += wi * __low2float(hi);
-                a3 += wi * __high2float(hi);
+                const uint32_t lo = raw.x;
+                const uint32_t hi = raw.y;
+                a0 += wi * act_lo<FP16>(lo);
+                a1 += wi * act_hi<FP16>(lo);
+                a2 += wi * act_lo<FP16>(hi);
+                a3 += wi * act_hi<FP16>(hi);
             }
         }
         uint2 o;
-        o.x = pack_bf16(a0, a1);
-        o.y = pack_bf16(a2, a3);
+        o.x = pack_act<FP16>(a0, a1);
+        o.y = pack_act<FP16>(a2, a3);
         *reinterpret_cast<uint2*>(P.out + (static_cast<int64_t>(b) * P.S + q) * (static_cast<int64_t>(P.Hq) * kHeadDim) +
                                   static_cast<int64_t>(h) * kHeadDim + lane * 4) = o;
     }
@@ -699,7 +701,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
 // small head ratios keep few accumulators in registers and reach a high occupancy (the kernel is
 // bound by memory latency).
 constexpr int kWideMaxHeads = 8;
-template <int KITER>
+template <int KITER, bool FP16>
 __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel(const CombineParams P) {
     constexpr int kWideMaxHeads = 2 * KITER;
     __shared__ float wsm[8][32][kWideMaxHeads + 1];
@@ -791,9 +793,9 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel
                     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&u[e]);
-                        acc[k][2 * e] += wgt * __low2float(v2);
-                        acc[k][2 * e + 1] += wgt * __high2float(v2);
+                        const uint32_t v2 = u[e];
+                        acc[k][2 * e] += wgt * act_lo<FP16>(v2);
+                        acc[k][2 * e + 1] += wgt * act_hi<FP16>(v2);
                     }
                 }
             }
@@ -806,10 +808,10 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel
         const int ck = k * 32 + lane;
         if (ck < nchunk) {
             uint4 o;
-            o.x = pack_bf16(acc[k][0], acc[k][1]);
-            o.y = pack_bf16(acc[k][2], acc[k][3]);
-            o.z = pack_bf16(acc[k][4], acc[k][5]);
-            o.w = pack_bf16(acc[k][6], acc[k][7]);
+            o.x = pack_act<FP16>(acc[k][0], acc[k][1]);
+            o.y = pack_act<FP16>(acc[k][2], acc[k][3]);
+            o.z = pack_act<FP16>(acc[k][4], acc[k][5]);
+            o.w = pack_act<FP16>(acc[k][6], acc[k][7]);
             *reinterpret_cast<uint4*>(orow + ck * 8) = o;
         }
     }
@@ -877,12 +879,15 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int sms = device_sm_count();
-    if (sms <= 0 || !ensure_smem_attr(reinterpret_cast<const void*>(sparse_fwd_kernel), kFwdSmemBytes)) return FMSA_ERR_CUDA;
+    const bool fp16 = pb->dtype == FMSA_DTYPE_FP16;
+    const void* kfn = fp16 ? reinterpret_cast<const void*>(sparse_fwd_kernel<true>) : reinterpret_cast<const void*>(sparse_fwd_kernel<false>);
+    if (sms <= 0 || !ensure_smem_attr(kfn, kFwdSmemBytes)) return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    sparse_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
+    if (fp16) sparse_fwd_kernel<true><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
+    else sparse_fwd_kernel<false><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
     return check_launch();
 }
 
@@ -904,16 +909,19 @@ extern "C" int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_par
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
     const dim3 cg(static_cast<unsigned>(grid));
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
-    if (P.mpp <= 2)
-        combine_wide_kernel<1><<<cg, 256, 0, cst>>>(P);
-    else if (P.mpp <= 4)
-        combine_wide_kernel<2><<<cg, 256, 0, cst>>>(P);
-    else if (P.mpp <= 6)
-        combine_wide_kernel<3><<<cg, 256, 0, cst>>>(P);
-    else if (P.mpp <= 8)
-        combine_wide_kernel<4><<<cg, 256, 0, cst>>>(P);
-    else
-        combine_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    if (pb->dtype == FMSA_DTYPE_FP16) {
+        if (P.mpp <= 2) combine_wide_kernel<1, true><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 4) combine_wide_kernel<2, true><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 6) combine_wide_kernel<3, true><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 8) combine_wide_kernel<4, true><<<cg, 256, 0, cst>>>(P);
+        else combine_kernel<true><<<cg, 256, 0, cst>>>(P);
+    } else {
+        if (P.mpp <= 2) combine_wide_kernel<1, false><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 4) combine_wide_kernel<2, false><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 6) combine_wide_kernel<3, false><<<cg, 256, 0, cst>>>(P);
+        else if (P.mpp <= 8) combine_wide_kernel<4, false><<<cg, 256, 0, cst>>>(P);
+        else combine_kernel<false><<<cg, 256, 0, cst>>>(P);
+    }
     return check_launch();
 }
 

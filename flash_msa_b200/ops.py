@@ -194,9 +194,20 @@ def _tensor_arg(t: torch.Tensor) -> "_lib.FmsaTensor":
     return _lib.FmsaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
 
 
+def _dtype_code(dtype) -> int:
+    """The library's code of an activation type (bf16 and fp16 are supported, as in the reference:
+    flash_msa/msa_backward_cutedsl.py:169-183)."""
+    if dtype == torch.bfloat16:
+        return _lib.FMSA_DTYPE_BF16
+    if dtype == torch.float16:
+        return _lib.FMSA_DTYPE_FP16
+    raise TypeError(f"flash_msa_b200 supports bf16 and fp16 activations, got {dtype}")
+
+
 def _problem(q, k, q_proxy, k_proxy, top_k_blocks, scale) -> "_lib.FmsaProblem":
     b, hq, s, _ = q.shape
-    return _lib.FmsaProblem(b, s, hq, k.shape[1], q_proxy.shape[1], k_proxy.shape[1], int(top_k_blocks), float(scale))
+    return _lib.FmsaProblem(b, s, hq, k.shape[1], q_proxy.shape[1], k_proxy.shape[1], int(top_k_blocks), float(scale),
+                            _dtype_code(q.dtype))
 
 
 def check_status(status: torch.Tensor, what: str) -> None:
@@ -210,8 +221,9 @@ def check_status(status: torch.Tensor, what: str) -> None:
 def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, status=None) -> torch.Tensor:
     """fp32 block scores [B,Hp,S,NB]; entries of future blocks are left unwritten."""
     _require_cuda(q_proxy, k_proxy)
-    if q_proxy.dtype != torch.bfloat16 or k_proxy.dtype != torch.bfloat16:
-        raise TypeError(f"flash_msa_b200 supports bf16 activations, got {q_proxy.dtype}")
+    if q_proxy.dtype != k_proxy.dtype:
+        raise TypeError("q_proxy and k_proxy must have one dtype")
+    code = _dtype_code(q_proxy.dtype)
     b, hp, s, d = q_proxy.shape
     qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
     dev = qp.device
@@ -221,7 +233,7 @@ def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: floa
     lib = _lib.load()
     with _Timed("select_scores", dev):
         _launch("fmsa_select_scores", 1, lib.fmsa_select_scores(_tensor_arg(qp), _tensor_arg(kp), scores.data_ptr(), b, hp,
-                                                              kp.shape[1], s, float(scale), status.data_ptr(),
+                                                              kp.shape[1], s, float(scale), code, status.data_ptr(),
                                                               _stream(dev)), dev)
     return scores
 
@@ -317,7 +329,7 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     go = _as_kernel_input(go)
     delta = torch.empty(b, hq, s, dtype=torch.float32, device=dev)
     with _Timed("bwd_delta", dev):
-        _launch("fmsa_bwd_delta", 1, lib.fmsa_bwd_delta(out.data_ptr(), _tensor_arg(go), delta.data_ptr(), b, s, hq, st), dev)
+        _launch("fmsa_bwd_delta", 1, lib.fmsa_bwd_delta(out.data_ptr(), _tensor_arg(go), delta.data_ptr(), b, s, hq, pb.dtype, st), dev)
 
     dkv_acc = torch.zeros(2, b, hkv, s, d, dtype=torch.float32, device=dev)
     if with_kl:
@@ -335,7 +347,7 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
 
     def cast(acc, dst, scale_ptr, const_scale):
         _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(acc.data_ptr(), dst.data_ptr(), acc.numel(), scale_ptr,
-                                                          float(const_scale), st), dev)
+                                                          float(const_scale), pb.dtype, st), dev)
 
     # dQ and dQp leave the kernel as per-edge partial rows; a combine pass sums them per query row
     dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)

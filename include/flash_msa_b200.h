@@ -9,7 +9,7 @@
  *    frees device memory; the caller owns every buffer, including workspaces whose size the
  *    *_workspace_bytes functions report.
  *  - Launches go to the given stream and never synchronise with the host.
- *  - Activations are bf16 with head dimension 128 and 128-token blocks.  A 4-D activation
+ *  - Activations are bf16 or fp16 (one type per call) with head dimension 128 and 128-token blocks.  A 4-D activation
  *    (B, H, S, 128) is described by its base pointer and element strides for B, H and S; the
  *    last dimension must be contiguous and rows 16-byte aligned.
  *
@@ -33,6 +33,10 @@ extern "C" {
 
 #define FMSA_MAX_TOPK_BLOCKS 128
 
+/* Activation types.  The reference accepts both (flash_msa/msa_backward_cutedsl.py:169-183). */
+#define FMSA_DTYPE_BF16 0
+#define FMSA_DTYPE_FP16 1
+
 /* Strided (B, H, S, 128) bf16 activation. */
 typedef struct {
     const void* ptr;
@@ -45,6 +49,7 @@ typedef struct {
 typedef struct {
     int32_t B, S, Hq, Hkv, Hp, Hpkv, top_k_blocks;
     float scale;
+    int32_t dtype; /* FMSA_DTYPE_BF16 or FMSA_DTYPE_FP16: the type of every activation, partial row and gradient */
 } fmsa_problem;
 
 /* Library ABI version (bumped on any signature change). */
@@ -122,7 +127,7 @@ int fmsa_reverse_index_static(const int32_t* block_indices, int32_t* row_ptr, in
  * (flash_msa/tests/testing_model.py:75-88); scores are NOT rounded to bf16.
  *   q_proxy (B,Hp,S,128), k_proxy (B,Hpkv,S,128) bf16;  block_scores fp32 [B,Hp,S,S/128];  status int32[1]. */
 int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores, int32_t B,
-                       int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t* status, void* stream);
+                       int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype, int32_t* status, void* stream);
 
 /* Sparse forward, stage 1: per-edge partial attention (key-block stationary).
  * Replaces sparse_flash_varlen_forward (flash_msa/sparse_flash_varlen.py:92-261: local-block
@@ -154,7 +159,7 @@ int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_part, const fl
  * Replaces the torch expression at flash_msa/flash_msa.py:99.  out is the contiguous
  * [B,S,Hq*128] forward output; d_out is described as a (B,Hq,S,128) view. */
 int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int32_t B, int32_t S, int32_t Hq,
-                   void* stream);
+                   int32_t dtype, void* stream);
 
 /* Fused backward over the selected edges (dense = 1: over every causal block pair, the warmup
  * backward).  Replaces run_fused_backward (flash_msa/msa_backward_cutedsl.py:944-1114) and
@@ -198,12 +203,13 @@ int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const v
                             int32_t split, const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
                             const float* grad_kl, int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
 
-/* dst[i] = bf16(src[i] * const_scale * f), f = *scale_ptr (a device scalar, e.g. the upstream
+/* dst[i] = bf16 or fp16 (dtype) of (src[i] * const_scale * f), f = *scale_ptr (a device scalar, e.g. the upstream
  * gradient of kl_loss: flash_msa/flash_msa.py:122-125) or 1 when scale_ptr is NULL.  n % 4 == 0.
  * Replaces the fp32 -> input-dtype casts at flash_msa/msa_backward_cutedsl.py:1075-1081.
  * fmsa_sparse_bwd leaves these factors to the cast: dv_acc needs 1, dk_acc needs scale, dkp_acc
  * needs scale/(B*Hp*S) times the upstream kl gradient. */
-int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale, void* stream);
+int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale, int32_t dtype,
+                     void* stream);
 
 /* Asynchronous strided copy between pinned host memory and the device (either direction; inferred
  * from the pointers): `rows` pieces of `width` bytes, source pieces `src_pitch` bytes apart, destination

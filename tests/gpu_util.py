@@ -6,11 +6,11 @@ from oracle import msa_oracle as O
 SCALE = 128 ** -0.5
 
 
-def bf16_inputs(cfg, device="cuda", layout="bhsd", skew=False):
-    """Seeded inputs, rounded to bf16.  layout "bshd" returns (B,H,S,D) views of (B,S,H,D)
+def bf16_inputs(cfg, device="cuda", layout="bhsd", skew=False, dtype=torch.bfloat16):
+    """Seeded inputs, rounded to bf16 (or to `dtype`).  layout "bshd" returns (B,H,S,D) views of (B,S,H,D)
     storage, the layout the reference's callers pass (flash_msa/tests/testing_model.py:173-185)."""
     ts = O.make_inputs(cfg["b"], cfg["s"], cfg["hq"], cfg["hkv"], cfg["hp"], cfg["hpkv"], seed=cfg.get("seed", 0),
-                       dtype=torch.bfloat16, device=device, skew=skew)
+                       dtype=dtype, device=device, skew=skew)
     qp, kp, q, k, v, do = ts
     if layout == "bshd":
         qp, kp, q, k, v = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (qp, kp, q, k, v))

@@ -129,3 +129,25 @@ def test_kl_value(fm, name):
     finally:
         api.COMPUTE_KL_VALUE = False
 
+
+
+@pytest.mark.parametrize("warmup", [False, True])
+def test_backward_fp16(fm, warmup):
+    """fp16 activations through the public functions: gradients come back in fp16 and stay within twice the error of
+    the fp16 eager arithmetic."""
+    cfg = CFGS["c1"]
+    qp, kp, q, k, v, do = bf16_inputs(cfg, dtype=torch.float16)
+    fn = fm.flash_msa_warmup_func if warmup else fm.flash_msa_func
+    out, grads, _ = _run_kernel(fn, (qp, kp, q, k, v), do, cfg["kb"] * 128, 1.0)
+    assert out.dtype == torch.float16
+    if warmup:
+        r32 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 1.0)
+        _, _, g16 = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, SCALE), (qp, kp, q, k, v), do, 1.0)
+    else:
+        idx = kernel_selection(qp, kp, cfg["kb"])
+        r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 1.0, block_indices=idx)
+        _, _, g16 = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE, block_indices=idx),
+                                             (qp, kp, q, k, v), do, 1.0)
+    for n, got, y in zip(NAMES, grads, g16):
+        assert got.dtype == torch.float16 and got.shape == r32[n].shape
+        yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())

@@ -79,3 +79,28 @@ def test_dense_forward(ops, name):
     yardstick_check("out", out, r32["out"], r16["out"], 1e-3)
     assert max_err(lse, r32["lse"]) <= 2e-3
     assert max_err(lse_p, r32["lse_proxy"]) <= 2e-3
+
+
+@pytest.mark.parametrize("name", ["tiny", "c1"])
+def test_sparse_forward_fp16(ops, name):
+    """fp16 activations (accepted by the reference kernels too, flash_msa/msa_backward_cutedsl.py:169-183): the same
+    check as for bf16 with the fp16 restatement as the yardstick."""
+    cfg = CFGS[name]
+    qp, kp, q, k, v, _ = bf16_inputs(cfg, dtype=torch.float16)
+    nb = cfg["s"] // 128
+    idx = ops.select_blocks(qp, kp, scale=SCALE, num_blocks=nb, top_k_blocks=cfg["kb"])
+    rix = ops.build_reverse_index(idx)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse, lse_p = ops.attention_forward(q, k, v, qp, kp, SCALE, rix, status=status)
+    ops.check_status(status, "sparse_fwd")
+    assert out.dtype == torch.float16
+    r32 = O.sparse_forward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, block_indices=idx)
+    r16 = O.sparse_forward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, block_indices=idx, dtype=torch.float16)
+    yardstick_check("out", out, r32["out"], r16["out"], 1e-3)
+    assert max_err(lse, r32["lse"]) <= 2e-3
+    assert max_err(lse_p, r32["lse_proxy"]) <= 2e-3
+    # the selection on fp16 inputs is bit-exact against the stable top-k of the kernel's own scores as well
+    scores = ops.proxy_block_scores(qp, kp, SCALE)
+    qblk = (torch.arange(cfg["s"], device="cuda") // 128).view(1, 1, -1, 1)
+    masked = scores.masked_fill(torch.arange(nb, device="cuda").view(1, 1, 1, nb) > qblk, float("-inf"))
+    assert torch.equal(idx.cpu(), O.stable_topk(masked.cpu(), cfg["kb"]))
