@@ -5,7 +5,7 @@ from .api import sparse_attention as flash_msa_func
 from .api import sparse_attention_warmup
 from .api import sparse_attention_warmup as flash_msa_func_warmup
 from .api import sparse_attention_warmup as flash_msa_warmup_func
-from .api import last_kl_value
+from .api import check_pending_status, last_kl_value
 
 __all__ = [
     "flash_msa_func",
@@ -13,4 +13,5 @@ __all__ = [
     "flash_msa_warmup_func",
     "sparse_attention_warmup",
     "last_kl_value",
+    "check_pending_status",
 ]

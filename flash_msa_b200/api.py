@@ -10,7 +10,10 @@ from . import ops
 BLOCK_SIZE = 128
 MAX_TOP_K_BLOCKS = 128
 
-# Set to True to read the device status word after every call (synchronises; for debugging).
+# The device status word of every call (a bounded wait that ran out, a bad index in metadata) is checked
+# without synchronising: it is copied to pinned memory behind the call and looked at by the next call of the
+# library, which raises RuntimeError then; `check_pending_status()` waits for everything queued so far.
+# DEBUG_CHECK_STATUS = True reads the word right after every call instead (synchronises; for debugging).
 DEBUG_CHECK_STATUS = False
 
 
@@ -90,6 +93,13 @@ def _publish_kl(buf):
 def _maybe_check(status, what):
     if DEBUG_CHECK_STATUS:
         ops.check_status(status, what)
+    else:
+        ops.deferred_status.push(status, what)
+
+
+def check_pending_status():
+    """Waits for the status words of all calls issued so far and raises RuntimeError for a non-zero one."""
+    ops.deferred_status.drain()
 
 
 class _SparseAttentionFunction(torch.autograd.Function):

@@ -210,12 +210,61 @@ def _problem(q, k, q_proxy, k_proxy, top_k_blocks, scale) -> "_lib.FmsaProblem":
                             _dtype_code(q.dtype))
 
 
+_STATUS_NAMES = {1: "a bounded device-side wait timed out", 2: "an out-of-range index was found in metadata",
+                 3: "the shared-memory window of a kernel was not 1024-byte aligned"}
+
+
 def check_status(status: torch.Tensor, what: str) -> None:
     """Reads the device status word (synchronises).  Used by tests and debug mode only."""
     code = int(status.item())
     if code != 0:
-        names = {1: "a bounded device-side wait timed out", 2: "an out-of-range index was found in metadata"}
-        raise RuntimeError(f"{what}: {names.get(code, code)}")
+        raise RuntimeError(f"{what}: {_STATUS_NAMES.get(code, code)}")
+
+
+class DeferredStatus:
+    """Checks device status words without synchronising: `push` copies the word to a slot of a small pinned
+    ring on the current stream and records an event; every later `push` (and `drain`) looks at the words
+    whose events have completed and raises for a non-zero one, so a timed-out wait or a bad index surfaces
+    at the next call of the library instead of passing silently.  Nothing is queued while the stream is
+    being captured into a graph."""
+    SLOTS = 64
+
+    def __init__(self):
+        self._host = None
+        self._pending = []        # (slot, event, what)
+        self._next = 0
+
+    def _poll(self, block: bool) -> None:
+        while self._pending:
+            slot, event, what = self._pending[0]
+            if block:
+                event.synchronize()
+            elif not event.query():
+                return
+            self._pending.pop(0)
+            code = int(self._host[slot])
+            if code != 0:
+                raise RuntimeError(f"{what} (reported late): {_STATUS_NAMES.get(code, code)}")
+
+    def push(self, status: torch.Tensor, what: str) -> None:
+        if torch.cuda.is_current_stream_capturing():
+            return
+        if self._host is None:
+            self._host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self._poll(block=len(self._pending) >= self.SLOTS - 1)
+        slot = self._next
+        self._next = (slot + 1) % self.SLOTS
+        self._host[slot:slot + 1].copy_(status, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._pending.append((slot, event, what))
+
+    def drain(self) -> None:
+        """Waits for every queued status word and raises for the first non-zero one."""
+        self._poll(block=True)
+
+
+deferred_status = DeferredStatus()
 
 
 def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, status=None) -> torch.Tensor:
@@ -249,9 +298,11 @@ def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_bloc
     return (idx, scores) if return_scores else idx
 
 
-# Upper bound on the bytes of forward partials held at once; larger problems run in several passes
-# over (batch, KV head) groups.
-MAX_PARTIAL_BYTES = 8 << 30
+# Upper bound on the bytes of per-edge partial rows (forward O partials, backward dQ partials) held at once;
+# larger problems run in several passes over (batch, KV head) groups.  4 GiB keeps the 8K training shapes in
+# one pass; lower it (module attribute, or FLASH_MSA_B200_MAX_PARTIAL_BYTES in the environment) when the
+# attention call has to fit beside model state.
+MAX_PARTIAL_BYTES = int(os.environ.get("FLASH_MSA_B200_MAX_PARTIAL_BYTES", 4 << 30))
 # Rows with more edges than this store their dQ partial rows as (value, rounding remainder) pairs.
 SPLIT_PARTIALS_ABOVE = 32
 

@@ -74,6 +74,22 @@ def test_bounded_wait_runs_out(ops):
     assert status_b.item() == 0 and torch.equal(d1, d1b)
 
 
+def test_status_word_surfaces_without_synchronising(ops):
+    """The status word of a call is copied to pinned memory behind it and raised by a later look: a kernel whose
+    bounded wait ran out (status 1) turns into a RuntimeError at `drain`, a clean call into nothing."""
+    g = torch.Generator(device="cpu").manual_seed(13)
+    src = torch.randn(256, 128, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(128, 128, generator=g).to(torch.bfloat16).cuda()
+    rows = torch.arange(128).cuda()
+    watch = ops.DeferredStatus()
+    watch.push(ops.pipeline_selftest(src, rows, b)[3], "clean call")
+    watch.drain()
+    watch.push(ops.pipeline_selftest(src, rows, b, withhold=True, limit_ns=2_000_000)[3], "withheld signal")
+    with pytest.raises(RuntimeError, match="withheld signal.*timed out"):
+        watch.drain()
+    watch.drain()                                   # the queue is empty again
+
+
 @pytest.mark.parametrize("s,kb", [(128, 1), (512, 2), (1024, 4), (2048, 16), (4096, 32), (8192, 33), (8192, 64), (16384, 128)])
 def test_topk_bit_exact(ops, s, kb):
     nb = s // 128
