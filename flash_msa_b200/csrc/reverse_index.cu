@@ -20,14 +20,28 @@
 namespace fmsa {
 namespace {
 
-// Shared bitmap: words[j*4 + w] holds rows 32w..32w+31 of the query block for key block j.
-__device__ __forceinline__ void build_bitmap(uint32_t* words, const int32_t* idx_rows, int NB, int Kb, int qblk) {
+// Shared memory of the count and fill kernels: the bitmap words[j*4 + w] (rows 32w..32w+31 of the query block that
+// selected key block j), then the query block's 128 x Kb selections, copied in with 16-byte loads (the rows of a
+// query block are contiguous).  Thread r works on row r and walks its Kb slots starting at slot r % Kb, so that the
+// lanes of a warp touch different banks.
+__device__ __forceinline__ int32_t* stage_rows(uint32_t* words, const int32_t* idx_rows, int NB, int Kb) {
+    int32_t* tile = reinterpret_cast<int32_t*>(words + NB * 4);
+    const int4* src = reinterpret_cast<const int4*>(idx_rows);
+    int4* dst = reinterpret_cast<int4*>(tile);
+    for (int t = threadIdx.x; t < kBlock * Kb / 4; t += blockDim.x) dst[t] = src[t];
     for (int t = threadIdx.x; t < NB * 4; t += blockDim.x) words[t] = 0u;
     __syncthreads();
+    return tile;
+}
+__device__ __forceinline__ int rotated_slot(int s, int r, int Kb) {
+    const int x = s + (r % Kb);
+    return x >= Kb ? x - Kb : x;
+}
+__device__ __forceinline__ void build_bitmap(uint32_t* words, const int32_t* tile, int NB, int Kb, int qblk) {
     const int r = threadIdx.x;   // 128 threads: one per row
-    const int32_t* row = idx_rows + static_cast<int64_t>(r) * Kb;
+    const int32_t* row = tile + r * Kb;
     for (int s = 0; s < Kb; ++s) {
-        const int j = row[s];
+        const int j = row[rotated_slot(s, r, Kb)];
         if (static_cast<unsigned>(j) < static_cast<unsigned>(NB) && j <= qblk) atomicOr(&words[j * 4 + (r >> 5)], 1u << (r & 31));
     }
     __syncthreads();
@@ -35,10 +49,11 @@ __device__ __forceinline__ void build_bitmap(uint32_t* words, const int32_t* idx
 
 __global__ void __launch_bounds__(128) rix_count_kernel(const int32_t* __restrict__ idx, uint8_t* __restrict__ counts,
                                                         int S, int NB, int Kb) {
-    extern __shared__ uint32_t words[];
+    extern __shared__ __align__(16) uint32_t words[];
     const int qblk = blockIdx.x;
     const int64_t bp = blockIdx.y;
-    build_bitmap(words, idx + (bp * S + static_cast<int64_t>(qblk) * kBlock) * Kb, NB, Kb, qblk);
+    const int32_t* tile = stage_rows(words, idx + (bp * S + static_cast<int64_t>(qblk) * kBlock) * Kb, NB, Kb);
+    build_bitmap(words, tile, NB, Kb, qblk);
     uint8_t* crow = counts + (bp * NB + qblk) * NB;
     for (int j = threadIdx.x; j <= qblk; j += blockDim.x) {
         const int c = __popc(words[j * 4]) + __popc(words[j * 4 + 1]) + __popc(words[j * 4 + 2]) + __popc(words[j * 4 + 3]);
@@ -89,28 +104,36 @@ __global__ void __launch_bounds__(1024) rix_rowscan_kernel(const int32_t* __rest
 __global__ void __launch_bounds__(128) rix_fill_kernel(const int32_t* __restrict__ idx, const int32_t* __restrict__ blk_off,
                                                        const int32_t* __restrict__ row_ptr, int32_t* __restrict__ col_q,
                                                        int32_t* __restrict__ edge_pos, int S, int NB, int Kb) {
-    extern __shared__ uint32_t words[];
+    extern __shared__ __align__(16) uint32_t words[];
     const int qblk = blockIdx.x;
     const int64_t bp = blockIdx.y;
     const int64_t row0 = bp * S + static_cast<int64_t>(qblk) * kBlock;
-    build_bitmap(words, idx + row0 * Kb, NB, Kb, qblk);
+    int32_t* tile = stage_rows(words, idx + row0 * Kb, NB, Kb);
+    build_bitmap(words, tile, NB, Kb, qblk);
     const int r = threadIdx.x;
     const int q = qblk * kBlock + r;
-    const int32_t* row = idx + (row0 + r) * Kb;
-    int32_t* erow = edge_pos + (row0 + r) * Kb;
+    int32_t* row = tile + r * Kb;   // the selections of row r; each is replaced by its edge position
+    const int32_t* rp = row_ptr + bp * NB;
+    const int32_t* bo = blk_off + (bp * NB + qblk) * NB;
     const int w = r >> 5;
     const uint32_t below = (1u << (r & 31)) - 1u;
     for (int s = 0; s < Kb; ++s) {
-        const int j = row[s];
+        const int at = rotated_slot(s, r, Kb);
+        const int j = row[at];
         int pos = -1;
         if (static_cast<unsigned>(j) < static_cast<unsigned>(NB) && j <= qblk) {
             int rank = __popc(words[j * 4 + w] & below);
             for (int ww = 0; ww < w; ++ww) rank += __popc(words[j * 4 + ww]);
-            pos = row_ptr[bp * NB + j] + blk_off[(bp * NB + qblk) * NB + j] + rank;
+            pos = rp[j] + bo[j] + rank;
             col_q[pos] = q;
         }
-        erow[s] = pos;
+        row[at] = pos;
     }
+    __syncthreads();
+    // edge positions of the query block leave as one contiguous run
+    const int4* src = reinterpret_cast<const int4*>(tile);
+    int4* dst = reinterpret_cast<int4*>(edge_pos + row0 * Kb);
+    for (int t = threadIdx.x; t < kBlock * Kb / 4; t += blockDim.x) dst[t] = src[t];
 }
 
 struct RixWorkspace {
@@ -142,7 +165,13 @@ int reverse_index_launch(const int32_t* block_indices, int32_t* row_ptr, int32_t
     const int NB = S / kBlock;
     const RixWorkspace w = carve(scratch, rows_bh, NB);
     const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(rows_bh));
-    const size_t smem = static_cast<size_t>(NB) * 16;
+    const size_t smem = static_cast<size_t>(NB) * 16 + static_cast<size_t>(kBlock) * Kb * sizeof(int32_t);
+    constexpr size_t kSmemCap = 160 * 1024;   // NB <= 2048 and Kb <= 128 need 96 KB; the attribute is set once, to the cap
+    if (smem > kSmemCap || (reinterpret_cast<uintptr_t>(block_indices) & 15u) != 0 || (reinterpret_cast<uintptr_t>(edge_pos) & 15u) != 0)
+        return FMSA_ERR_UNSUPPORTED;
+    if (!ensure_smem_attr(reinterpret_cast<const void*>(rix_count_kernel), kSmemCap) ||
+        !ensure_smem_attr(reinterpret_cast<const void*>(rix_fill_kernel), kSmemCap))
+        return FMSA_ERR_CUDA;
     rix_count_kernel<<<grid, 128, smem, st>>>(block_indices, w.counts, S, NB, Kb);
     const int64_t cols = rows_bh * NB;
     rix_colscan_kernel<<<static_cast<unsigned>((cols + 127) / 128), 128, 0, st>>>(w.counts, w.blk_off, w.totals, rows_bh, NB);

@@ -915,25 +915,56 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
 // -------------------------------------------------------------------------------------------
 // delta[b,h,q] = sum_d out[b,q,h,d] * dout[b,q,h,d]   (flash_msa/flash_msa.py:99)
 // -------------------------------------------------------------------------------------------
+// One CTA per (batch, 32 consecutive query positions): half-warp g takes positions 2g and 2g+1 and walks the heads,
+// each lane reading 16 bytes of the `out` row and of the `dout` row (a half-warp covers one 256-byte row per load, four
+// rows in flight); the sums meet in shared memory so that delta leaves in 128-byte runs along the sequence.
 template <bool FP16>
 __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                                                     int64_t do_sb, int64_t do_ss, int64_t do_sh, float* __restrict__ delta,
                                                     int B, int S, int Hq) {
-    const int lane = threadIdx.x & 31;
-    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (w >= static_cast<int64_t>(B) * S * Hq) return;
-    const int h = static_cast<int>(w % Hq);
-    const int64_t bq = w / Hq;
-    const int q = static_cast<int>(bq % S);
-    const int b = static_cast<int>(bq / S);
-    const uint2 a = *reinterpret_cast<const uint2*>(out + w * kHeadDim + lane * 4);
-    const uint2 d = *reinterpret_cast<const uint2*>(dout + b * do_sb + q * do_ss + h * do_sh + lane * 4);
-    const uint32_t a0 = a.x, a1 = a.y, d0 = d.x, d1 = d.y;
-    float s = act_lo<FP16>(a0) * act_lo<FP16>(d0) + act_hi<FP16>(a0) * act_hi<FP16>(d0) + act_lo<FP16>(a1) * act_lo<FP16>(d1) +
-              act_hi<FP16>(a1) * act_hi<FP16>(d1);
+    extern __shared__ float sdelta[];   // [Hq][32]
+    const int lane = threadIdx.x & 31, l16 = lane & 15;
+    const int g = threadIdx.x >> 4;   // half-warp 0..15
+    const int qblocks = S >> 5;
+    const int b = blockIdx.x / qblocks, q0 = (blockIdx.x % qblocks) << 5;
+    auto dot8 = [](const uint4& a, const uint4& d) {
+        return act_lo<FP16>(a.x) * act_lo<FP16>(d.x) + act_hi<FP16>(a.x) * act_hi<FP16>(d.x) + act_lo<FP16>(a.y) * act_lo<FP16>(d.y) +
+               act_hi<FP16>(a.y) * act_hi<FP16>(d.y) + act_lo<FP16>(a.z) * act_lo<FP16>(d.z) + act_hi<FP16>(a.z) * act_hi<FP16>(d.z) +
+               act_lo<FP16>(a.w) * act_lo<FP16>(d.w) + act_hi<FP16>(a.w) * act_hi<FP16>(d.w);
+    };
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) delta[(static_cast<int64_t>(b) * Hq + h) * S + q] = s;
+    for (int qq = 0; qq < 2; ++qq) {
+        const int ql = 2 * g + qq, q = q0 + ql;
+        const __nv_bfloat16* orow = out + (static_cast<int64_t>(b) * S + q) * Hq * kHeadDim + l16 * 8;
+        const __nv_bfloat16* drow = dout + b * do_sb + q * do_ss + l16 * 8;
+        int h = 0;
+        for (; h + 4 <= Hq; h += 4) {
+            uint4 a[4], d[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a[i] = *reinterpret_cast<const uint4*>(orow + static_cast<int64_t>(h + i) * kHeadDim);
+                d[i] = *reinterpret_cast<const uint4*>(drow + (h + i) * do_sh);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float sum = dot8(a[i], d[i]);
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (l16 == 0) sdelta[(h + i) * 32 + ql] = sum;
+            }
+        }
+        for (; h < Hq; ++h) {
+            const uint4 a = *reinterpret_cast<const uint4*>(orow + static_cast<int64_t>(h) * kHeadDim);
+            const uint4 d = *reinterpret_cast<const uint4*>(drow + h * do_sh);
+            float sum = dot8(a, d);
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (l16 == 0) sdelta[h * 32 + ql] = sum;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < Hq * 32; i += 256)
+        delta[(static_cast<int64_t>(b) * Hq + (i >> 5)) * S + q0 + (i & 31)] = sdelta[i];
 }
 
 // dst = bf16(src * const_scale * factor), factor = *scale_ptr when given (the upstream kl gradient lives on the
@@ -960,17 +991,17 @@ extern "C" int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* 
     using namespace fmsa;
     FMSA_REQUIRE(out && d_out && d_out->ptr && delta && B > 0 && S > 0 && Hq > 0);
     FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
-    FMSA_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7u) == 0 && (reinterpret_cast<uintptr_t>(d_out->ptr) & 7u) == 0);
-    FMSA_REQUIRE(d_out->stride_b % 4 == 0 && d_out->stride_h % 4 == 0 && d_out->stride_s % 4 == 0);
-    const int64_t rows = static_cast<int64_t>(B) * S * Hq;
-    const int64_t grid = (rows + 7) / 8;
-    FMSA_REQUIRE(grid <= 0x7fffffffLL);
+    FMSA_REQUIRE(aligned16(out) && aligned16(d_out->ptr));
+    FMSA_REQUIRE(d_out->stride_b % 8 == 0 && d_out->stride_h % 8 == 0 && d_out->stride_s % 8 == 0);
+    const int64_t grid = static_cast<int64_t>(B) * (S / 32);
+    FMSA_REQUIRE(S % 32 == 0 && grid <= 0x7fffffffLL && Hq * 32 * sizeof(float) <= 48 * 1024);
+    const size_t smem = static_cast<size_t>(Hq) * 32 * sizeof(float);
     if (dtype == FMSA_DTYPE_FP16)
-        delta_kernel<true><<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        delta_kernel<true><<<static_cast<unsigned>(grid), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out->ptr), d_out->stride_b, d_out->stride_s,
         d_out->stride_h, delta, B, S, Hq);
     else
-        delta_kernel<false><<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        delta_kernel<false><<<static_cast<unsigned>(grid), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out->ptr), d_out->stride_b, d_out->stride_s,
         d_out->stride_h, delta, B, S, Hq);
     return check_launch();
