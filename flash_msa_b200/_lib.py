@@ -82,9 +82,11 @@ def _declare(lib):
     lib.fmsa_sparse_bwd.argtypes = [PB, T, T, T, T, T, T, P, P, P, P, P, P, P, c_int64, c_int32, P, P, P, c_int32, c_int32,
                                     c_int32, c_int32, P, P, P, P]
     lib.fmsa_sparse_bwd_combine.restype = c_int
-    lib.fmsa_sparse_bwd_combine.argtypes = [PB, P, P, c_int64, c_int32, P, P, P, P, P, c_int32, c_int32, c_int32, P]
+    lib.fmsa_sparse_bwd_combine.argtypes = [PB, P, P, c_int64, c_int32, P, P, T, T, P, c_int32, c_int32, c_int32, P]
     lib.fmsa_cast_scaled.restype = c_int
     lib.fmsa_cast_scaled.argtypes = [P, P, c_int64, P, c_float, c_int32, P]
+    lib.fmsa_cast_scaled_rows.restype = c_int
+    lib.fmsa_cast_scaled_rows.argtypes = [P, T, c_int32, c_int32, c_int32, P, c_float, c_int32, P]
     lib.fmsa_copy2d_async.restype = c_int
     lib.fmsa_copy2d_async.argtypes = [P, ctypes.c_size_t, P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, P]
 

@@ -761,8 +761,9 @@ struct BwdCombineParams {
     const __nv_bfloat16* dqp_part;
     const int32_t* edge_pos;   // sparse: [B*Hp, S, Kb]
     const int32_t* row_ptr;
-    __nv_bfloat16* dq;         // [B,Hq,S,128]
-    __nv_bfloat16* dqp;        // [B,Hp,S,128] or null
+    __nv_bfloat16* dq;         // (B,Hq,S,128) view: element strides below
+    __nv_bfloat16* dqp;        // (B,Hp,S,128) view or null
+    int32_t dq_sb, dq_sh, dq_ss, dqp_sb, dqp_sh, dqp_ss;   // element strides of the two views (each below 2^31)
     const float* grad_kl;      // device scalar or null (= 1)
     float scale, kl_out_scale; // factors the backward kernel left out of its partial rows
     int S, NB, Hq, Hp, mpp, ppk, Kb;
@@ -818,11 +819,11 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams
         if (proxy) {
             o.x = pack_act<FP16>(a0 * gk, a1 * gk);
             o.y = pack_act<FP16>(a2 * gk, a3 * gk);
-            *reinterpret_cast<uint2*>(P.dqp + (bp * P.S + q) * kHeadDim + lane * 4) = o;
+            *reinterpret_cast<uint2*>(P.dqp + (static_cast<int64_t>(b) * P.dqp_sb + static_cast<int64_t>(p) * P.dqp_sh + static_cast<int64_t>(q) * P.dqp_ss) + lane * 4) = o;
         } else {
             o.x = pack_act<FP16>(a0 * P.scale, a1 * P.scale);
             o.y = pack_act<FP16>(a2 * P.scale, a3 * P.scale);
-            *reinterpret_cast<uint2*>(P.dq + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q) * kHeadDim + lane * 4) = o;
+            *reinterpret_cast<uint2*>(P.dq + (static_cast<int64_t>(b) * P.dq_sb + static_cast<int64_t>(p * P.mpp + hh) * P.dq_sh + static_cast<int64_t>(q) * P.dq_ss) + lane * 4) = o;
         }
     }
 }
@@ -853,39 +854,50 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
     float pa0 = 0.f, pa1 = 0.f, pa2 = 0.f, pa3 = 0.f;   // proxy row: lane owns columns 4*lane..+3
+    // Four edges at a time: every load of the group is issued before the first sum (the kernel is bound by memory
+    // latency; left to itself the compiler batches the loads only when the register budget happens to allow it).
+    const bool has_proxy = P.dqp != nullptr;
     for (int s0 = 0; s0 < nslots; s0 += 32) {
-        const int64_t sl = slot_of(s0 + lane);
+        const int sl = static_cast<int>(slot_of(s0 + lane));   // slot numbers of a pass fit 31 bits
         const int cnt = min(32, nslots - s0);
-#pragma unroll 4
-        for (int i = 0; i < cnt; ++i) {
-            const int64_t si = __shfl_sync(0xffffffffu, sl, i);
-            if (si < 0) continue;
+        for (int i = 0; i < cnt; i += 4) {
+            int si[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = __shfl_sync(0xffffffffu, sl, (i + u) & 31);
+                si[u] = (i + u < cnt) ? v : -1;
+            }
 #pragma unroll
             for (int part = 0; part < (SPLIT ? 2 : 1); ++part) {
-                const int64_t sp = si + part * P.part_slots;
-                const __nv_bfloat16* rec = P.dq_part + sp * P.mpp * kHeadDim;
+                uint4 raw[4][KITER];
+                uint2 praw[4];
 #pragma unroll
-                for (int k = 0; k < KITER; ++k) {
-                    const int ck = k * 32 + lane;
-                    if (ck < nchunk) {
-                        const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
-                        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t sp = static_cast<int64_t>(si[u]) + part * P.part_slots;
+                    const __nv_bfloat16* rec = P.dq_part + sp * P.mpp * kHeadDim;
+#pragma unroll
+                    for (int k = 0; k < KITER; ++k) {
+                        const int ck = k * 32 + lane;
+                        raw[u][k] = (si[u] >= 0 && ck < nchunk) ? *reinterpret_cast<const uint4*>(rec + ck * 8) : make_uint4(0, 0, 0, 0);
+                    }
+                    praw[u] = (si[u] >= 0 && has_proxy) ? *reinterpret_cast<const uint2*>(P.dqp_part + sp * kHeadDim + lane * 4)
+                                                        : make_uint2(0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int k = 0; k < KITER; ++k) {
+                        const uint32_t w4[4] = {raw[u][k].x, raw[u][k].y, raw[u][k].z, raw[u][k].w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const uint32_t v2 = u[e];
-                            acc[k][2 * e] += act_lo<FP16>(v2);
-                            acc[k][2 * e + 1] += act_hi<FP16>(v2);
+                            acc[k][2 * e] += act_lo<FP16>(w4[e]);
+                            acc[k][2 * e + 1] += act_hi<FP16>(w4[e]);
                         }
                     }
-                }
-                if (P.dqp) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(P.dqp_part + sp * kHeadDim + lane * 4);
-                    const uint32_t lo = raw.x;
-                    const uint32_t hi = raw.y;
-                    pa0 += act_lo<FP16>(lo);
-                    pa1 += act_hi<FP16>(lo);
-                    pa2 += act_lo<FP16>(hi);
-                    pa3 += act_hi<FP16>(hi);
+                    pa0 += act_lo<FP16>(praw[u].x);
+                    pa1 += act_hi<FP16>(praw[u].x);
+                    pa2 += act_lo<FP16>(praw[u].y);
+                    pa3 += act_hi<FP16>(praw[u].y);
                 }
             }
         }
@@ -900,7 +912,7 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
             o.y = pack_act<FP16>(acc[k][2] * P.scale, acc[k][3] * P.scale);
             o.z = pack_act<FP16>(acc[k][4] * P.scale, acc[k][5] * P.scale);
             o.w = pack_act<FP16>(acc[k][6] * P.scale, acc[k][7] * P.scale);
-            *reinterpret_cast<uint4*>(P.dq + ((static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q) * kHeadDim + col) = o;
+            *reinterpret_cast<uint4*>(P.dq + (static_cast<int64_t>(b) * P.dq_sb + static_cast<int64_t>(p * P.mpp + hh) * P.dq_sh + static_cast<int64_t>(q) * P.dq_ss) + col) = o;
         }
     }
     if (P.dqp) {
@@ -908,7 +920,7 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_ke
         uint2 o;
         o.x = pack_act<FP16>(pa0 * gk, pa1 * gk);
         o.y = pack_act<FP16>(pa2 * gk, pa3 * gk);
-        *reinterpret_cast<uint2*>(P.dqp + (bp * P.S + q) * kHeadDim + lane * 4) = o;
+        *reinterpret_cast<uint2*>(P.dqp + (static_cast<int64_t>(b) * P.dqp_sb + static_cast<int64_t>(p) * P.dqp_sh + static_cast<int64_t>(q) * P.dqp_ss) + lane * 4) = o;
     }
 }
 
@@ -983,8 +995,51 @@ __global__ void __launch_bounds__(256) cast_scaled_kernel(const float* __restric
     }
 }
 
+// The same cast with a strided destination: src is contiguous fp32 [B,H,S,128], dst a (B,H,S,128) view given by
+// element strides (a gradient written straight into (B,S,H,128) storage).  One thread per four elements.
+template <bool FP16>
+__global__ void __launch_bounds__(256) cast_scaled_rows_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                               int64_t sb, int64_t sh, int64_t ss, int H, int S, int64_t n4,
+                                                               const float* __restrict__ scale_ptr, float const_scale) {
+    const float f = (scale_ptr ? *scale_ptr : 1.f) * const_scale;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const int64_t rowi = i >> 5;                // 32 float4 per row of 128
+        const int c4 = static_cast<int>(i & 31);
+        const int sq = static_cast<int>(rowi % S);
+        const int64_t bh = rowi / S;
+        const int h = static_cast<int>(bh % H);
+        const int64_t b = bh / H;
+        const float4 v = reinterpret_cast<const float4*>(src)[i];
+        uint2 o;
+        o.x = pack_act<FP16>(v.x * f, v.y * f);
+        o.y = pack_act<FP16>(v.z * f, v.w * f);
+        *reinterpret_cast<uint2*>(dst + b * sb + h * sh + sq * ss + c4 * 4) = o;
+    }
+}
+
 }  // namespace
 }  // namespace fmsa
+
+extern "C" int fmsa_cast_scaled_rows(const float* src, const fmsa_tensor* dst, int32_t B, int32_t H, int32_t S,
+                                     const float* scale_ptr, float const_scale, int32_t dtype, void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(src && dst && dst->ptr && B > 0 && H > 0 && S > 0);
+    FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
+    FMSA_REQUIRE(aligned16(src) && (reinterpret_cast<uintptr_t>(dst->ptr) & 7u) == 0);
+    FMSA_REQUIRE(dst->stride_b % 4 == 0 && dst->stride_h % 4 == 0 && dst->stride_s % 4 == 0);
+    const int64_t n4 = static_cast<int64_t>(B) * H * S * (kHeadDim / 4);
+    int64_t grid = (n4 + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == FMSA_DTYPE_FP16)
+        cast_scaled_rows_kernel<true><<<static_cast<unsigned>(grid), 256, 0, st>>>(
+            src, static_cast<__nv_bfloat16*>(const_cast<void*>(dst->ptr)), dst->stride_b, dst->stride_h, dst->stride_s, H, S, n4, scale_ptr, const_scale);
+    else
+        cast_scaled_rows_kernel<false><<<static_cast<unsigned>(grid), 256, 0, st>>>(
+            src, static_cast<__nv_bfloat16*>(const_cast<void*>(dst->ptr)), dst->stride_b, dst->stride_h, dst->stride_s, H, S, n4, scale_ptr, const_scale);
+    return check_launch();
+}
 
 extern "C" int fmsa_bwd_delta(const void* out, const fmsa_tensor* d_out, float* delta, int32_t B, int32_t S, int32_t Hq,
                               int32_t dtype, void* stream) {
@@ -1109,20 +1164,31 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
 
 extern "C" int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part,
                                        int64_t part_slots, int32_t split, const int32_t* edge_pos, const int32_t* row_ptr,
-                                       void* dq, void* dq_proxy, const float* grad_kl, int32_t g_begin, int32_t g_count,
-                                       int32_t dense, void* stream) {
+                                       const fmsa_tensor* dq, const fmsa_tensor* dq_proxy, const float* grad_kl,
+                                       int32_t g_begin, int32_t g_count, int32_t dense, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(problem_ok(pb));
-    FMSA_REQUIRE(dq_part && dq);
+    FMSA_REQUIRE(dq_part && dq && dq->ptr);
     FMSA_REQUIRE(dense || (edge_pos && row_ptr));
-    FMSA_REQUIRE(!dq_proxy || dqp_part);
+    FMSA_REQUIRE(!dq_proxy || (dq_proxy->ptr && dqp_part));
+    FMSA_REQUIRE(aligned16(dq->ptr) && dq->stride_b % 8 == 0 && dq->stride_h % 8 == 0 && dq->stride_s % 8 == 0);
+    FMSA_REQUIRE(!dq_proxy || (aligned16(dq_proxy->ptr) && dq_proxy->stride_b % 8 == 0 && dq_proxy->stride_h % 8 == 0 &&
+                               dq_proxy->stride_s % 8 == 0));
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
     FMSA_REQUIRE(!split || part_slots > 0);
     BwdCombineParams P;
     P.dq_part = static_cast<const __nv_bfloat16*>(dq_part); P.dqp_part = static_cast<const __nv_bfloat16*>(dqp_part);
     P.edge_pos = edge_pos; P.row_ptr = row_ptr;
     P.split = split ? 1 : 0; P.part_slots = part_slots;
-    P.dq = static_cast<__nv_bfloat16*>(dq); P.dqp = static_cast<__nv_bfloat16*>(dq_proxy); P.grad_kl = grad_kl;
+    auto fits = [](int64_t x) { return x >= 0 && x < 0x7fffffffLL; };
+    FMSA_REQUIRE(fits(dq->stride_b) && fits(dq->stride_h) && fits(dq->stride_s));
+    FMSA_REQUIRE(!dq_proxy || (fits(dq_proxy->stride_b) && fits(dq_proxy->stride_h) && fits(dq_proxy->stride_s)));
+    P.dq = static_cast<__nv_bfloat16*>(const_cast<void*>(dq->ptr));
+    P.dq_sb = static_cast<int32_t>(dq->stride_b); P.dq_sh = static_cast<int32_t>(dq->stride_h); P.dq_ss = static_cast<int32_t>(dq->stride_s);
+    P.dqp = dq_proxy ? static_cast<__nv_bfloat16*>(const_cast<void*>(dq_proxy->ptr)) : nullptr;
+    P.dqp_sb = dq_proxy ? static_cast<int32_t>(dq_proxy->stride_b) : 0; P.dqp_sh = dq_proxy ? static_cast<int32_t>(dq_proxy->stride_h) : 0;
+    P.dqp_ss = dq_proxy ? static_cast<int32_t>(dq_proxy->stride_s) : 0;
+    P.grad_kl = grad_kl;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hp = pb->Hp; P.mpp = pb->Hq / pb->Hp; P.ppk = pb->Hp / pb->Hkv;
     P.Kb = pb->top_k_blocks; P.g_begin = g_begin; P.G = g_count; P.dense = dense ? 1 : 0;
     P.scale = pb->scale;

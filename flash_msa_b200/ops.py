@@ -194,6 +194,17 @@ def _tensor_arg(t: torch.Tensor) -> "_lib.FmsaTensor":
     return _lib.FmsaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
 
 
+def _grad_like(t: torch.Tensor) -> torch.Tensor:
+    """Uninitialised gradient buffer for the (B,H,S,D) input `t`, in `t`'s own memory layout when `t` is a view of
+    (B,S,H,D) storage (what the reference's callers pass, flash_msa/tests/testing_model.py:173-185): autograd then
+    hands the gradient back through the caller's transpose and reshape as views, with no copy.  Otherwise (B,H,S,D)
+    contiguous."""
+    b, h, s, d = t.shape
+    if t.stride(3) == 1 and t.stride(2) == h * d and t.stride(1) == d and t.stride(0) == s * h * d and h > 1:
+        return torch.empty(b, s, h, d, dtype=t.dtype, device=t.device).transpose(1, 2)
+    return torch.empty(b, h, s, d, dtype=t.dtype, device=t.device)
+
+
 def _dtype_code(dtype) -> int:
     """The library's code of an activation type (bf16 and fp16 are supported, as in the reference:
     flash_msa/msa_backward_cutedsl.py:169-183)."""
@@ -387,8 +398,8 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
         gk = grad_kl.detach().to(device=dev, dtype=torch.float32).reshape(1)
         dkp_acc = torch.zeros(b, hpkv, s, d, dtype=torch.float32, device=dev)
     else:
-        dqp = torch.zeros(b, hp, s, d, dtype=q.dtype, device=dev)
-        dkp = torch.zeros(b, hpkv, s, d, dtype=q.dtype, device=dev)
+        dqp = _grad_like(qp).zero_()
+        dkp = _grad_like(kp).zero_()
     groups = b * hkv
     row_ptr = 0 if dense else rix.row_ptr.data_ptr()
     col_q = 0 if dense else rix.col_q.data_ptr()
@@ -397,13 +408,18 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     kl_norm = float(scale) / float(b * hp * s)
 
     def cast(acc, dst, scale_ptr, const_scale):
-        _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(acc.data_ptr(), dst.data_ptr(), acc.numel(), scale_ptr,
-                                                          float(const_scale), pb.dtype, st), dev)
+        if dst.is_contiguous():
+            _launch("fmsa_cast_scaled", 1, lib.fmsa_cast_scaled(acc.data_ptr(), dst.data_ptr(), acc.numel(), scale_ptr,
+                                                              float(const_scale), pb.dtype, st), dev)
+        else:
+            _launch("fmsa_cast_scaled_rows", 1, lib.fmsa_cast_scaled_rows(
+                acc.data_ptr(), _tensor_arg(dst), acc.shape[0], acc.shape[1], acc.shape[2], scale_ptr, float(const_scale),
+                pb.dtype, st), dev)
 
     # dQ and dQp leave the kernel as per-edge partial rows; a combine pass sums them per query row
-    dq = torch.empty(b, hq, s, d, dtype=q.dtype, device=dev)
+    dq = _grad_like(q)
     if with_kl:
-        dqp = torch.empty(b, hp, s, d, dtype=q.dtype, device=dev)
+        dqp = _grad_like(qp)
     per_group = lib.fmsa_fwd_partial_slots(ctypes_byref(pb), 1, int(dense))
     # A query row's dQ is the sum of one bf16 partial row per selected block.  Beyond ~32 blocks the rounding of the
     # partial rows starts to show against the reference's fp32 accumulation, so each partial is then stored as a
@@ -428,13 +444,14 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
         with _Timed("bwd_combine", dev):
             _launch("fmsa_sparse_bwd_combine", 1, lib.fmsa_sparse_bwd_combine(
                 ctypes_byref(pb), dq_part.data_ptr(), dqp_part.data_ptr() if with_kl else 0, slots, split, edge_pos, row_ptr,
-                dq.data_ptr(), dqp.data_ptr() if with_kl else 0, gk.data_ptr() if with_kl else 0, g0, gc, int(dense), st), dev)
+                _tensor_arg(dq), _tensor_arg(dqp) if with_kl else None, gk.data_ptr() if with_kl else 0, g0, gc, int(dense),
+                st), dev)
 
-    dkv = torch.empty(2, b, hkv, s, d, dtype=q.dtype, device=dev)
+    dk, dv = _grad_like(k), _grad_like(v)
     with _Timed("cast", dev):
-        cast(dkv_acc[0], dkv[0], 0, scale)
-        cast(dkv_acc[1], dkv[1], 0, 1.0)
+        cast(dkv_acc[0], dk, 0, scale)
+        cast(dkv_acc[1], dv, 0, 1.0)
         if with_kl:
-            dkp = torch.empty(b, hpkv, s, d, dtype=q.dtype, device=dev)
+            dkp = _grad_like(kp)
             cast(dkp_acc, dkp, gk.data_ptr(), kl_norm)
-    return dqp, dkp, dq, dkv[0], dkv[1]
+    return dqp, dkp, dq, dk, dv

@@ -195,13 +195,14 @@ int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_ten
                     int32_t* counter, int32_t* status, void* stream);
 
 /* Sums the per-edge contributions of every query row:
- *   dq bf16 [B,Hq,S,128];  dq_proxy bf16 [B,Hp,S,128] (or NULL), multiplied by *grad_kl (device
+ *   dq (B,Hq,S,128) view, written through its `ptr`;  dq_proxy (B,Hp,S,128) view (or NULL), multiplied by *grad_kl (device
  *   scalar, the upstream gradient of kl_loss: flash_msa/flash_msa.py:122-125; NULL = 1).
  * Takes the place of the reference's fp32 atomic accumulation + cast
  * (flash_msa/msa_backward_cutedsl.py:738-836, 1075-1081). */
 int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const void* dqp_part, int64_t part_slots,
-                            int32_t split, const int32_t* edge_pos, const int32_t* row_ptr, void* dq, void* dq_proxy,
-                            const float* grad_kl, int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
+                            int32_t split, const int32_t* edge_pos, const int32_t* row_ptr, const fmsa_tensor* dq,
+                            const fmsa_tensor* dq_proxy, const float* grad_kl, int32_t g_begin, int32_t g_count,
+                            int32_t dense, void* stream);
 
 /* dst[i] = bf16 or fp16 (dtype) of (src[i] * const_scale * f), f = *scale_ptr (a device scalar, e.g. the upstream
  * gradient of kl_loss: flash_msa/flash_msa.py:122-125) or 1 when scale_ptr is NULL.  n % 4 == 0.
@@ -210,6 +211,11 @@ int fmsa_sparse_bwd_combine(const fmsa_problem* pb, const void* dq_part, const v
  * needs scale/(B*Hp*S) times the upstream kl gradient. */
 int fmsa_cast_scaled(const float* src, void* dst, int64_t n, const float* scale_ptr, float const_scale, int32_t dtype,
                      void* stream);
+/* The same cast from a contiguous fp32 [B,H,S,128] accumulator into a (B,H,S,128) VIEW given by element strides, so
+ * that dK, dV and dKp can be written straight into (B,S,H,128) storage, the layout the reference's callers hold
+ * their activations in (flash_msa/tests/testing_model.py:173-185): no transposing copy after the backward. */
+int fmsa_cast_scaled_rows(const float* src, const fmsa_tensor* dst, int32_t B, int32_t H, int32_t S,
+                          const float* scale_ptr, float const_scale, int32_t dtype, void* stream);
 
 /* Asynchronous strided copy between pinned host memory and the device (either direction; inferred
  * from the pointers): `rows` pieces of `width` bytes, source pieces `src_pitch` bytes apart, destination

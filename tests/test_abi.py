@@ -14,7 +14,7 @@ def test_library_builds_and_exports_declared_symbols():
     assert "fmsa_select_topk" in names and "fmsa_reverse_index" in names
     for name in names:
         assert hasattr(lib, name), name
-    assert lib.fmsa_abi_version() == 5          # 5: activation dtype (bf16 / fp16) in fmsa_problem and the stand-alone entry points
+    assert lib.fmsa_abi_version() == 6          # 6: gradients written through (B,H,S,128) views (strided dq / dq_proxy, fmsa_cast_scaled_rows)
 
 
 def test_argument_errors_do_not_launch():
@@ -25,6 +25,7 @@ def test_argument_errors_do_not_launch():
     # null pointers / nonsense sizes are rejected before anything touches the device
     assert lib.fmsa_copy2d_async(None, 0, None, 0, 0, 0, None) == -1
     assert lib.fmsa_cast_scaled(None, None, 16, None, 1.0, 0, None) == -1
+    assert lib.fmsa_cast_scaled_rows(None, None, 1, 1, 128, None, 1.0, 0, None) == -1
     assert lib.fmsa_bwd_delta(None, None, None, 1, 128, 1, 0, None) == -1
     pb = _lib.FmsaProblem(1, 100, 4, 2, 2, 2, 1, 0.1, 0)      # S is not a multiple of 128
     assert lib.fmsa_fwd_partial_slots(ctypes.byref(pb), 1, 0) <= 0

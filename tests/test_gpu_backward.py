@@ -151,3 +151,29 @@ def test_backward_fp16(fm, warmup):
     for n, got, y in zip(NAMES, grads, g16):
         assert got.dtype == torch.float16 and got.shape == r32[n].shape
         yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
+
+
+@pytest.mark.parametrize("warmup", [False, True])
+def test_gradients_in_caller_layout(fm, warmup):
+    """Inputs that are (B,H,S,D) views of (B,S,H,D) storage (the reference's callers: flash_msa/tests/testing_model.py:173-185)
+    get their gradients back in that same storage layout, written there by the kernels (no transposing copy), with
+    exactly the values of a run on (B,H,S,D)-contiguous inputs."""
+    from flash_msa_b200 import ops
+    cfg = CFGS["c1"]
+    views = bf16_inputs(cfg, layout="bshd")
+    plain = bf16_inputs(cfg, layout="bhsd")
+    gk = torch.tensor(0.5, device="cuda")
+    results = []
+    for qp, kp, q, k, v, do in (views, plain):
+        if warmup:
+            rix = None
+            out, lse, lse_p = ops.attention_forward(q, k, v, qp, kp, SCALE, None, dense=True)
+        else:
+            rix = ops.build_reverse_index(ops.select_blocks(qp, kp, scale=SCALE, num_blocks=cfg["s"] // 128, top_k_blocks=cfg["kb"]))
+            out, lse, lse_p = ops.attention_forward(q, k, v, qp, kp, SCALE, rix)
+        go = do if do.dim() == 3 else do.permute(0, 2, 1, 3).reshape(out.shape).contiguous()
+        results.append(ops.attention_backward(q, k, v, qp, kp, out, go, lse, lse_p, SCALE, rix, gk, dense=warmup))
+    for g_view, g_plain, x in zip(results[0], results[1], (views[0], views[1], views[2], views[3], views[4])):
+        assert g_view.stride() == x.stride() and g_view.transpose(1, 2).is_contiguous()
+        assert g_plain.is_contiguous()
+        assert torch.equal(g_view, g_plain)
