@@ -99,19 +99,33 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
             ok = mbar_wait(smem_u32(&sm->s_full[st]), (j >> 1) & 1);
             if (!ok) break;   // every lane of the warp waits on the same phase: uniform
             tc_fence_after_sync();
+            // The factor `scale` is positive, so it is applied once to the row maximum instead of to every logit
+            // (rounding is monotone: the result is the same bit for bit).  Only the diagonal block needs the causal
+            // mask; every other block is a plain maximum over 128 values, taken three at a time with the loads of
+            // the next 32 columns already in flight.
             float m = -INFINITY;
-            const int limit = (j == qt) ? r : 127;   // last visible key column of this row
+            if (j == qt) {
 #pragma unroll 1
-            for (int c = 0; c < 128; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_addr(tmem + st * 128, quarter, c), v);
-                tmem_ld_wait();
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_addr(tmem + st * 128, quarter, c), v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float x = __uint_as_float(v[i]) * scale;
-                    m = (c + i <= limit) ? fmaxf(m, x) : m;
+                    for (int i = 0; i < 32; ++i) m = (c + i <= r) ? fmaxf(m, __uint_as_float(v[i])) : m;
+                }
+            } else {
+                uint32_t v[2][32];
+                tmem_ld32(tmem_addr(tmem + st * 128, quarter, 0), v[0]);
+#pragma unroll
+                for (int c = 0; c < 128; c += 32) {
+                    const int cur = (c >> 5) & 1;
+                    tmem_ld_wait();
+                    if (c + 32 < 128) tmem_ld32(tmem_addr(tmem + st * 128, quarter, c + 32), v[cur ^ 1]);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) m = fmax3(m, __uint_as_float(v[cur][i]), __uint_as_float(v[cur][i + 1]));
                 }
             }
+            m *= scale;
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&sm->s_empty[st]));
             sm->stage[r][j % kScoreStageCols] = m;
@@ -147,6 +161,7 @@ extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor*
     FMSA_REQUIRE(q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && block_scores && status);
     FMSA_REQUIRE(B > 0 && Hp > 0 && Hpkv > 0 && Hp % Hpkv == 0 && S > 0 && S % kBlock == 0);
     FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
+    FMSA_REQUIRE(scale > 0.f);   // the kernel scales the block maximum, not every logit
     FMSA_REQUIRE(static_cast<int64_t>(B) * Hp <= 65535);
     FMSA_REQUIRE(tma_compatible(q_proxy->ptr, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s));
     FMSA_REQUIRE(tma_compatible(k_proxy->ptr, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s));
