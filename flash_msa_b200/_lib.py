@@ -69,7 +69,7 @@ def _declare(lib):
     T = ctypes.POINTER(FmsaTensor)
     PB = ctypes.POINTER(FmsaProblem)
     lib.fmsa_select_scores.restype = c_int
-    lib.fmsa_select_scores.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, P, P]
+    lib.fmsa_select_scores.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, P, P, P]
     lib.fmsa_fwd_partial_slots.restype = c_int64
     lib.fmsa_fwd_partial_slots.argtypes = [PB, c_int32, c_int32]
     lib.fmsa_sparse_fwd.restype = c_int
@@ -94,7 +94,8 @@ def _declare(lib):
 class FmsaProblem(ctypes.Structure):
     """Mirror of ``fmsa_problem``."""
     _fields_ = [("B", c_int32), ("S", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("Hp", c_int32),
-                ("Hpkv", c_int32), ("top_k_blocks", c_int32), ("scale", c_float), ("dtype", c_int32)]
+                ("Hpkv", c_int32), ("top_k_blocks", c_int32), ("scale", c_float), ("dtype", c_int32),
+                ("doc_start", ctypes.c_void_p)]
 
 
 def check(status: int, what: str) -> None:

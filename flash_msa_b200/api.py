@@ -104,15 +104,16 @@ def check_pending_status():
 
 class _SparseAttentionFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale):
+    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale, doc_start=None):
         num_blocks, top_k_blocks = _validate_inputs(q_proxy, k_proxy, q, k, v, int(top_k), True)
         _require_cuda(q)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
-        scores = ops.proxy_block_scores(q_proxy, k_proxy, float(scale), status=status)
+        scores = ops.proxy_block_scores(q_proxy, k_proxy, float(scale), status=status, doc_start=doc_start)
         block_indices = ops.select_topk(scores, top_k_blocks)
         del scores
         rix = ops.build_reverse_index(block_indices)
-        out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), rix, status=status)
+        out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), rix, status=status,
+                                                         doc_start=doc_start)
         _maybe_check(status, "flash_msa_func forward")
         # kl_loss is a placeholder whose gradient switches the KL branch of the backward on
         # (reference: flash_msa/msa_forward_cutedsl.py:69)
@@ -123,6 +124,7 @@ class _SparseAttentionFunction(torch.autograd.Function):
         ctx.set_materialize_grads(False)
         ctx.scale = float(scale)
         ctx.top_k_blocks = top_k_blocks
+        ctx.doc_start = doc_start
         return out, kl_loss
 
     @staticmethod
@@ -135,10 +137,11 @@ class _SparseAttentionFunction(torch.autograd.Function):
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         klv = _kl_buffer(grad_kl, q.device)
         dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
-                                                      ctx.scale, rix, grad_kl, status=status, kl_value=klv)
+                                                      ctx.scale, rix, grad_kl, status=status, kl_value=klv,
+                                                      doc_start=ctx.doc_start)
         _publish_kl(klv)
         _maybe_check(status, "flash_msa_func backward")
-        return dqp, dkp, dq, dk, dv, None, None
+        return dqp, dkp, dq, dk, dv, None, None, None
 
 
 class _WarmupSparseAttentionFunction(torch.autograd.Function):
@@ -174,7 +177,21 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
 
 def sparse_attention(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
     """Block-sparse top-k GQA attention.  Returns ``(attn_out [B,S,Hq*D], kl_loss placeholder)``."""
-    return _SparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale))
+    return _SparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), None)
+
+
+def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float):
+    """`sparse_attention` on packed sequences: the S positions of every batch element hold several documents laid end
+    to end, `cu_seqlens` ([n+1], or [B,n+1] for a packing per batch element; starts at 0, ends at S: the FlashAttention
+    varlen convention) gives their boundaries, and a query sees only the keys of its own document - in the block scores
+    and the selection, in the attention and in every gradient.  Blocks stay 128 positions of the PACKED sequence, so S
+    must still be a multiple of 128 (pad the last document).  The reference has no such path (its README lists
+    variable-length batches as missing)."""
+    if q.ndim != 4:
+        raise ValueError("all attention tensors must have shape (B, H, S, D)")
+    _require_cuda(q)
+    doc_start = ops.doc_start_from_cu_seqlens(cu_seqlens, q.shape[0], q.shape[2], q.device)
+    return _SparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), doc_start)
 
 
 def sparse_attention_warmup(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):

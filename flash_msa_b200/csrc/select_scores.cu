@@ -30,7 +30,8 @@ template <bool FP16>
 __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                             const __grid_constant__ CUtensorMap tmap_k,
                                                             float* __restrict__ block_scores, int Hp, int pg, int S,
-                                                            int NB, float scale, int* __restrict__ status) {
+                                                            int NB, float scale, const int32_t* __restrict__ doc_start,
+                                                            int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t tile_q = tiles, tile_k0 = tiles + kTileBytes;
@@ -94,6 +95,10 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
     } else {
         const int quarter = warp & 3;            // TMEM lane quarter this warp may read
         const int r = quarter * 32 + lane;        // row of the query tile
+        // Document masking of a packed sequence: keys before the first token of the row's document are hidden
+        // (lo = 0 without documents).
+        const int lo = doc_start ? doc_start[static_cast<int64_t>(b) * S + qt * kBlock + r] : 0;
+        const int lo_blk = lo >> 7, lo_col = lo & 127;
         for (int j = 0; j <= qt; ++j) {
             const int st = j & 1;
             ok = mbar_wait(smem_u32(&sm->s_full[st]), (j >> 1) & 1);
@@ -104,14 +109,16 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
             // mask; every other block is a plain maximum over 128 values, taken three at a time with the loads of
             // the next 32 columns already in flight.
             float m = -INFINITY;
-            if (j == qt) {
+            const bool low_edge = (j == lo_blk) && lo_col > 0;   // the row's document starts inside this block
+            if (j == qt || __any_sync(0xffffffffu, low_edge)) {
+                const int c_lo = low_edge ? lo_col : 0, c_hi = (j == qt) ? r : 127;
 #pragma unroll 1
                 for (int c = 0; c < 128; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(tmem_addr(tmem + st * 128, quarter, c), v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) m = (c + i <= r) ? fmaxf(m, __uint_as_float(v[i])) : m;
+                    for (int i = 0; i < 32; ++i) m = (c + i >= c_lo && c + i <= c_hi) ? fmaxf(m, __uint_as_float(v[i])) : m;
                 }
             } else {
                 uint32_t v[2][32];
@@ -126,6 +133,7 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
                 }
             }
             m *= scale;
+            if (j < lo_blk) m = -INFINITY;   // the whole block lies before the row's document
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&sm->s_empty[st]));
             sm->stage[r][j % kScoreStageCols] = m;
@@ -156,7 +164,7 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
 
 extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores,
                                   int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype,
-                                  int32_t* status, void* stream) {
+                                  const int32_t* doc_start, int32_t* status, void* stream) {
     using namespace fmsa;
     FMSA_REQUIRE(q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && block_scores && status);
     FMSA_REQUIRE(B > 0 && Hp > 0 && Hpkv > 0 && Hp % Hpkv == 0 && S > 0 && S % kBlock == 0);
@@ -177,7 +185,7 @@ extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor*
     if (!ensure_smem_attr(kfn, smem)) return FMSA_ERR_CUDA;
     const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(B * Hp));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (fp16) select_scores_kernel<true><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, status);
-    else select_scores_kernel<false><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, status);
+    if (fp16) select_scores_kernel<true><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, doc_start, status);
+    else select_scores_kernel<false><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, doc_start, status);
     return check_launch();
 }

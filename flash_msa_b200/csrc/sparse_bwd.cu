@@ -51,6 +51,7 @@ struct BwdParams {
     const float *lse, *lse_proxy, *delta;   // [B,Hq,S], [B,Hp,S], [B,Hq,S]
     const int32_t* row_ptr;
     const int32_t* col_q;
+    const int32_t* doc_start;   // [B,S] first token of each token's document (packed sequences), or null
     __nv_bfloat16* dq_part;    // [(edge - edge_base) * mpp + head][128]: per-edge dQ contributions (unscaled)
     __nv_bfloat16* dqp_part;   // [(edge - edge_base)][128]: per-edge dQp contributions (unscaled)
     int64_t part_slots;        // slots per plane of the two buffers above
@@ -68,9 +69,11 @@ struct BwdParams {
     float kl_value_scale;   // ln(2) / (B*Hp*S)
 };
 
-struct BwdUnit {
-    int32_t j, b, kvh, p, n, chunk0, chunk1, pad;   // chunk1 < 0: no more work
+struct BwdUnit {   // (kept small: the control block shares the last 3 KB of shared memory with the row statistics)
     int64_t e0;
+    int32_t n;
+    uint16_t j, b, kvh, p, chunk0;   // (B*Hp < 65536 and S/128 <= 2048 are required by the entry point)
+    int16_t chunk1;                  // < 0: no more work
 };
 
 constexpr int kBwdUnitRing = 8;
@@ -80,6 +83,8 @@ struct alignas(16) BwdRowStats {   // (filled and read with 16-byte vector acces
     float neg_lse[128];    // -lse * log2(e); -inf for a dead row, whose probabilities then come out as 0
     float neg_delta[128];  // -delta
     uint8_t limit[128];    // last visible key of the row inside this key block (127 = all)
+    uint8_t low[128];      // first visible key (0 = all, 128 = none): document masking; written only with documents
+    int32_t any_low;       // some row of the tile has low > 0
 };
 
 struct BwdCtrl {
@@ -125,7 +130,9 @@ constexpr int kStatusBadSmem = 3;   // the dynamic shared memory window does not
 // st_full <- st_empty (row statistics); sdp_full (S^T and dP^T of a tile), pds_full (P^T, dS^T written), dq_full,
 // r0_free (dQ read out), ds_free (the dS^T tile, which doubles as the staging tile of the dQ store, is reusable),
 // dkp_full / r1_free (proxy tile), acc_full / acc_free (dV, dK flushed at the end of a sub-unit).
-template <bool FP16>
+// VARLEN: document masking of packed sequences (P.doc_start given).  A separate instantiation, so that the plain kernel
+// carries none of its registers or code.
+template <bool FP16, bool VARLEN>
 __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                     const __grid_constant__ CUtensorMap tmap_do,
                                                                     const __grid_constant__ CUtensorMap tmap_qp,
@@ -265,9 +272,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                     n = P.row_ptr[bp * P.NB + su.j + 1] - static_cast<int>(e0);
                 }
                 if (su.chunk0 * kBlock < n) {
-                    nu.j = su.j; nu.b = b; nu.kvh = kvh; nu.p = p; nu.n = n; nu.e0 = e0;
-                    nu.chunk0 = su.chunk0;
-                    nu.chunk1 = min((n + kBlock - 1) / kBlock, su.chunk0 + kChunksPerSubUnit);
+                    nu.j = static_cast<uint16_t>(su.j); nu.b = static_cast<uint16_t>(b); nu.kvh = static_cast<uint16_t>(kvh);
+                    nu.p = static_cast<uint16_t>(p); nu.n = n; nu.e0 = e0;
+                    nu.chunk0 = static_cast<uint16_t>(su.chunk0);
+                    nu.chunk1 = static_cast<int16_t>(min((n + kBlock - 1) / kBlock, su.chunk0 + kChunksPerSubUnit));
                     break;
                 }
             }
@@ -374,13 +382,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                 __syncwarp();
                 for (int chunk = ud.chunk0; chunk < ud.chunk1 && !bad; ++chunk) {
                     int qid[4];
-                    uint32_t lim4 = 0;
+                    uint32_t lim4 = 0, low4 = 0;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         qid[i] = row_qid(ud, chunk * kBlock + 4 * lane + i);
                         const uint32_t lim = (qid[i] >= 0 && (qid[i] >> 7) == ud.j) ? static_cast<uint32_t>(qid[i] & 127) : 127u;
                         lim4 |= lim << (8 * i);
+                        if (VARLEN && qid[i] >= 0) {
+                            const int lo = P.doc_start[static_cast<int64_t>(ud.b) * P.S + qid[i]];
+                            const int lb = lo >> 7;
+                            low4 |= static_cast<uint32_t>(lb < ud.j ? 0 : (lb == ud.j ? (lo & 127) : 128)) << (8 * i);
+                        }
                     }
+                    const bool any_low = VARLEN && __any_sync(0xffffffffu, low4 != 0);
                     for (int hh = 0; hh < hpc && !bad; ++hh, ++gt) {
                         const uint32_t s = gt & 1;
                         const bool proxy = hh == P.mpp;
@@ -405,6 +419,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                         reinterpret_cast<float4*>(st->neg_lse)[lane] = make_float4(nl[0], nl[1], nl[2], nl[3]);
                         reinterpret_cast<float4*>(st->neg_delta)[lane] = make_float4(dl[0], dl[1], dl[2], dl[3]);
                         reinterpret_cast<uint32_t*>(st->limit)[lane] = lim4;
+                        if (VARLEN) {
+                            reinterpret_cast<uint32_t*>(st->low)[lane] = low4;
+                            if (lane == 0) st->any_low = any_low ? 1 : 0;
+                        }
                         warp_arrive(BAR(sm->st_full[s]));
                     }
                 }
@@ -632,7 +650,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                 tc_fence_after_sync();
                 const BwdRowStats* st = &sm->stats[s];
                 // only the first chunk of a reverse-index row can hold rows of the key block itself
-                const bool masked = (chunk == 0);
+                const bool own = (chunk == 0);
+                const bool masked = own || (VARLEN && st->any_low != 0);
                 // The body is instantiated per (masked, proxy) combination: the common tile (neither) must not pay for
                 // predicated-off mask arithmetic or per-element branches in its inner loop, which is bound by instruction issue.
                 auto compute_tile = [&](auto masked_c, auto proxy_c) __attribute__((always_inline)) {
@@ -652,9 +671,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                             if (!kProxy) tmem_ld16(tmem_addr(r1, quarter, cbase + c + 16), dv[cur ^ 1]);
                         }
                         uint32_t lim[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+                        uint32_t lw[4] = {0u, 0u, 0u, 0u};
                         if (kMasked) {
-                            const uint4 l4 = *reinterpret_cast<const uint4*>(&st->limit[cbase + c]);
-                            lim[0] = l4.x; lim[1] = l4.y; lim[2] = l4.z; lim[3] = l4.w;
+                            if (own) {
+                                const uint4 l4 = *reinterpret_cast<const uint4*>(&st->limit[cbase + c]);
+                                lim[0] = l4.x; lim[1] = l4.y; lim[2] = l4.z; lim[3] = l4.w;
+                            }
+                            if (VARLEN) {
+                                const uint4 w4 = *reinterpret_cast<const uint4*>(&st->low[cbase + c]);
+                                lw[0] = w4.x; lw[1] = w4.y; lw[2] = w4.z; lw[3] = w4.w;
+                            }
                         }
                         uint32_t pk[8], dk[8];
 #pragma unroll
@@ -666,8 +692,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_kernel(const __grid
                             if (kMasked) {
                                 const int l0 = static_cast<int>((lim[i >> 2] >> (8 * (i & 3))) & 0xffu);
                                 const int l1 = static_cast<int>((lim[i >> 2] >> (8 * ((i + 1) & 3))) & 0xffu);
-                                p0 = (row <= l0) ? p0 : 0.f;
-                                p1 = (row <= l1) ? p1 : 0.f;
+                                if (VARLEN) {
+                                    const int w0 = static_cast<int>((lw[i >> 2] >> (8 * (i & 3))) & 0xffu);
+                                    const int w1 = static_cast<int>((lw[i >> 2] >> (8 * ((i + 1) & 3))) & 0xffu);
+                                    p0 = (row <= l0 && row >= w0) ? p0 : 0.f;
+                                    p1 = (row <= l1 && row >= w1) ? p1 : 0.f;
+                                } else {
+                                    p0 = (row <= l0) ? p0 : 0.f;
+                                    p1 = (row <= l1) ? p1 : 0.f;
+                                }
                             }
                             const int ti = (c + i) >> 1;
                             if (!kProxy) {
@@ -1096,6 +1129,8 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
     FMSA_REQUIRE(dense || (pb->top_k_blocks >= 1 && pb->top_k_blocks <= pb->S / kBlock));
     FMSA_REQUIRE(pb->scale > 0.f);
+    if (dense && pb->doc_start) return FMSA_ERR_UNSUPPORTED;   // document masking: sparse paths only
+    FMSA_REQUIRE(static_cast<int64_t>(pb->B) * pb->Hp <= 65535 && pb->S / kBlock <= 32767);   // 16-bit fields of the sub-unit record
     if (part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
     FMSA_REQUIRE(tma_compatible(k->ptr, k->stride_b, k->stride_h, k->stride_s));
     FMSA_REQUIRE(tma_compatible(v->ptr, v->stride_b, v->stride_h, v->stride_s));
@@ -1135,7 +1170,7 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.q_rows_total = static_cast<int32_t>(q_rows); P.do_rows_total = static_cast<int32_t>(do_rows);
     P.qp_rows_total = static_cast<int32_t>(qp_rows);
     P.lse = lse; P.lse_proxy = lse_proxy; P.delta = delta;
-    P.row_ptr = row_ptr; P.col_q = col_q;
+    P.row_ptr = row_ptr; P.col_q = col_q; P.doc_start = pb->doc_start;
     P.dq_part = static_cast<__nv_bfloat16*>(dq_part); P.dqp_part = static_cast<__nv_bfloat16*>(dqp_part);
     P.part_slots = part_slots; P.split = split ? 1 : 0;
     P.dkp_acc = dkp_acc; P.dk_acc = dk_acc; P.dv_acc = dv_acc;
@@ -1151,14 +1186,18 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int sms = device_sm_count();
     const bool fp16 = pb->dtype == FMSA_DTYPE_FP16;
-    const void* kfn = fp16 ? reinterpret_cast<const void*>(sparse_bwd_kernel<true>) : reinterpret_cast<const void*>(sparse_bwd_kernel<false>);
+    const bool varlen = P.doc_start != nullptr;
+    const void* kfn = fp16 ? (varlen ? reinterpret_cast<const void*>(sparse_bwd_kernel<true, true>) : reinterpret_cast<const void*>(sparse_bwd_kernel<true, false>))
+                           : (varlen ? reinterpret_cast<const void*>(sparse_bwd_kernel<false, true>) : reinterpret_cast<const void*>(sparse_bwd_kernel<false, false>));
     if (sms <= 0 || !ensure_smem_attr(kfn, kBwdSmemBytes)) return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    if (fp16) sparse_bwd_kernel<true><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
-    else sparse_bwd_kernel<false><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
+    if (fp16 && varlen) sparse_bwd_kernel<true, true><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
+    else if (fp16) sparse_bwd_kernel<true, false><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
+    else if (varlen) sparse_bwd_kernel<false, true><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
+    else sparse_bwd_kernel<false, false><<<grid, kBwdThreads, kBwdSmemBytes, st>>>(tq, tdo, tqp, tk, tv, tkp, tdq, tdqp, P);
     return check_launch();
 }
 

@@ -47,6 +47,7 @@ struct FwdParams {
     int32_t q_rows_total, qp_rows_total;   // first row index outside the views (reads as zeros)
     const int32_t* row_ptr;
     const int32_t* col_q;
+    const int32_t* doc_start;   // [B,S] first token of each token's document (packed sequences), or null
     __nv_bfloat16* o_part;   // [(edge - edge_base) * mpp + head][128]
     float* stat_part;        // [(edge - edge_base) * (mpp + 1) + head][2] = (row max in the log2 domain, row sum);
                              // head == mpp is the proxy head
@@ -113,7 +114,9 @@ static_assert(kFwdSmemBytes <= 232448, "shared memory budget of one CTA");
 // P V(t+1) waits until O(t) has been read out, which takes far less time than a softmax.
 // The register file is re-divided between the warpgroups (setmaxnreg): the softmax and output groups get what the
 // gather and issue warps do not need.
-template <bool FP16>
+// VARLEN: document masking of packed sequences (P.doc_start given).  A separate instantiation, so that the plain kernel
+// carries none of its registers or code.
+template <bool FP16, bool VARLEN>
 __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                     const __grid_constant__ CUtensorMap tmap_qp,
                                                                     const __grid_constant__ CUtensorMap tmap_k,
@@ -385,6 +388,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     }
                     sm->limits[(cbase + chunk - ud.chunk0) & (kLimitRing - 1)][16 * g + lane] =
                         (q >= 0 && (q >> 7) == ud.j) ? static_cast<uint8_t>(q & 127) : static_cast<uint8_t>(127);
+
                 }
                 int qr[4];
 #pragma unroll
@@ -487,8 +491,25 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
             const int ntiles = (ud.chunk1 - ud.chunk0) * hpc;
             const int64_t slot_base = ud.e0 - edge_base;
             int hh = 0, chunk = ud.chunk0;
+            int low = 0, low_chunk = -1;   // document masking: first visible key of this thread's row in the chunk `low_chunk`
             for (int t = 0; t < ntiles && !bad; ++t, ++gt) {
                 if ((gt & 1) == wg) {
+                    if (VARLEN && low_chunk != chunk) {
+                        // Keys before the first token of the row's document are hidden (0 = none of this block, 128 = all
+                        // of it).  The row looks its own query position and document start up: shared memory has no room
+                        // for a second per-row array, and only packed-sequence calls pay for the two loads.
+                        const int at = chunk * kBlock + row;
+                        low = 0;
+                        if (at < ud.n) {
+                            const int q = P.col_q[ud.e0 + at];
+                            if (static_cast<unsigned>(q) < static_cast<unsigned>(P.S)) {
+                                const int lo = P.doc_start[static_cast<int64_t>(ud.b) * P.S + q];
+                                const int lb = lo >> 7;
+                                low = lb < ud.j ? 0 : (lb == ud.j ? (lo & 127) : 128);
+                            }
+                        }
+                        low_chunk = chunk;
+                    }
                     const uint32_t ts = tmem_s0 + sb * 128;
                     const bool is_proxy = hh == P.mpp;
                     const int nrows = min(kBlock, ud.n - chunk * kBlock);
@@ -496,8 +517,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                     if (bad) break;
                     tc_fence_after_sync();
                     // only the first chunk of a reverse-index row can hold rows of the key block itself
-                    const bool masked = (chunk == 0);
-                    const int limit = masked ? sm->limits[(cbase + chunk - ud.chunk0) & (kLimitRing - 1)][row] : 127;
+                    const bool masked = (chunk == 0) || (VARLEN && __any_sync(0xffffffffu, low > 0));
+                    const int limit = (chunk == 0) ? sm->limits[(cbase + chunk - ud.chunk0) & (kLimitRing - 1)][row] : 127;
                     float m = 0.f, l = 0.f;
                     {
                         const bool kMasked = masked, kProxy = is_proxy;
@@ -510,9 +531,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         float mloc = -INFINITY;
                         auto piece_max = [&](const uint32_t (&v)[32], int c) __attribute__((always_inline)) {
                             if (kMasked) {
-                                const int lc = limit - c;
+                                const int lc = limit - c, wc = low - c;
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) mloc = (i <= lc) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
+                                for (int i = 0; i < 32; ++i) mloc = (i <= lc && (!VARLEN || i >= wc)) ? fmaxf(mloc, __uint_as_float(v[i])) : mloc;
                             } else {
 #pragma unroll
                                 for (int i = 0; i < 32; i += 2) mloc = fmax3(mloc, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
@@ -533,15 +554,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         float2 l2 = make_float2(0.f, 0.f);
                         auto piece_exp = [&](const uint32_t (&v)[32], int c) __attribute__((always_inline)) {
                             uint32_t pk[16];
-                            const int lc = limit - c;
+                            const int lc = limit - c, wc = low - c;
 #pragma unroll
                             for (int i = 0; i < 32; i += 2) {
                                 const float2 a = f2_fma(f2_from_bits(v[i], v[i + 1]), sc2, nm2);
                                 float p0 = fast_exp2(a.x);
                                 float p1 = fast_exp2(a.y);
                                 if (kMasked) {
-                                    p0 = (i <= lc) ? p0 : 0.f;
-                                    p1 = (i + 1 <= lc) ? p1 : 0.f;
+                                    p0 = (i <= lc && (!VARLEN || i >= wc)) ? p0 : 0.f;
+                                    p1 = (i + 1 <= lc && (!VARLEN || i + 1 >= wc)) ? p1 : 0.f;
                                 }
                                 l2 = f2_add(l2, make_float2(p0, p1));
                                 pk[i >> 1] = pack_act<FP16>(p0, p1);
@@ -840,6 +861,7 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     FMSA_REQUIRE(!with_proxy || (q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr));
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
     FMSA_REQUIRE(dense || (pb->top_k_blocks >= 1 && pb->top_k_blocks <= pb->S / kBlock));
+    if (dense && pb->doc_start) return FMSA_ERR_UNSUPPORTED;   // document masking: sparse paths only
     FMSA_REQUIRE(pb->scale > 0.f);
     if (part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
     FMSA_REQUIRE(tma_compatible(k->ptr, k->stride_b, k->stride_h, k->stride_s));
@@ -869,7 +891,7 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     P.q_row_b = q->stride_b / 128; P.q_row_h = q->stride_h / 128; P.q_row_s = q->stride_s / 128;
     P.qp_row_b = qpx->stride_b / 128; P.qp_row_h = qpx->stride_h / 128; P.qp_row_s = qpx->stride_s / 128;
     P.q_rows_total = static_cast<int32_t>(q_rows); P.qp_rows_total = static_cast<int32_t>(qp_rows);
-    P.row_ptr = row_ptr; P.col_q = col_q;
+    P.row_ptr = row_ptr; P.col_q = col_q; P.doc_start = pb->doc_start;
     P.o_part = static_cast<__nv_bfloat16*>(o_part); P.stat_part = lse_part;
     P.counter = counter; P.status = status;
     P.S = pb->S; P.NB = pb->S / kBlock; P.Hq = pb->Hq; P.Hkv = pb->Hkv; P.Hp = pb->Hp;
@@ -880,14 +902,18 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int sms = device_sm_count();
     const bool fp16 = pb->dtype == FMSA_DTYPE_FP16;
-    const void* kfn = fp16 ? reinterpret_cast<const void*>(sparse_fwd_kernel<true>) : reinterpret_cast<const void*>(sparse_fwd_kernel<false>);
+    const bool varlen = P.doc_start != nullptr;
+    const void* kfn = fp16 ? (varlen ? reinterpret_cast<const void*>(sparse_fwd_kernel<true, true>) : reinterpret_cast<const void*>(sparse_fwd_kernel<true, false>))
+                           : (varlen ? reinterpret_cast<const void*>(sparse_fwd_kernel<false, true>) : reinterpret_cast<const void*>(sparse_fwd_kernel<false, false>));
     if (sms <= 0 || !ensure_smem_attr(kfn, kFwdSmemBytes)) return FMSA_ERR_CUDA;
     if (cudaMemsetAsync(counter, 0, sizeof(int32_t), st) != cudaSuccess) return FMSA_ERR_CUDA;
     P.n_subunits = g_count * subunits_per_group(P.NB, P.ppk, kChunksPerSubUnit);
     FMSA_REQUIRE(P.n_subunits < 0x7fffffffLL);
     const int grid = static_cast<int>(P.n_subunits < sms ? P.n_subunits : sms);
-    if (fp16) sparse_fwd_kernel<true><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
-    else sparse_fwd_kernel<false><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
+    if (fp16 && varlen) sparse_fwd_kernel<true, true><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
+    else if (fp16) sparse_fwd_kernel<true, false><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
+    else if (varlen) sparse_fwd_kernel<false, true><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
+    else sparse_fwd_kernel<false, false><<<grid, kFwdThreads, kFwdSmemBytes, st>>>(tq, tqp, tk, tv, tkp, to, P);
     return check_launch();
 }
 

@@ -215,10 +215,35 @@ def _dtype_code(dtype) -> int:
     raise TypeError(f"flash_msa_b200 supports bf16 and fp16 activations, got {dtype}")
 
 
-def _problem(q, k, q_proxy, k_proxy, top_k_blocks, scale) -> "_lib.FmsaProblem":
+def _problem(q, k, q_proxy, k_proxy, top_k_blocks, scale, doc_start=None) -> "_lib.FmsaProblem":
     b, hq, s, _ = q.shape
     return _lib.FmsaProblem(b, s, hq, k.shape[1], q_proxy.shape[1], k_proxy.shape[1], int(top_k_blocks), float(scale),
-                            _dtype_code(q.dtype))
+                            _dtype_code(q.dtype), doc_start.data_ptr() if doc_start is not None else None)
+
+
+def doc_start_from_cu_seqlens(cu_seqlens, batch: int, seq_len: int, device) -> torch.Tensor:
+    """int32 [B,S] on `device`: for every token of a packed sequence the position of the first token of its document.
+    `cu_seqlens` is [n+1] (one packing for every batch element) or [B,n+1]; it starts at 0 and ends at `seq_len`
+    (the FlashAttention varlen convention).  The kernels take this array (`fmsa_problem.doc_start`)."""
+    cu = torch.as_tensor(cu_seqlens).to(device=device, dtype=torch.int64)
+    if cu.dim() == 1:
+        cu = cu.unsqueeze(0).expand(batch, -1)
+    if cu.dim() != 2 or cu.shape[0] != batch or cu.shape[1] < 2:
+        raise ValueError("cu_seqlens must have shape [n+1] or [B, n+1]")
+    cu = cu.contiguous()
+    if bool((cu[:, 0] != 0).any()) or bool((cu[:, -1] != seq_len).any()) or bool((cu[:, 1:] < cu[:, :-1]).any()):
+        raise ValueError("cu_seqlens must rise from 0 to the sequence length")
+    pos = torch.arange(seq_len, device=device, dtype=torch.int64).unsqueeze(0).expand(batch, -1).contiguous()
+    which = torch.searchsorted(cu, pos, right=True) - 1
+    return torch.gather(cu, 1, which).to(torch.int32).contiguous()
+
+
+def _check_doc_start(doc_start, b, s, dev):
+    if doc_start is None:
+        return None
+    if doc_start.dtype != torch.int32 or tuple(doc_start.shape) != (b, s) or doc_start.device != dev or not doc_start.is_contiguous():
+        raise ValueError("doc_start must be a contiguous int32 [B,S] tensor on the inputs' device")
+    return doc_start
 
 
 _STATUS_NAMES = {1: "a bounded device-side wait timed out", 2: "an out-of-range index was found in metadata",
@@ -278,8 +303,9 @@ class DeferredStatus:
 deferred_status = DeferredStatus()
 
 
-def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, status=None) -> torch.Tensor:
-    """fp32 block scores [B,Hp,S,NB]; entries of future blocks are left unwritten."""
+def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, status=None, doc_start=None) -> torch.Tensor:
+    """fp32 block scores [B,Hp,S,NB]; entries of future blocks are left unwritten.  With `doc_start` (int32 [B,S]) the
+    keys before a row's document are hidden and blocks that lie entirely before it score -inf."""
     _require_cuda(q_proxy, k_proxy)
     if q_proxy.dtype != k_proxy.dtype:
         raise TypeError("q_proxy and k_proxy must have one dtype")
@@ -287,24 +313,26 @@ def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: floa
     b, hp, s, d = q_proxy.shape
     qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
     dev = qp.device
+    doc_start = _check_doc_start(doc_start, b, s, dev)
     scores = torch.empty(b, hp, s, s // BLOCK_SIZE, dtype=torch.float32, device=dev)
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     lib = _lib.load()
     with _Timed("select_scores", dev):
         _launch("fmsa_select_scores", 1, lib.fmsa_select_scores(_tensor_arg(qp), _tensor_arg(kp), scores.data_ptr(), b, hp,
-                                                              kp.shape[1], s, float(scale), code, status.data_ptr(),
-                                                              _stream(dev)), dev)
+                                                              kp.shape[1], s, float(scale), code,
+                                                              doc_start.data_ptr() if doc_start is not None else None,
+                                                              status.data_ptr(), _stream(dev)), dev)
     return scores
 
 
-def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_blocks: int, return_scores=False):
+def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_blocks: int, return_scores=False, doc_start=None):
     """Counterpart of the reference's select_blocks (flash_msa/msa_select_cutedsl.py:481-538)."""
     if q_proxy.ndim != 4 or k_proxy.ndim != 4:
         raise ValueError("q_proxy and k_proxy must have shape (B, H, S, D)")
     if int(num_blocks) != q_proxy.shape[2] // BLOCK_SIZE:
         raise ValueError("num_blocks does not match q_proxy sequence length")
-    scores = proxy_block_scores(q_proxy, k_proxy, scale)
+    scores = proxy_block_scores(q_proxy, k_proxy, scale, doc_start=doc_start)
     idx = select_topk(scores, top_k_blocks)
     return (idx, scores) if return_scores else idx
 
@@ -318,7 +346,7 @@ MAX_PARTIAL_BYTES = int(os.environ.get("FLASH_MSA_B200_MAX_PARTIAL_BYTES", 4 << 
 SPLIT_PARTIALS_ABOVE = 32
 
 
-def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, with_proxy=True, status=None):
+def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, with_proxy=True, status=None, doc_start=None):
     """Sparse (or dense warmup) forward.  Returns (out [B,S,Hq*D] bf16, lse [B,Hq,S] fp32,
     lse_proxy [B,Hp,S] fp32 or None)."""
     _require_cuda(q, k, v)
@@ -329,7 +357,10 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
     hkv, hp = k.shape[1], qp.shape[1]
     mpp = hq // hp
     dev = q.device
-    pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale)
+    doc_start = _check_doc_start(doc_start, q.shape[0], q.shape[2], q.device)
+    if dense and doc_start is not None:
+        raise NotImplementedError("document masking is implemented for the sparse path only")
+    pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale, doc_start)
     out = torch.empty(b, s, hq * d, dtype=q.dtype, device=dev)
     lse = torch.empty(b, hq, s, dtype=torch.float32, device=dev)
     lse_proxy = torch.empty(b, hp, s, dtype=torch.float32, device=dev) if with_proxy else None
@@ -362,7 +393,7 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
 
 
 def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy, scale, rix, grad_kl, *, dense=False,
-                       status=None, kl_value=None):
+                       status=None, kl_value=None, doc_start=None):
     """Fused backward.  ``out`` is the [B,S,Hq*D] forward output, ``grad_out`` its upstream gradient,
     ``grad_kl`` the upstream gradient of kl_loss (0-dim tensor) or None.  Returns
     (dq_proxy, dk_proxy, dq, dk, dv) in the input dtype, shaped like the inputs.
@@ -378,7 +409,10 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     mpp = hq // hp
     dev = q.device
     st = _stream(dev)
-    pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale)
+    doc_start = _check_doc_start(doc_start, q.shape[0], q.shape[2], q.device)
+    if dense and doc_start is not None:
+        raise NotImplementedError("document masking is implemented for the sparse path only")
+    pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale, doc_start)
     with_kl = grad_kl is not None
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)

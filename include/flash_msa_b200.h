@@ -50,6 +50,12 @@ typedef struct {
     int32_t B, S, Hq, Hkv, Hp, Hpkv, top_k_blocks;
     float scale;
     int32_t dtype; /* FMSA_DTYPE_BF16 or FMSA_DTYPE_FP16: the type of every activation, partial row and gradient */
+    /* Document masking of packed sequences (no counterpart in the reference, whose README lists variable-length
+     * batches as missing): NULL, or int32 [B,S] on the device holding, for every token, the position of the first
+     * token of its document (cu_seqlens[i] for the tokens of document i).  A query then sees only the keys of its own
+     * document: block scores, selection, forward and backward all honour it.  Sparse paths only: the dense warmup
+     * entry points refuse it with FMSA_ERR_UNSUPPORTED. */
+    const int32_t* doc_start;
 } fmsa_problem;
 
 /* Library ABI version (bumped on any signature change). */
@@ -127,7 +133,8 @@ int fmsa_reverse_index_static(const int32_t* block_indices, int32_t* row_ptr, in
  * (flash_msa/tests/testing_model.py:75-88); scores are NOT rounded to bf16.
  *   q_proxy (B,Hp,S,128), k_proxy (B,Hpkv,S,128) bf16;  block_scores fp32 [B,Hp,S,S/128];  status int32[1]. */
 int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores, int32_t B,
-                       int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype, int32_t* status, void* stream);
+                       int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype, const int32_t* doc_start,
+                       int32_t* status, void* stream);
 
 /* Sparse forward, stage 1: per-edge partial attention (key-block stationary).
  * Replaces sparse_flash_varlen_forward (flash_msa/sparse_flash_varlen.py:92-261: local-block

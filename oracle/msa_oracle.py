@@ -47,11 +47,39 @@ BLOCK = 128
 # selection
 # ----------------------------------------------------------------------------
 
+def doc_start_from_cu_seqlens(cu_seqlens, s: int, b: int = 1) -> torch.Tensor:
+    """``[B,S]`` int32: for every token of a packed sequence the position of the first token of its
+    document.  ``cu_seqlens`` is ``[n+1]`` (the same packing for every batch element) or ``[B,n+1]``,
+    starts at 0 and ends at ``s`` (the FlashAttention varlen convention)."""
+    cu = torch.as_tensor(cu_seqlens, dtype=torch.int64)
+    if cu.dim() == 1:
+        cu = cu.unsqueeze(0).expand(b, -1)
+    pos = torch.arange(s, dtype=torch.int64)
+    out = torch.empty(b, s, dtype=torch.int32)
+    for i in range(b):
+        c = cu[i].contiguous()
+        if int(c[0]) != 0 or int(c[-1]) != s or bool((c[1:] < c[:-1]).any()):
+            raise ValueError("cu_seqlens must rise from 0 to the sequence length")
+        which = torch.searchsorted(c, pos, right=True) - 1
+        out[i] = c[which].to(torch.int32)
+    return out
+
+
+def _lo(doc_start, b, rows, dev):
+    """[B,1,len(rows),1] first visible key of the query rows (0 without documents)."""
+    if doc_start is None:
+        return torch.zeros(b, 1, rows.stop - rows.start, 1, dtype=torch.int64, device=dev)
+    return doc_start[:, rows].to(device=dev, dtype=torch.int64).view(b, 1, -1, 1)
+
+
 def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float,
-                       dtype=torch.float32) -> torch.Tensor:
+                       dtype=torch.float32, doc_start=None) -> torch.Tensor:
     """``[B,Hp,S,NB]`` block scores: max over the causally visible keys of each
     128-key block of ``scale * Qp . Kp`` (testing_model.py:75-88).  Blocks that lie
-    entirely in the future hold ``-inf``.  The local block is NOT forced here."""
+    entirely in the future hold ``-inf``.  The local block is NOT forced here.
+    ``doc_start`` ([B,S], see doc_start_from_cu_seqlens) additionally hides the keys before the row's
+    own document (document masking of a packed sequence: an extension, the reference has none);
+    blocks that lie entirely before the document hold ``-inf``."""
     b, hp, s, d = q_proxy.shape
     hpkv = k_proxy.shape[1]
     pg = hp // hpkv
@@ -66,7 +94,7 @@ def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: floa
         sc = torch.matmul(qf, keys.transpose(-1, -2)) * scale   # [B,Hp,128,n]
         qpos = torch.arange(i * BLOCK, (i + 1) * BLOCK, device=sc.device).view(-1, 1)
         kpos = torch.arange((i + 1) * BLOCK, device=sc.device).view(1, -1)
-        sc = sc.masked_fill(kpos > qpos, float("-inf"))
+        sc = sc.masked_fill((kpos > qpos) | (kpos.view(1, 1, 1, -1) < _lo(doc_start, b, rows, sc.device)), float("-inf"))
         out[:, :, rows, : i + 1] = sc.view(b, hp, BLOCK, i + 1, BLOCK).amax(dim=-1)
     return out
 
@@ -93,9 +121,9 @@ def stable_topk(block_scores: torch.Tensor, top_k_blocks: int) -> torch.Tensor:
     return idx.to(torch.int32)
 
 
-def select_blocks(q_proxy, k_proxy, scale, top_k_blocks, dtype=torch.float32):
+def select_blocks(q_proxy, k_proxy, scale, top_k_blocks, dtype=torch.float32, doc_start=None):
     """Scores + stable top-k.  Returns ``(block_indices, block_scores)``."""
-    sc = proxy_block_scores(q_proxy, k_proxy, scale, dtype=dtype)
+    sc = proxy_block_scores(q_proxy, k_proxy, scale, dtype=dtype, doc_start=doc_start)
     return stable_topk(sc, top_k_blocks), sc
 
 
@@ -173,7 +201,7 @@ def _row_token_mask(block_indices_rows: torch.Tensor, q0: int, nkeys: int, nb: i
 # ----------------------------------------------------------------------------
 
 def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
-         want_grads: bool):
+         want_grads: bool, doc_start=None):
     """Shared worker.  ``block_indices is None`` means warmup (every causal block)."""
     b, hq, s, d = q.shape
     hkv = k.shape[1]
@@ -212,6 +240,8 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
             vis_p = (kpos <= qpos).view(1, 1, BLOCK, n).expand(b, hp, BLOCK, n)
         else:
             vis_p = _row_token_mask(block_indices[:, :, rows], i * BLOCK, n, nb)   # [B,Hp,128,n]
+        if doc_start is not None:
+            vis_p = vis_p & (torch.arange(n, device=dev).view(1, 1, 1, -1) >= _lo(doc_start, b, rows, dev))
         vis = vis_p.repeat_interleave(mpp, dim=1)                                   # [B,Hq,128,n]
 
         kk = kf[:, :, :n].repeat_interleave(g, dim=1)           # [B,Hq,n,D]
@@ -262,25 +292,25 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
 
 
 def sparse_forward(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None,
-                   dtype=torch.float32):
+                   dtype=torch.float32, doc_start=None):
     """Sparse MSA forward.  Returns dict(out [B,S,Hq*D], lse [B,Hq,S], lse_proxy
     [B,Hp,S], kl scalar, block_indices)."""
     kb = int(top_k) // BLOCK
     if block_indices is None:
-        block_indices, _ = select_blocks(q_proxy, k_proxy, scale, kb, dtype=dtype)
-    r = _run(q_proxy, k_proxy, q, k, v, scale, block_indices, None, None, dtype, False)
+        block_indices, _ = select_blocks(q_proxy, k_proxy, scale, kb, dtype=dtype, doc_start=doc_start)
+    r = _run(q_proxy, k_proxy, q, k, v, scale, block_indices, None, None, dtype, False, doc_start=doc_start)
     r["block_indices"] = block_indices
     return r
 
 
 def sparse_forward_backward(q_proxy, k_proxy, q, k, v, top_k, scale, d_out,
                             grad_kl: Optional[float] = 1.0, block_indices=None,
-                            dtype=torch.float32):
+                            dtype=torch.float32, doc_start=None):
     """Forward plus closed-form gradients of ``sum(out*d_out) + grad_kl*kl``."""
     kb = int(top_k) // BLOCK
     if block_indices is None:
-        block_indices, _ = select_blocks(q_proxy, k_proxy, scale, kb, dtype=dtype)
-    r = _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype, True)
+        block_indices, _ = select_blocks(q_proxy, k_proxy, scale, kb, dtype=dtype, doc_start=doc_start)
+    r = _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype, True, doc_start=doc_start)
     r["block_indices"] = block_indices
     return r
 
@@ -301,7 +331,7 @@ def warmup_forward_backward(q_proxy, k_proxy, q, k, v, scale, d_out,
 # reference's own tests run.
 # ----------------------------------------------------------------------------
 
-def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None):
+def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None, doc_start=None):
     """Line-by-line restatement of testing_model.py:61-169 with stable top-k (or a given
     selection).  Differentiable; returns ``(attn_out [B,S,Hq*D], kl_loss)``."""
     b, hp, s, d = q_proxy.shape
@@ -314,6 +344,9 @@ def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None):
     kp = k_proxy.repeat_interleave(pg, dim=1)
     proxy_scores = torch.matmul(q_proxy, kp.transpose(-2, -1)) * scale
     future = torch.triu(torch.ones(s, s, device=dev, dtype=torch.bool), diagonal=1)
+    if doc_start is not None:   # document masking (extension): keys before the row's document are hidden as well
+        other = torch.arange(s, device=dev).view(1, 1, 1, s) < doc_start.to(device=dev, dtype=torch.int64).view(b, 1, s, 1)
+        future = future.view(1, 1, s, s) | other
     proxy_scores = proxy_scores.masked_fill(future, float("-inf"))
     block_scores = proxy_scores.view(b, hp, s, nb, BLOCK).amax(dim=-1)
     if block_indices is None:
@@ -324,7 +357,7 @@ def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None):
     block_mask.scatter_(3, idx, True)
     block_mask = block_mask[..., :nb]
     token_mask = block_mask.unsqueeze(-1).expand(b, hp, s, nb, BLOCK).reshape(b, hp, s, s)
-    vis_p = token_mask.tril()
+    vis_p = token_mask & ~future
     vis = vis_p.repeat_interleave(mpp, dim=1)
 
     kk = k.repeat_interleave(g, dim=1)

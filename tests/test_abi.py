@@ -14,7 +14,7 @@ def test_library_builds_and_exports_declared_symbols():
     assert "fmsa_select_topk" in names and "fmsa_reverse_index" in names
     for name in names:
         assert hasattr(lib, name), name
-    assert lib.fmsa_abi_version() == 6          # 6: gradients written through (B,H,S,128) views (strided dq / dq_proxy, fmsa_cast_scaled_rows)
+    assert lib.fmsa_abi_version() == 7          # 7: document masking (fmsa_problem.doc_start, doc_start of fmsa_select_scores)
 
 
 def test_argument_errors_do_not_launch():

@@ -162,3 +162,39 @@ def test_key_block_reference_matches_the_full_restatement():
         assert (r["dk"] - full["dk"][b, kvh, sl]).abs().max().item() <= 1e-5
         for kph, t in r["dk_proxy"].items():
             assert (t - full["dk_proxy"][b, kph, sl]).abs().max().item() <= 1e-9
+
+
+def test_document_masking_of_the_oracle():
+    """Document masking (an extension: the reference has none) is pinned by its definition: with every block selected a
+    packed sequence must give, document by document, plain dense causal attention; the closed-form gradients must equal
+    autograd through the eager restatement; no row may select a block that lies entirely in an earlier document; and
+    without documents nothing changes."""
+    import torch
+    from oracle import msa_oracle as O
+    b, s, hq, hkv, hp, hpkv = 2, 512, 4, 2, 2, 1
+    qp, kp, q, k, v, do = O.make_inputs(b, s, hq, hkv, hp, hpkv, seed=3)
+    cu = [0, 100, 101, 333, 512]
+    ds = O.doc_start_from_cu_seqlens(cu, s, b)
+    assert ds[0, [0, 99, 100, 101, 332, 333, 511]].tolist() == [0, 0, 100, 101, 101, 333, 333]
+    r0 = O.sparse_forward_backward(qp, kp, q, k, v, 256, 0.088, do, 1.0)
+    r1 = O.sparse_forward_backward(qp, kp, q, k, v, 256, 0.088, do, 1.0, doc_start=torch.zeros(b, s, dtype=torch.int32))
+    assert all(torch.equal(r0[n], r1[n]) for n in ("out", "dq", "dk", "dv", "dq_proxy", "dk_proxy"))
+    r = O.sparse_forward_backward(qp, kp, q, k, v, 256, 0.088, do, 0.7, doc_start=ds, dtype=torch.float64)
+    idx = r["block_indices"]
+    out, kl, grads = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, 256, 0.088, block_indices=idx, doc_start=ds),
+                                              [t.double() for t in (qp, kp, q, k, v)], do.double(), 0.7)
+    assert (out - r["out"]).abs().max().item() < 1e-12 and abs(kl.item() - r["kl"].item()) < 1e-12
+    for n, g in zip(["dq_proxy", "dk_proxy", "dq", "dk", "dv"], grads):
+        assert (g - r[n]).abs().max().item() < 1e-12, n
+    nb = s // 128
+    assert not bool(((idx < (ds // 128).view(b, 1, s, 1)) & (idx < nb)).any())
+    dense = O.sparse_forward(qp, kp, q, k, v, s, 0.088, doc_start=ds, dtype=torch.float64)
+    parts = []
+    for a, e in zip(cu[:-1], cu[1:]):
+        qq = q[:, :, a:e].double()
+        kk = k[:, :, a:e].double().repeat_interleave(hq // hkv, 1)
+        vv = v[:, :, a:e].double().repeat_interleave(hq // hkv, 1)
+        att = (qq @ kk.transpose(-1, -2)) * 0.088
+        att = att.masked_fill(torch.triu(torch.ones(e - a, e - a, dtype=torch.bool), 1), float("-inf"))
+        parts.append((torch.softmax(att, -1) @ vv).transpose(1, 2).reshape(b, e - a, -1))
+    assert (torch.cat(parts, 1) - dense["out"]).abs().max().item() < 1e-12
