@@ -146,19 +146,20 @@ class _SparseAttentionFunction(torch.autograd.Function):
 
 class _WarmupSparseAttentionFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale):
+    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale, doc_start=None):
         _ = int(top_k)                         # accepted and ignored, as in the reference
         _validate_inputs(q_proxy, k_proxy, q, k, v, 0, False)
         if q.device.type != "cuda":
             raise RuntimeError("warmup MSA forward requires CUDA tensors")
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), None, dense=True,
-                                                         status=status)
+                                                         status=status, doc_start=doc_start)
         _maybe_check(status, "flash_msa_warmup_func forward")
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
         ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy)
         ctx.set_materialize_grads(False)
         ctx.scale = float(scale)
+        ctx.doc_start = doc_start
         return out, kl_loss
 
     @staticmethod
@@ -169,10 +170,11 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         klv = _kl_buffer(grad_kl, q.device)
         dqp, dkp, dq, dk, dv = ops.attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse_main, lse_proxy,
-                                                      ctx.scale, None, grad_kl, dense=True, status=status, kl_value=klv)
+                                                      ctx.scale, None, grad_kl, dense=True, status=status, kl_value=klv,
+                                                      doc_start=ctx.doc_start)
         _publish_kl(klv)
         _maybe_check(status, "flash_msa_warmup_func backward")
-        return dqp, dkp, dq, dk, dv, None, None
+        return dqp, dkp, dq, dk, dv, None, None, None
 
 
 def sparse_attention(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
@@ -196,4 +198,15 @@ def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, s
 
 def sparse_attention_warmup(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
     """Dense causal warmup attention with full-sequence proxy KL gradients."""
-    return _WarmupSparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale))
+    return _WarmupSparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), None)
+
+
+def sparse_attention_warmup_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float):
+    """`sparse_attention_warmup` on packed sequences (see `sparse_attention_varlen`): dense causal attention and the
+    full-sequence proxy KL inside every document.  The schedule still visits every causal block pair of the packed
+    sequence; pairs that straddle documents are masked."""
+    if q.ndim != 4:
+        raise ValueError("all attention tensors must have shape (B, H, S, D)")
+    _require_cuda(q)
+    doc_start = ops.doc_start_from_cu_seqlens(cu_seqlens, q.shape[0], q.shape[2], q.device)
+    return _WarmupSparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), doc_start)

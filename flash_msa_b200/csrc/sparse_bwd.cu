@@ -1129,7 +1129,6 @@ extern "C" int fmsa_sparse_bwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
     FMSA_REQUIRE(dense || (pb->top_k_blocks >= 1 && pb->top_k_blocks <= pb->S / kBlock));
     FMSA_REQUIRE(pb->scale > 0.f);
-    if (dense && pb->doc_start) return FMSA_ERR_UNSUPPORTED;   // document masking: sparse paths only
     FMSA_REQUIRE(static_cast<int64_t>(pb->B) * pb->Hp <= 65535 && pb->S / kBlock <= 32767);   // 16-bit fields of the sub-unit record
     if (part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
     FMSA_REQUIRE(tma_compatible(k->ptr, k->stride_b, k->stride_h, k->stride_s));

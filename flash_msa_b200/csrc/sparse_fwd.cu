@@ -501,7 +501,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                         const int at = chunk * kBlock + row;
                         low = 0;
                         if (at < ud.n) {
-                            const int q = P.col_q[ud.e0 + at];
+                            const int q = P.dense ? (ud.j * kBlock + at) : P.col_q[ud.e0 + at];
                             if (static_cast<unsigned>(q) < static_cast<unsigned>(P.S)) {
                                 const int lo = P.doc_start[static_cast<int64_t>(ud.b) * P.S + q];
                                 const int lb = lo >> 7;
@@ -550,6 +550,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
                             piece_max(bb, c + 32);
                         }
                         m = mloc * P.scale_log2e;   // raw logits: scale > 0, so the maximum commutes with it
+                        // (dense schedule with documents: a row may see nothing of this block; a finite stand-in for
+                        // -inf keeps the merge of the partial statistics free of inf - inf)
+                        if (VARLEN) m = fmaxf(m, -1.0e30f);
                         const float2 nm2 = make_float2(-m, -m);
                         float2 l2 = make_float2(0.f, 0.f);
                         auto piece_exp = [&](const uint32_t (&v)[32], int c) __attribute__((always_inline)) {
@@ -861,7 +864,6 @@ extern "C" int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, con
     FMSA_REQUIRE(!with_proxy || (q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr));
     FMSA_REQUIRE(g_begin >= 0 && g_count > 0 && g_begin + g_count <= pb->B * pb->Hkv);
     FMSA_REQUIRE(dense || (pb->top_k_blocks >= 1 && pb->top_k_blocks <= pb->S / kBlock));
-    if (dense && pb->doc_start) return FMSA_ERR_UNSUPPORTED;   // document masking: sparse paths only
     FMSA_REQUIRE(pb->scale > 0.f);
     if (part_slots < fmsa_fwd_partial_slots(pb, g_count, dense)) return FMSA_ERR_WORKSPACE;
     FMSA_REQUIRE(tma_compatible(k->ptr, k->stride_b, k->stride_h, k->stride_s));

@@ -358,8 +358,6 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
     mpp = hq // hp
     dev = q.device
     doc_start = _check_doc_start(doc_start, q.shape[0], q.shape[2], q.device)
-    if dense and doc_start is not None:
-        raise NotImplementedError("document masking is implemented for the sparse path only")
     pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale, doc_start)
     out = torch.empty(b, s, hq * d, dtype=q.dtype, device=dev)
     lse = torch.empty(b, hq, s, dtype=torch.float32, device=dev)
@@ -410,8 +408,6 @@ def attention_backward(q, k, v, q_proxy, k_proxy, out, grad_out, lse, lse_proxy,
     dev = q.device
     st = _stream(dev)
     doc_start = _check_doc_start(doc_start, q.shape[0], q.shape[2], q.device)
-    if dense and doc_start is not None:
-        raise NotImplementedError("document masking is implemented for the sparse path only")
     pb = _problem(q, k, qp, kp, 1 if dense else rix.top_k_blocks, scale, doc_start)
     with_kl = grad_kl is not None
     if status is None:

@@ -53,8 +53,7 @@ typedef struct {
     /* Document masking of packed sequences (no counterpart in the reference, whose README lists variable-length
      * batches as missing): NULL, or int32 [B,S] on the device holding, for every token, the position of the first
      * token of its document (cu_seqlens[i] for the tokens of document i).  A query then sees only the keys of its own
-     * document: block scores, selection, forward and backward all honour it.  Sparse paths only: the dense warmup
-     * entry points refuse it with FMSA_ERR_UNSUPPORTED. */
+     * document: block scores, selection, forward and backward (sparse and dense warmup) all honour it. */
     const int32_t* doc_start;
 } fmsa_problem;
 

@@ -315,14 +315,14 @@ def sparse_forward_backward(q_proxy, k_proxy, q, k, v, top_k, scale, d_out,
     return r
 
 
-def warmup_forward(q_proxy, k_proxy, q, k, v, scale, dtype=torch.float32):
+def warmup_forward(q_proxy, k_proxy, q, k, v, scale, dtype=torch.float32, doc_start=None):
     """Dense causal main attention + full-sequence proxy statistics."""
-    return _run(q_proxy, k_proxy, q, k, v, scale, None, None, None, dtype, False)
+    return _run(q_proxy, k_proxy, q, k, v, scale, None, None, None, dtype, False, doc_start=doc_start)
 
 
 def warmup_forward_backward(q_proxy, k_proxy, q, k, v, scale, d_out,
-                            grad_kl: Optional[float] = 1.0, dtype=torch.float32):
-    return _run(q_proxy, k_proxy, q, k, v, scale, None, d_out, grad_kl, dtype, True)
+                            grad_kl: Optional[float] = 1.0, dtype=torch.float32, doc_start=None):
+    return _run(q_proxy, k_proxy, q, k, v, scale, None, d_out, grad_kl, dtype, True, doc_start=doc_start)
 
 
 # ----------------------------------------------------------------------------
@@ -375,13 +375,16 @@ def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None, do
     return out, kl
 
 
-def eager_warmup(q_proxy, k_proxy, q, k, v, scale):
+def eager_warmup(q_proxy, k_proxy, q, k, v, scale, doc_start=None):
     """Restatement of testing_model_warmup.py:63-104.  Differentiable."""
     b, hp, s, d = q_proxy.shape
     hq, hkv, hpkv = q.shape[1], k.shape[1], k_proxy.shape[1]
     mpp, g, pg = hq // hp, hq // hkv, hp // hpkv
     dev = q.device
     future = torch.triu(torch.ones(s, s, device=dev, dtype=torch.bool), diagonal=1)
+    if doc_start is not None:   # document masking (extension): keys before the row's document are hidden as well
+        other = torch.arange(s, device=dev).view(1, 1, 1, s) < doc_start.to(device=dev, dtype=torch.int64).view(b, 1, s, 1)
+        future = future.view(1, 1, s, s) | other
     kp = k_proxy.repeat_interleave(pg, dim=1)
     proxy_scores = (torch.matmul(q_proxy, kp.transpose(-2, -1)) * scale).masked_fill(future, float("-inf"))
     kk = k.repeat_interleave(g, dim=1)

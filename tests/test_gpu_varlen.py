@@ -103,3 +103,25 @@ def test_varlen_argument_errors(fm):
         fm.flash_msa_varlen_func(qp, kp, q, k, v, [0, 100], cfg["kb"] * 128, SCALE)         # does not end at S
     with pytest.raises(ValueError):
         fm.flash_msa_varlen_func(qp, kp, q, k, v, [0, 300, 200, 512], cfg["kb"] * 128, SCALE)   # not rising
+
+
+@pytest.mark.parametrize("name", ["ragged", "per_batch"])
+def test_varlen_warmup_forward_backward(fm, name):
+    """Dense warmup on packed sequences: block pairs that straddle documents are masked, rows that see nothing of a
+    block contribute nothing."""
+    from flash_msa_b200 import ops
+    cfg, cu = CASES[name]
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    leaves = [t.detach().clone().requires_grad_(True) for t in (qp, kp, q, k, v)]
+    out, kl = fm.flash_msa_warmup_varlen_func(*leaves, cu, 0, SCALE)
+    ((out.float() * do.reshape(out.shape).float()).sum() + 0.6 * kl).backward()
+    ds = ops.doc_start_from_cu_seqlens(cu, cfg["b"], cfg["s"], qp.device).cpu()
+    cpu = [t.float().cpu() for t in (qp, kp, q, k, v)]
+    r32 = O.warmup_forward_backward(*cpu, SCALE, do.float().cpu(), 0.6, doc_start=ds)
+    o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, SCALE, doc_start=ds),
+                                           [t.cpu() for t in (qp, kp, q, k, v)], do.cpu(), 0.6)
+    assert torch.isfinite(out.float()).all()
+    yardstick_check("out", out.cpu(), r32["out"], o16, 1e-3)
+    for n, leaf, y in zip(NAMES, leaves, g16):
+        yardstick_check(n, leaf.grad.cpu(), r32[n], y, 1e-3 * max(1.0, r32[n].abs().max().item()) if n in ("dq", "dk", "dv")
+                        else 1e-3 * r32[n].abs().max().item())
