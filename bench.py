@@ -352,7 +352,7 @@ def ref_kernels(args):
             res["ref_reverse_index_ms"] = timed(lambda: build_reverse_index_cuda(idx, query_chunk=qc))
         attempt(f"build_reverse_index_cuda [{tag}]", ref_rix)
 
-        # backward: both kernels get the same forward results (ours), the oracle is the judge
+        # backward: both kernels get the same forward results (ours) and are measured against the oracle
         rix = ops.build_reverse_index(idx)
         o, lse, lse_p = ops.attention_forward(q, k, v, qp, kp, SCALE, rix)
         gk = torch.ones((), device=dev)

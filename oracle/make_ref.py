@@ -1,6 +1,6 @@
 """Makes the reference project's own eager model importable next to the oracle, for timing and checking only.
 
-    python oracle/make_ref.py [REFERENCE_ROOT]        (default: $REFERENCE_ROOT or /root/reference)
+    python oracle/make_ref.py [REFERENCE_ROOT]        (default: $REFERENCE_ROOT, else the build machine's reference checkout)
 
 Copies the reference's ``flash_msa`` Python package (the eager models live in ``flash_msa/tests/testing_model.py``
 and ``testing_model_warmup.py``; they import the package itself) into ``oracle/_ref/``, which is excluded from

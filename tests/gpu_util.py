@@ -49,7 +49,7 @@ _REPORT = {}
 
 def report(section, values):
     """Collects parity figures (error / yardstick ratios, near-tie and flip counts) of the GPU tests into one
-    JSON file: $FMSA_PARITY_REPORT, or gpurun_out/parity_report.json under the repository root."""
+    JSON file: $FMSA_PARITY_REPORT, or parity_report.json in the scratch output folder under the repository root."""
     import json
     import os
     _REPORT[section] = values

@@ -1,7 +1,7 @@
 """The tolerance the task states for out/dQ/dK/dV/dQp/dKp is "within twice the reference kernel's max-abs error
 against an fp32 eager MSA".  Where the reference's own fused backward kernel can be built and run on this machine
 (its copy under oracle/_ref, see oracle/make_ref.py) that is checked literally: same inputs, same selection, same
-forward statistics for both kernels, the fp32 oracle as the judge.  Elsewhere the test is skipped and the bf16-eager
+forward statistics for both kernels, both measured against the fp32 oracle.  Elsewhere the test is skipped and the bf16-eager
 yardstick of the other tests stands in."""
 import pytest
 import torch
