@@ -198,3 +198,15 @@ def test_document_masking_of_the_oracle():
         att = att.masked_fill(torch.triu(torch.ones(e - a, e - a, dtype=torch.bool), 1), float("-inf"))
         parts.append((torch.softmax(att, -1) @ vv).transpose(1, 2).reshape(b, e - a, -1))
     assert (torch.cat(parts, 1) - dense["out"]).abs().max().item() < 1e-12
+
+
+def test_doc_start_helper_matches_the_oracle_and_rejects_bad_packings():
+    import pytest
+    import torch
+    from flash_msa_b200 import ops
+    from oracle import msa_oracle as O
+    for cu, b, s in (([0, 100, 101, 333, 512], 2, 512), ([[0, 130, 1024, 1024], [0, 5, 640, 1024]], 2, 1024), ([0, 256], 1, 256)):
+        assert torch.equal(ops.doc_start_from_cu_seqlens(cu, b, s, "cpu"), O.doc_start_from_cu_seqlens(cu, s, b))
+    for bad in ([1, 512], [0, 100], [0, 300, 200, 512], [[0, 512]] * 3):
+        with pytest.raises(ValueError):
+            ops.doc_start_from_cu_seqlens(bad, 2, 512, "cpu")
