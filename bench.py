@@ -443,7 +443,7 @@ class GpuContext:
         return float(t.item())
 
 
-def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks):
+def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks, docs=0):
     """W warm-up steps, then K timed fwd+bwd steps of one workload on this rank's share of it (CUDA events on the
     launching stream, barrier + synchronize on both sides, max over ranks)."""
     import flash_msa_b200
@@ -454,6 +454,11 @@ def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks):
     dev = ctx.dev
     fn = flash_msa_b200.flash_msa_warmup_func if cfg["dense"] else flash_msa_b200.flash_msa_func
     top_k = cfg["kb"] * 128
+    cu = None
+    if docs > 0:
+        # packed sequences: `docs` documents of (nearly) equal length whose boundaries do not fall on block boundaries
+        fn = flash_msa_b200.flash_msa_warmup_varlen_func if cfg["dense"] else flash_msa_b200.flash_msa_varlen_func
+        cu = [0] + [min(local["s"], i * local["s"] // docs + 37) for i in range(1, docs)] + [local["s"]]
     host = make_inputs(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], seed=ctx.rank,
                        dtype=torch.bfloat16)
     host = [t.pin_memory() for t in host]
@@ -462,7 +467,7 @@ def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks):
 
     def step():
         leaves = [t.detach().requires_grad_(True) for t in (qp, kp, q, k, v)]
-        out, kl = fn(*leaves, top_k, SCALE)
+        out, kl = fn(*leaves, top_k, SCALE) if cu is None else fn(*leaves, cu, top_k, SCALE)
         torch.autograd.backward([out, kl], [do, ones])
 
     for _ in range(warmup):
@@ -560,6 +565,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--varlen-docs", type=int, default=0,
+                    help="also time the workload as a packed sequence of this many documents (document masking)")
     ap.add_argument("--no-strong-c5", action="store_true", help="skip the config-5 strong-scaling measurement of the default run")
     ap.add_argument("--micro-select", action="store_true", help="time the top-k and reverse-index kernels at config-5 size")
     ap.add_argument("--ref-kernels", action="store_true", help="try the reference's own GPU kernels beside ours (needs oracle/_ref)")
@@ -584,6 +591,11 @@ def main():
     strong = None
     if args.workload == "c2" and not args.no_strong_c5 and WORKLOADS["c5"]["hkv"] % ctx.world == 0:
         strong = time_workload(ctx, "c5", max(2, min(args.steps, 5)), 2, with_e2e=False, sample_clocks=False)
+
+    packed = None
+    if args.varlen_docs > 0:
+        packed = time_workload(ctx, args.workload, max(2, min(args.steps, 5)), 3, with_e2e=False, sample_clocks=False,
+                               docs=args.varlen_docs)
 
     if ctx.rank != 0:
         if ctx.dist is not None:
@@ -630,6 +642,10 @@ def main():
                              "ms_per_step": strong["ms_per_step"], "tokens_per_s": c5["b"] * c5["s"] / t5,
                              "tflops": flops(c5) / t5 / 1e12, "per_rank": strong["local"], "kernels": strong["kernels"],
                              "peak_mem_gib": strong["peak_mem_gib"]}
+    if packed is not None:
+        line["varlen"] = {"docs": args.varlen_docs, "steps": packed["steps"], "ms_per_step": packed["ms_per_step"],
+                          "kernels": packed["kernels"],
+                          "note": "same tensors as a packed sequence; fewer visible (query, key) pairs, so no TFLOP/s figure"}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = {k_: v_ for k_, v_ in run_cpu_baseline(cfg, 1, 1).items() if k_ not in ("s_per_slice", "slices")}
     print(json.dumps(line))
