@@ -37,16 +37,18 @@ __global__ void __launch_bounds__(256) topk_rows_kernel(const float* __restrict_
     }
     const int kt = (Kb - 1) >> 5, lt = (Kb - 1) & 31;   // position of the Kb-th entry
     float tv = -INFINITY;
-    int ti = NB;
 
-    // sorted insertion of (cv, ci) with shift; the last entry of the list falls out
-    auto insert = [&](float cv, int ci) {
+    // Sorted insertion of (cv, ci) with shift; the last entry of the list falls out.  Candidates arrive in ascending
+    // block index, so an entry of equal score that is already in the list has the lower index and stays ahead: the
+    // position is decided by the scores alone (a strict comparison), except for the forced own block (`by_index`).
+    auto insert = [&](float cv, int ci, bool by_index) {
         float inv = cv;
         int ini = ci;
         bool placed = false;
 #pragma unroll
         for (int k = 0; k < KPL; ++k) {
-            const unsigned bm = placed ? 0xffffffffu : __ballot_sync(0xffffffffu, beats(cv, ci, lv[k], li[k]));
+            const unsigned bm = placed ? 0xffffffffu
+                                       : __ballot_sync(0xffffffffu, by_index ? beats(cv, ci, lv[k], li[k]) : (cv > lv[k]));
             if (bm != 0) {
                 const int first = __ffs(bm) - 1;
                 const float outv = __shfl_sync(0xffffffffu, lv[k], 31);
@@ -65,8 +67,11 @@ __global__ void __launch_bounds__(256) topk_rows_kernel(const float* __restrict_
                 placed = true;
             }
         }
+    };
+    // the current Kb-th entry: what a candidate has to beat (refreshed once per batch of 32 candidates, not after every
+    // insertion: a stale, lower bar only lets a candidate through that the insertion then places beyond the Kb-th slot)
+    auto refresh_bar = [&]() {
         tv = __shfl_sync(0xffffffffu, lv[kt], lt);
-        ti = __shfl_sync(0xffffffffu, li[kt], lt);
     };
 
     int base = 0;
@@ -100,22 +105,22 @@ __global__ void __launch_bounds__(256) topk_rows_kernel(const float* __restrict_
         li[0] = id;
         base = 32;
     }
-    insert(INFINITY, local);   // the row's own block is forced first
+    insert(INFINITY, local, true);   // the row's own block is forced first
+    refresh_bar();
 
     for (; base < nvalid; base += 32) {
         const int j = base + lane;
         const bool have = (j < nvalid) && (j != local);
         const float s = have ? srow[j] : -INFINITY;
         // a score of -inf (or NaN) never enters the list: such a slot keeps the sentinel
-        unsigned mask = __ballot_sync(0xffffffffu, have && s > -INFINITY && beats(s, j, tv, ti));
+        // (a candidate that only ties the bar loses to it: the entry in the list has the lower block index)
+        unsigned mask = __ballot_sync(0xffffffffu, have && s > -INFINITY && s > tv);
         while (mask) {
             const int src = __ffs(mask) - 1;
             mask &= mask - 1;
-            const float cv = __shfl_sync(0xffffffffu, s, src);
-            const int ci = base + src;
-            if (!beats(cv, ci, tv, ti)) continue;
-            insert(cv, ci);
+            insert(__shfl_sync(0xffffffffu, s, src), base + src, false);
         }
+        refresh_bar();
     }
     int32_t* orow = out + row * Kb;
 #pragma unroll
