@@ -70,6 +70,8 @@ def _declare(lib):
     PB = ctypes.POINTER(FmsaProblem)
     lib.fmsa_select_scores.restype = c_int
     lib.fmsa_select_scores.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, P, P, P]
+    lib.fmsa_select_fused.restype = c_int
+    lib.fmsa_select_fused.argtypes = [T, T, P, c_int32, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, P, P, P]
     lib.fmsa_fwd_partial_slots.restype = c_int64
     lib.fmsa_fwd_partial_slots.argtypes = [PB, c_int32, c_int32]
     lib.fmsa_sparse_fwd.restype = c_int

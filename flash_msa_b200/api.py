@@ -108,9 +108,13 @@ class _SparseAttentionFunction(torch.autograd.Function):
         num_blocks, top_k_blocks = _validate_inputs(q_proxy, k_proxy, q, k, v, int(top_k), True)
         _require_cuda(q)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
-        scores = ops.proxy_block_scores(q_proxy, k_proxy, float(scale), status=status, doc_start=doc_start)
-        block_indices = ops.select_topk(scores, top_k_blocks)
-        del scores
+        if top_k_blocks <= ops.FUSED_SELECT_MAX_BLOCKS:
+            block_indices = ops.select_blocks_fused(q_proxy, k_proxy, float(scale), top_k_blocks, status=status,
+                                                    doc_start=doc_start)
+        else:
+            scores = ops.proxy_block_scores(q_proxy, k_proxy, float(scale), status=status, doc_start=doc_start)
+            block_indices = ops.select_topk(scores, top_k_blocks)
+            del scores
         rix = ops.build_reverse_index(block_indices)
         out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), rix, status=status,
                                                          doc_start=doc_start)

@@ -11,6 +11,12 @@
 // tcgen05.mma into one of two TMEM accumulators, warps 2-5 read an accumulator back (one row per
 // thread), take the masked row maximum and stage it in shared memory so that global stores are
 // row-contiguous.
+//
+// Fused selection (LK > 0, top_k_blocks <= LK): the thread that owns a row sees the row's block scores one by one, in
+// ascending block index, so it can keep the row's best LK blocks in a sorted register list and write block_indices
+// itself; block_scores is then never written and the separate top-k kernel is not needed.  The order is the one of
+// the top-k kernel (score descending, equal scores by ascending block index, own block first, sentinel NB): a new
+// score goes behind every entry that is at least as large, and the own block is put in front at the end.
 #include "host_common.h"
 #include "sm100.cuh"
 #include "tma_host.h"
@@ -26,11 +32,12 @@ struct ScoreSmem {
     float stage[128][kScoreStageCols + 1];
 };
 
-template <bool FP16>
+template <bool FP16, int LK>
 __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                             const __grid_constant__ CUtensorMap tmap_k,
                                                             float* __restrict__ block_scores, int Hp, int pg, int S,
                                                             int NB, float scale, const int32_t* __restrict__ doc_start,
+                                                            int32_t* __restrict__ block_indices, int Kb,
                                                             int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -99,6 +106,28 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
         // (lo = 0 without documents).
         const int lo = doc_start ? doc_start[static_cast<int64_t>(b) * S + qt * kBlock + r] : 0;
         const int lo_blk = lo >> 7, lo_col = lo & 127;
+        constexpr int kList = LK > 0 ? LK : 1;
+        float lv[kList];   // fused selection: the row's best blocks so far, best first
+        int li[kList];
+#pragma unroll
+        for (int i = 0; i < kList; ++i) {
+            lv[i] = -INFINITY;
+            li[i] = NB;
+        }
+        // (value, block) goes behind every entry that is at least as large; the last entry falls out
+        auto list_insert = [&](float val, int blk) {
+#pragma unroll
+            for (int i = kList - 1; i > 0; --i) {
+                const bool shift = lv[i - 1] < val;           // entry i-1 moves down to i
+                const bool here = !shift && lv[i] < val;      // the new entry lands at i
+                lv[i] = shift ? lv[i - 1] : (here ? val : lv[i]);
+                li[i] = shift ? li[i - 1] : (here ? blk : li[i]);
+            }
+            if (lv[0] < val) {
+                lv[0] = val;
+                li[0] = blk;
+            }
+        };
         for (int j = 0; j <= qt; ++j) {
             const int st = j & 1;
             ok = mbar_wait(smem_u32(&sm->s_full[st]), (j >> 1) & 1);
@@ -136,6 +165,11 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
             if (j < lo_blk) m = -INFINITY;   // the whole block lies before the row's document
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&sm->s_empty[st]));
+            if (LK > 0) {
+                // (a score of -inf or NaN never enters; the own block is forced in after the loop)
+                if (j < qt && __any_sync(0xffffffffu, m > lv[kList - 1])) list_insert(m, j);
+                continue;
+            }
             sm->stage[r][j % kScoreStageCols] = m;
             if ((j % kScoreStageCols) == kScoreStageCols - 1 || j == qt) {
                 __syncwarp();
@@ -152,6 +186,14 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
                 __syncwarp();
             }
         }
+        if (LK > 0 && ok) {
+            // the row's own block always comes first (flash_msa/tests/testing_model.py:90-94)
+            list_insert(INFINITY, qt);
+            int32_t* orow = block_indices + (static_cast<int64_t>(bp) * S + qt * kBlock + r) * Kb;
+#pragma unroll
+            for (int i = 0; i < kList; ++i)
+                if (i < Kb) orow[i] = li[i];
+        }
     }
     if (!ok) atomicMax(status, kStatusWaitTimeout);
     tc_fence_before_sync();
@@ -162,11 +204,25 @@ __global__ void __launch_bounds__(192) select_scores_kernel(const __grid_constan
 }  // namespace
 }  // namespace fmsa
 
-extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores,
-                                  int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype,
-                                  const int32_t* doc_start, int32_t* status, void* stream) {
-    using namespace fmsa;
-    FMSA_REQUIRE(q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && block_scores && status);
+namespace fmsa {
+namespace {
+
+template <bool FP16, int LK>
+int launch_select(const CUtensorMap& tq, const CUtensorMap& tk, float* block_scores, int32_t* block_indices, int B, int Hp,
+                  int Hpkv, int S, int Kb, float scale, const int32_t* doc_start, int32_t* status, cudaStream_t st) {
+    const int NB = S / kBlock;
+    const size_t smem = 3 * kTileBytes + 1024 + sizeof(ScoreSmem);
+    if (!ensure_smem_attr(reinterpret_cast<const void*>(select_scores_kernel<FP16, LK>), smem)) return FMSA_ERR_CUDA;
+    const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(B * Hp));
+    select_scores_kernel<FP16, LK><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, doc_start,
+                                                           block_indices, Kb, status);
+    return check_launch();
+}
+
+int select_common(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores, int32_t* block_indices,
+                  int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, int32_t Kb, float scale, int32_t dtype,
+                  const int32_t* doc_start, int32_t* status, void* stream) {
+    FMSA_REQUIRE(q_proxy && k_proxy && q_proxy->ptr && k_proxy->ptr && status);
     FMSA_REQUIRE(B > 0 && Hp > 0 && Hpkv > 0 && Hp % Hpkv == 0 && S > 0 && S % kBlock == 0);
     FMSA_REQUIRE(dtype == FMSA_DTYPE_BF16 || dtype == FMSA_DTYPE_FP16);
     FMSA_REQUIRE(scale > 0.f);   // the kernel scales the block maximum, not every logit
@@ -177,15 +233,35 @@ extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor*
     if (!make_tmap_bhsd(&tq, q_proxy->ptr, B, Hp, S, q_proxy->stride_b, q_proxy->stride_h, q_proxy->stride_s, 128) ||
         !make_tmap_bhsd(&tk, k_proxy->ptr, B, Hpkv, S, k_proxy->stride_b, k_proxy->stride_h, k_proxy->stride_s, 128))
         return FMSA_ERR_CUDA;
-    const int NB = S / kBlock;
-    const size_t smem = 3 * kTileBytes + 1024 + sizeof(ScoreSmem);
-    const bool fp16 = dtype == FMSA_DTYPE_FP16;
-    const void* kfn = fp16 ? reinterpret_cast<const void*>(select_scores_kernel<true>)
-                           : reinterpret_cast<const void*>(select_scores_kernel<false>);
-    if (!ensure_smem_attr(kfn, smem)) return FMSA_ERR_CUDA;
-    const dim3 grid(static_cast<unsigned>(NB), static_cast<unsigned>(B * Hp));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (fp16) select_scores_kernel<true><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, doc_start, status);
-    else select_scores_kernel<false><<<grid, 192, smem, st>>>(tq, tk, block_scores, Hp, Hp / Hpkv, S, NB, scale, doc_start, status);
-    return check_launch();
+    const bool fp16 = dtype == FMSA_DTYPE_FP16;
+#define FMSA_SELECT(LKV)                                                                                              \
+    (fp16 ? launch_select<true, LKV>(tq, tk, block_scores, block_indices, B, Hp, Hpkv, S, Kb, scale, doc_start, status, st) \
+          : launch_select<false, LKV>(tq, tk, block_scores, block_indices, B, Hp, Hpkv, S, Kb, scale, doc_start, status, st))
+    if (Kb == 0) return FMSA_SELECT(0);
+    if (Kb <= 8) return FMSA_SELECT(8);
+    if (Kb <= 16) return FMSA_SELECT(16);
+    return FMSA_SELECT(32);
+#undef FMSA_SELECT
+}
+
+}  // namespace
+}  // namespace fmsa
+
+extern "C" int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float* block_scores,
+                                  int32_t B, int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype,
+                                  const int32_t* doc_start, int32_t* status, void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(block_scores);
+    return select_common(q_proxy, k_proxy, block_scores, nullptr, B, Hp, Hpkv, S, 0, scale, dtype, doc_start, status, stream);
+}
+
+extern "C" int fmsa_select_fused(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, int32_t* block_indices, int32_t B,
+                                 int32_t Hp, int32_t Hpkv, int32_t S, int32_t top_k_blocks, float scale, int32_t dtype,
+                                 const int32_t* doc_start, int32_t* status, void* stream) {
+    using namespace fmsa;
+    FMSA_REQUIRE(block_indices && S > 0 && top_k_blocks >= 1 && top_k_blocks <= S / kBlock);
+    if (top_k_blocks > FMSA_FUSED_SELECT_MAX_BLOCKS) return FMSA_ERR_UNSUPPORTED;
+    return select_common(q_proxy, k_proxy, nullptr, block_indices, B, Hp, Hpkv, S, top_k_blocks, scale, dtype, doc_start, status,
+                         stream);
 }

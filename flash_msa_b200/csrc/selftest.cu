@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(128) pipeline_selftest_kernel(const __grid_con
 }  // namespace
 }  // namespace fmsa
 
-extern "C" int fmsa_abi_version(void) { return 7; }
+extern "C" int fmsa_abi_version(void) { return 8; }
 
 extern "C" int fmsa_umma_selftest(const void* a, const void* b, float* d, int a_mn, int b_mn, int use_tma, int* status,
                                   void* stream) {

@@ -339,6 +339,37 @@ def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: floa
     return scores
 
 
+FUSED_SELECT_MAX_BLOCKS = 32
+
+
+def select_blocks_fused(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, top_k_blocks: int, status=None,
+                        doc_start=None) -> torch.Tensor:
+    """block_indices [B,Hp,S,Kb] int32 from one kernel that scores the key blocks and keeps every row's best ones in
+    registers (Kb <= FUSED_SELECT_MAX_BLOCKS); the fp32 block scores are never written.  Bit for bit the result of
+    `proxy_block_scores` + `select_topk`."""
+    _require_cuda(q_proxy, k_proxy)
+    if q_proxy.dtype != k_proxy.dtype:
+        raise TypeError("q_proxy and k_proxy must have one dtype")
+    kb = int(top_k_blocks)
+    b, hp, s, d = q_proxy.shape
+    if not 1 <= kb <= min(FUSED_SELECT_MAX_BLOCKS, s // BLOCK_SIZE):
+        raise ValueError("top_k_blocks outside the range of the fused selection")
+    code = _dtype_code(q_proxy.dtype)
+    qp, kp = _as_kernel_input(q_proxy.detach()), _as_kernel_input(k_proxy.detach())
+    dev = qp.device
+    doc_start = _check_doc_start(doc_start, b, s, dev)
+    idx = torch.empty(b, hp, s, kb, dtype=torch.int32, device=dev)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    with _Timed("select_scores", dev):
+        _launch("fmsa_select_fused", 1, lib.fmsa_select_fused(_tensor_arg(qp), _tensor_arg(kp), idx.data_ptr(), b, hp,
+                                                            kp.shape[1], s, kb, float(scale), code,
+                                                            doc_start.data_ptr() if doc_start is not None else None,
+                                                            status.data_ptr(), _stream(dev)), dev)
+    return idx
+
+
 def select_blocks(q_proxy, k_proxy, *, scale: float, num_blocks: int, top_k_blocks: int, return_scores=False, doc_start=None):
     """Counterpart of the reference's select_blocks (flash_msa/msa_select_cutedsl.py:481-538)."""
     if q_proxy.ndim != 4 or k_proxy.ndim != 4:

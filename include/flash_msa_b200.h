@@ -135,6 +135,16 @@ int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, f
                        int32_t Hp, int32_t Hpkv, int32_t S, float scale, int32_t dtype, const int32_t* doc_start,
                        int32_t* status, void* stream);
 
+/* Scores and top-k in one kernel, for top_k_blocks <= FMSA_FUSED_SELECT_MAX_BLOCKS: the thread that owns a query row
+ * keeps the row's best blocks in registers while the block scores come out of the tensor core, and writes
+ * block_indices [B,Hp,S,top_k_blocks] (int32) itself; the fp32 block scores are never materialised.  Same result,
+ * bit for bit, as fmsa_select_scores followed by fmsa_select_topk; larger top_k_blocks return FMSA_ERR_UNSUPPORTED.
+ * Replaces the whole reference select kernel (flash_msa/msa_select_cutedsl.py:149-329, 481-538). */
+#define FMSA_FUSED_SELECT_MAX_BLOCKS 32
+int fmsa_select_fused(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, int32_t* block_indices, int32_t B, int32_t Hp,
+                      int32_t Hpkv, int32_t S, int32_t top_k_blocks, float scale, int32_t dtype, const int32_t* doc_start,
+                      int32_t* status, void* stream);
+
 /* Sparse forward, stage 1: per-edge partial attention (key-block stationary).
  * Replaces sparse_flash_varlen_forward (flash_msa/sparse_flash_varlen.py:92-261: local-block
  * FlashAttention call + chunked paged-varlen calls + torch gathers) and, with with_proxy = 1, the

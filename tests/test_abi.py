@@ -14,7 +14,7 @@ def test_library_builds_and_exports_declared_symbols():
     assert "fmsa_select_topk" in names and "fmsa_reverse_index" in names
     for name in names:
         assert hasattr(lib, name), name
-    assert lib.fmsa_abi_version() == 7          # 7: document masking (fmsa_problem.doc_start, doc_start of fmsa_select_scores)
+    assert lib.fmsa_abi_version() == 8          # 8: fmsa_select_fused (block scores and top-k in one kernel)
 
 
 def test_argument_errors_do_not_launch():

@@ -104,3 +104,25 @@ def test_sparse_forward_fp16(ops, name):
     qblk = (torch.arange(cfg["s"], device="cuda") // 128).view(1, 1, -1, 1)
     masked = scores.masked_fill(torch.arange(nb, device="cuda").view(1, 1, 1, nb) > qblk, float("-inf"))
     assert torch.equal(idx.cpu(), O.stable_topk(masked.cpu(), cfg["kb"]))
+
+
+@pytest.mark.parametrize("s,kb,hp,hpkv", [(128, 1, 1, 1), (512, 2, 2, 1), (1024, 4, 2, 2), (2048, 8, 3, 1), (2048, 9, 2, 2), (4096, 16, 2, 1),
+                                          (4096, 17, 1, 1), (8192, 32, 2, 2), (8192, 5, 1, 1)])
+@pytest.mark.parametrize("docs", [False, True])
+def test_fused_selection_equals_scores_plus_topk(s, kb, hp, hpkv, docs):
+    """The fused kernel (block scores and the per-row top-k in one pass, nothing materialised) must give, bit for bit,
+    what the score kernel followed by the top-k kernel gives - also with ties (a proxy head made of repeated rows) and
+    with documents."""
+    from flash_msa_b200 import ops
+    cfg = dict(b=2, s=s, hq=hp, hkv=1, hp=hp, hpkv=hpkv, seed=7 * s + kb)
+    qp, kp, *_ = bf16_inputs(cfg)
+    kp = kp.clone()
+    kp[:, :, 128:256] = kp[:, :, 0:128] if s >= 256 else kp[:, :, 128:256]   # two identical key blocks: exact ties
+    ds = None
+    if docs:
+        cu = sorted({0, s} | {int(x) for x in torch.randint(1, s, (3,), generator=torch.Generator().manual_seed(s + kb))})
+        ds = ops.doc_start_from_cu_seqlens(cu, 2, s, qp.device)
+    want = ops.select_blocks(qp, kp, scale=SCALE, num_blocks=s // 128, top_k_blocks=kb, doc_start=ds)
+    got = ops.select_blocks_fused(qp, kp, SCALE, kb, doc_start=ds)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
