@@ -177,3 +177,30 @@ def test_gradients_in_caller_layout(fm, warmup):
         assert g_view.stride() == x.stride() and g_view.transpose(1, 2).is_contiguous()
         assert g_plain.is_contiguous()
         assert torch.equal(g_view, g_plain)
+
+
+@pytest.mark.parametrize("warmup", [False, True])
+def test_passes_over_groups_give_the_same_result(fm, warmup):
+    """When the per-edge partial rows of a call would exceed `ops.MAX_PARTIAL_BYTES` the forward and the backward run in
+    several passes over (batch, KV head) groups, reusing one partial buffer.  One group per pass must give what one
+    pass over everything gives: out, lse and dQ bit for bit (they are sums in a fixed order), dK / dV / dKp up to the
+    order of their fp32 reductions."""
+    from flash_msa_b200 import ops
+    cfg = dict(b=2, s=1024, hq=12, hkv=3, hp=6, hpkv=3, kb=3, seed=31)
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    fn = fm.flash_msa_warmup_func if warmup else fm.flash_msa_func
+    saved = ops.MAX_PARTIAL_BYTES
+    results = []
+    try:
+        for cap in (saved, 1):
+            ops.MAX_PARTIAL_BYTES = cap
+            results.append(_run_kernel(fn, (qp, kp, q, k, v), do, cfg["kb"] * 128, 0.8))
+    finally:
+        ops.MAX_PARTIAL_BYTES = saved
+    (out_a, grads_a, _), (out_b, grads_b, _) = results
+    assert torch.equal(out_a, out_b)
+    for n, ga, gb in zip(NAMES, grads_a, grads_b):
+        if n in ("dq", "dq_proxy"):
+            assert torch.equal(ga, gb), n
+        else:
+            assert max_err(ga, gb) <= 2 ** -7 * ga.float().abs().max().item() + 1e-6, n
