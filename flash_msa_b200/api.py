@@ -181,9 +181,25 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
         return dqp, dkp, dq, dk, dv, None, None, None
 
 
+def _spread_proxy_heads(q_proxy, k_proxy, q, k):
+    """Fewer proxy heads than KV heads (Hkv % Hp == 0; the reference refuses this, flash_msa/flash_msa.py:44-62): the
+    kernels walk one KV head at a time and want that head's proxy head(s) with it, so every proxy query head is
+    repeated Hkv/Hp times (a differentiable copy of the small proxy tensor).  Each copy then steers the main heads of
+    one KV head with the same scores, hence the same selection, and autograd sums the copies' gradients.  That sum is
+    exact: the gradient of the KL term is linear in the teacher, the copies' teachers are the means over their own
+    main heads, and the per-call factor 1/(B*Hp'*S) with Hp' = Hkv makes their sum the gradient for the mean over all
+    main heads of the proxy head.  (Only the optional KL VALUE differs: it becomes the mean of the copies' KL terms,
+    an upper bound of the KL against the pooled teacher.)"""
+    if q_proxy.ndim == 4 and k_proxy.ndim == 4 and q.ndim == 4 and k.ndim == 4:
+        hp, hpkv, hq, hkv = q_proxy.shape[1], k_proxy.shape[1], q.shape[1], k.shape[1]
+        if 0 < hp < hkv and hkv % hp == 0 and hpkv > 0 and hp % hpkv == 0 and hq % hkv == 0:
+            return q_proxy.repeat_interleave(hkv // hp, dim=1)
+    return q_proxy   # (anything else is judged by the shape checks of the call)
+
+
 def sparse_attention(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
     """Block-sparse top-k GQA attention.  Returns ``(attn_out [B,S,Hq*D], kl_loss placeholder)``."""
-    return _SparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), None)
+    return _SparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), None)
 
 
 def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float):
@@ -197,12 +213,12 @@ def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, s
         raise ValueError("all attention tensors must have shape (B, H, S, D)")
     _require_cuda(q)
     doc_start = ops.doc_start_from_cu_seqlens(cu_seqlens, q.shape[0], q.shape[2], q.device)
-    return _SparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), doc_start)
+    return _SparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), doc_start)
 
 
 def sparse_attention_warmup(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
     """Dense causal warmup attention with full-sequence proxy KL gradients."""
-    return _WarmupSparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), None)
+    return _WarmupSparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), None)
 
 
 def sparse_attention_warmup_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float):
@@ -213,4 +229,4 @@ def sparse_attention_warmup_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k:
         raise ValueError("all attention tensors must have shape (B, H, S, D)")
     _require_cuda(q)
     doc_start = ops.doc_start_from_cu_seqlens(cu_seqlens, q.shape[0], q.shape[2], q.device)
-    return _WarmupSparseAttentionFunction.apply(q_proxy, k_proxy, q, k, v, int(top_k), float(scale), doc_start)
+    return _WarmupSparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), doc_start)

@@ -204,3 +204,28 @@ def test_passes_over_groups_give_the_same_result(fm, warmup):
             assert torch.equal(ga, gb), n
         else:
             assert max_err(ga, gb) <= 2 ** -7 * ga.float().abs().max().item() + 1e-6, n
+
+
+@pytest.mark.parametrize("warmup", [False, True])
+@pytest.mark.parametrize("heads", [(8, 4, 2, 1), (12, 6, 2, 2), (6, 3, 1, 1)])
+def test_fewer_proxy_heads_than_kv_heads(fm, heads, warmup):
+    """Hp < Hkv (refused by the reference): every proxy head steers the main heads of several KV heads and its KL teacher
+    is the mean over all of them.  The public functions spread the proxy query heads over the KV heads and let autograd
+    sum the copies' gradients; the result must be the oracle's for the original head counts."""
+    hq, hkv, hp, hpkv = heads
+    cfg = dict(b=2, s=512, hq=hq, hkv=hkv, hp=hp, hpkv=hpkv, kb=2, seed=41)
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    fn = fm.flash_msa_warmup_func if warmup else fm.flash_msa_func
+    out, grads, _ = _run_kernel(fn, (qp, kp, q, k, v), do, cfg["kb"] * 128, 0.7)
+    assert grads[0].shape == qp.shape
+    if warmup:
+        r32 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 0.7)
+        o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, SCALE), (qp, kp, q, k, v), do, 0.7)
+    else:
+        idx = kernel_selection(qp, kp, cfg["kb"])
+        r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 0.7, block_indices=idx)
+        o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE, block_indices=idx),
+                                               (qp, kp, q, k, v), do, 0.7)
+    yardstick_check("out", out, r32["out"], o16, 1e-3)
+    for n, got, y in zip(NAMES, grads, g16):
+        yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
