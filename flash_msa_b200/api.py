@@ -102,11 +102,46 @@ def check_pending_status():
     ops.deferred_status.drain()
 
 
+# Softmax bias ("attention sink": one learnable logit per main head that joins the softmax denominator and takes
+# probability mass without contributing a value; the reference lists it as missing).  It changes nothing but the
+# normaliser of a row, so it is applied around the kernels: lse' = logaddexp(lse, sink) and out' = out * exp(lse - lse')
+# after the forward; the backward runs on (out', lse') unchanged, because P = exp(s - lse') and delta = rowsum(out' dO)
+# are exactly what it needs.  The KL teacher (mean of the main probabilities) then has rows that sum to
+# T = mean_h exp(lse_h - lse'_h) < 1, and the gradient of -sum_k t_k log p_k becomes T p - t: the proxy log-sum-exp handed
+# to the backward is lowered by log T, which scales the proxy probabilities by T.  The sink's own gradient is
+# -sum over rows of exp(sink - lse') * delta.
+def _apply_sinks(out, lse_main, lse_proxy, sinks, hp):
+    b, hq, s = lse_main.shape
+    sk = sinks.detach().float().view(1, hq, 1)
+    lse2 = torch.logaddexp(lse_main, sk)
+    keep = torch.exp(lse_main - lse2)                                      # 1 - probability of the sink, [B,Hq,S]
+    out2 = (out.view(b, s, hq, -1).float() * keep.transpose(1, 2).unsqueeze(-1)).to(out.dtype).view(out.shape)
+    lse_proxy2 = None
+    if lse_proxy is not None:
+        lse_proxy2 = lse_proxy - torch.log(keep.view(b, hp, hq // hp, s).mean(dim=2))
+    return out2, lse2, lse_proxy2
+
+
+def _sink_grad(out, grad_out, lse_main, sinks):
+    b, hq, s = lse_main.shape
+    delta = (out.view(b, s, hq, -1).float() * grad_out.reshape(b, s, hq, -1).float()).sum(-1).transpose(1, 2)   # [B,Hq,S]
+    return (-(torch.exp(sinks.detach().float().view(1, hq, 1) - lse_main) * delta).sum(dim=(0, 2))).to(sinks.dtype)
+
+
+def _check_sinks(sinks, q):
+    if sinks is None:
+        return None
+    if sinks.ndim != 1 or sinks.shape[0] != q.shape[1] or sinks.device != q.device:
+        raise ValueError("sinks must hold one logit per main query head, on the inputs' device")
+    return sinks
+
+
 class _SparseAttentionFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale, doc_start=None):
+    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale, doc_start=None, sinks=None):
         num_blocks, top_k_blocks = _validate_inputs(q_proxy, k_proxy, q, k, v, int(top_k), True)
         _require_cuda(q)
+        sinks = _check_sinks(sinks, q)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         if top_k_blocks <= ops.FUSED_SELECT_MAX_BLOCKS:
             block_indices = ops.select_blocks_fused(q_proxy, k_proxy, float(scale), top_k_blocks, status=status,
@@ -119,6 +154,9 @@ class _SparseAttentionFunction(torch.autograd.Function):
         out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), rix, status=status,
                                                          doc_start=doc_start)
         _maybe_check(status, "flash_msa_func forward")
+        if sinks is not None:
+            out, lse_main, lse_proxy = _apply_sinks(out, lse_main, lse_proxy, sinks, q_proxy.shape[1])
+        ctx.sinks = sinks
         # kl_loss is a placeholder whose gradient switches the KL branch of the backward on
         # (reference: flash_msa/msa_forward_cutedsl.py:69)
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
@@ -145,20 +183,25 @@ class _SparseAttentionFunction(torch.autograd.Function):
                                                       doc_start=ctx.doc_start)
         _publish_kl(klv)
         _maybe_check(status, "flash_msa_func backward")
-        return dqp, dkp, dq, dk, dv, None, None, None
+        dsinks = _sink_grad(out, grad_out, lse_main, ctx.sinks) if ctx.sinks is not None else None
+        return dqp, dkp, dq, dk, dv, None, None, None, dsinks
 
 
 class _WarmupSparseAttentionFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale, doc_start=None):
+    def forward(ctx, q_proxy, k_proxy, q, k, v, top_k, scale, doc_start=None, sinks=None):
         _ = int(top_k)                         # accepted and ignored, as in the reference
         _validate_inputs(q_proxy, k_proxy, q, k, v, 0, False)
+        sinks = _check_sinks(sinks, q)
         if q.device.type != "cuda":
             raise RuntimeError("warmup MSA forward requires CUDA tensors")
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), None, dense=True,
                                                          status=status, doc_start=doc_start)
         _maybe_check(status, "flash_msa_warmup_func forward")
+        if sinks is not None:
+            out, lse_main, lse_proxy = _apply_sinks(out, lse_main, lse_proxy, sinks, q_proxy.shape[1])
+        ctx.sinks = sinks
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
         ctx.save_for_backward(q_proxy, k_proxy, q, k, v, out, lse_main, lse_proxy)
         ctx.set_materialize_grads(False)
@@ -178,7 +221,8 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
                                                       doc_start=ctx.doc_start)
         _publish_kl(klv)
         _maybe_check(status, "flash_msa_warmup_func backward")
-        return dqp, dkp, dq, dk, dv, None, None, None
+        dsinks = _sink_grad(out, grad_out, lse_main, ctx.sinks) if ctx.sinks is not None else None
+        return dqp, dkp, dq, dk, dv, None, None, None, dsinks
 
 
 def _spread_proxy_heads(q_proxy, k_proxy, q, k):
@@ -197,12 +241,14 @@ def _spread_proxy_heads(q_proxy, k_proxy, q, k):
     return q_proxy   # (anything else is judged by the shape checks of the call)
 
 
-def sparse_attention(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
-    """Block-sparse top-k GQA attention.  Returns ``(attn_out [B,S,Hq*D], kl_loss placeholder)``."""
-    return _SparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), None)
+def sparse_attention(q_proxy, k_proxy, q, k, v, top_k: int, scale: float, sinks=None):
+    """Block-sparse top-k GQA attention.  Returns ``(attn_out [B,S,Hq*D], kl_loss placeholder)``.
+    ``sinks`` (optional, beyond the reference): one softmax-bias logit per main query head, see `_apply_sinks`."""
+    return _SparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), None,
+                                          sinks)
 
 
-def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float):
+def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float, sinks=None):
     """`sparse_attention` on packed sequences: the S positions of every batch element hold several documents laid end
     to end, `cu_seqlens` ([n+1], or [B,n+1] for a packing per batch element; starts at 0, ends at S: the FlashAttention
     varlen convention) gives their boundaries, and a query sees only the keys of its own document - in the block scores
@@ -213,15 +259,17 @@ def sparse_attention_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, s
         raise ValueError("all attention tensors must have shape (B, H, S, D)")
     _require_cuda(q)
     doc_start = ops.doc_start_from_cu_seqlens(cu_seqlens, q.shape[0], q.shape[2], q.device)
-    return _SparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), doc_start)
+    return _SparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), doc_start,
+                                          sinks)
 
 
-def sparse_attention_warmup(q_proxy, k_proxy, q, k, v, top_k: int, scale: float):
+def sparse_attention_warmup(q_proxy, k_proxy, q, k, v, top_k: int, scale: float, sinks=None):
     """Dense causal warmup attention with full-sequence proxy KL gradients."""
-    return _WarmupSparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), None)
+    return _WarmupSparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), None,
+                                                sinks)
 
 
-def sparse_attention_warmup_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float):
+def sparse_attention_warmup_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k: int, scale: float, sinks=None):
     """`sparse_attention_warmup` on packed sequences (see `sparse_attention_varlen`): dense causal attention and the
     full-sequence proxy KL inside every document.  The schedule still visits every causal block pair of the packed
     sequence; pairs that straddle documents are masked."""
@@ -229,4 +277,5 @@ def sparse_attention_warmup_varlen(q_proxy, k_proxy, q, k, v, cu_seqlens, top_k:
         raise ValueError("all attention tensors must have shape (B, H, S, D)")
     _require_cuda(q)
     doc_start = ops.doc_start_from_cu_seqlens(cu_seqlens, q.shape[0], q.shape[2], q.device)
-    return _WarmupSparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), doc_start)
+    return _WarmupSparseAttentionFunction.apply(_spread_proxy_heads(q_proxy, k_proxy, q, k), k_proxy, q, k, v, int(top_k), float(scale), doc_start,
+                                                sinks)

@@ -201,7 +201,7 @@ def _row_token_mask(block_indices_rows: torch.Tensor, q0: int, nkeys: int, nb: i
 # ----------------------------------------------------------------------------
 
 def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
-         want_grads: bool, doc_start=None):
+         want_grads: bool, doc_start=None, sinks=None):
     """Shared worker.  ``block_indices is None`` means warmup (every causal block)."""
     b, hq, s, d = q.shape
     hkv = k.shape[1]
@@ -230,6 +230,7 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
         do = d_out.to(dtype).reshape(b, s, hq, d).permute(0, 2, 1, 3)   # [B,Hq,S,D]
         cnorm = 1.0 / float(b * hp * s)
         gk = None if grad_kl is None else float(grad_kl)
+        dsink = torch.zeros(hq, dtype=dtype, device=dev)
 
     for i in range(nb):
         rows = slice(i * BLOCK, (i + 1) * BLOCK)
@@ -249,6 +250,10 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
         sc = torch.matmul(qf[:, :, rows], kk.transpose(-1, -2)) * scale
         sc = sc.masked_fill(~vis, float("-inf"))
         l = torch.logsumexp(sc, dim=-1)                         # [B,Hq,128]
+        if sinks is not None:
+            # softmax bias ("attention sink", an extension: the reference has none): one learnable logit per main head
+            # joins the softmax denominator and takes probability mass without contributing a value
+            l = torch.logaddexp(l, sinks.to(dtype).view(1, hq, 1).expand_as(l))
         p = torch.exp(sc - l.unsqueeze(-1))
         o = torch.matmul(p, vv)                                 # [B,Hq,128,D]
         out[:, rows] = o.permute(0, 2, 1, 3).reshape(b, BLOCK, hq * d)
@@ -272,6 +277,8 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
             dp = torch.matmul(dob, vv.transpose(-1, -2))        # [B,Hq,128,n]
             delta = (o * dob).sum(-1, keepdim=True)
             ds = p * (dp - delta)                               # dL/d(scaled logits)
+            if sinks is not None:   # the sink's probability times (its zero value's dP - delta)
+                dsink -= (torch.exp(sinks.to(dtype).view(1, hq, 1) - l) * delta.squeeze(-1)).sum(dim=(0, 2))
             dq[:, :, rows] = torch.matmul(ds, kk) * scale
             dk_h = torch.matmul(ds.transpose(-1, -2), qf[:, :, rows]) * scale   # [B,Hq,n,D]
             dv_h = torch.matmul(p.transpose(-1, -2), dob)
@@ -279,7 +286,10 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
             dv[:, :, :n] += dv_h.view(b, hkv, g, n, d).sum(2)
             if gk is not None:
                 ppx = torch.exp(logp).masked_fill(~vis_p, 0.0)
-                dsp = (ppx - teacher) * (cnorm * gk)
+                if sinks is None:
+                    dsp = (ppx - teacher) * (cnorm * gk)
+                else:   # the teacher's rows no longer sum to one: d/dz_j of -sum_k t_k log p_k = (sum_k t_k) p_j - t_j
+                    dsp = (ppx * teacher.sum(-1, keepdim=True) - teacher) * (cnorm * gk)
                 dqp[:, :, rows] = torch.matmul(dsp, kkp) * scale
                 dkp_h = torch.matmul(dsp.transpose(-1, -2), qpf[:, :, rows]) * scale
                 dkp[:, :, :n] += dkp_h.view(b, hpkv, pg, n, d).sum(2)
@@ -288,6 +298,8 @@ def _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype,
     res = {"out": out, "lse": lse, "lse_proxy": lse_p, "kl": kl}
     if want_grads:
         res.update({"dq": dq, "dk": dk, "dv": dv, "dq_proxy": dqp, "dk_proxy": dkp})
+        if sinks is not None:
+            res["dsinks"] = dsink
     return res
 
 
@@ -305,12 +317,12 @@ def sparse_forward(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None,
 
 def sparse_forward_backward(q_proxy, k_proxy, q, k, v, top_k, scale, d_out,
                             grad_kl: Optional[float] = 1.0, block_indices=None,
-                            dtype=torch.float32, doc_start=None):
+                            dtype=torch.float32, doc_start=None, sinks=None):
     """Forward plus closed-form gradients of ``sum(out*d_out) + grad_kl*kl``."""
     kb = int(top_k) // BLOCK
     if block_indices is None:
         block_indices, _ = select_blocks(q_proxy, k_proxy, scale, kb, dtype=dtype, doc_start=doc_start)
-    r = _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype, True, doc_start=doc_start)
+    r = _run(q_proxy, k_proxy, q, k, v, scale, block_indices, d_out, grad_kl, dtype, True, doc_start=doc_start, sinks=sinks)
     r["block_indices"] = block_indices
     return r
 
@@ -321,8 +333,8 @@ def warmup_forward(q_proxy, k_proxy, q, k, v, scale, dtype=torch.float32, doc_st
 
 
 def warmup_forward_backward(q_proxy, k_proxy, q, k, v, scale, d_out,
-                            grad_kl: Optional[float] = 1.0, dtype=torch.float32, doc_start=None):
-    return _run(q_proxy, k_proxy, q, k, v, scale, None, d_out, grad_kl, dtype, True, doc_start=doc_start)
+                            grad_kl: Optional[float] = 1.0, dtype=torch.float32, doc_start=None, sinks=None):
+    return _run(q_proxy, k_proxy, q, k, v, scale, None, d_out, grad_kl, dtype, True, doc_start=doc_start, sinks=sinks)
 
 
 # ----------------------------------------------------------------------------
@@ -331,7 +343,15 @@ def warmup_forward_backward(q_proxy, k_proxy, q, k, v, scale, d_out,
 # reference's own tests run.
 # ----------------------------------------------------------------------------
 
-def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None, doc_start=None):
+def _softmax_with_sinks(attn, sinks):
+    """Row softmax whose denominator also holds exp(sink) of the row's head (attn [B,H,S,S], sinks [H])."""
+    if sinks is None:
+        return torch.softmax(attn, dim=-1)
+    col = sinks.to(attn.dtype).view(1, -1, 1, 1).expand(attn.shape[0], -1, attn.shape[2], 1)
+    return torch.softmax(torch.cat([attn, col], dim=-1), dim=-1)[..., :-1]
+
+
+def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None, doc_start=None, sinks=None):
     """Line-by-line restatement of testing_model.py:61-169 with stable top-k (or a given
     selection).  Differentiable; returns ``(attn_out [B,S,Hq*D], kl_loss)``."""
     b, hp, s, d = q_proxy.shape
@@ -364,7 +384,7 @@ def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None, do
     vv = v.repeat_interleave(g, dim=1)
     attn = torch.matmul(q, kk.transpose(-2, -1)) * scale
     attn = attn.masked_fill(~vis, float("-inf"))
-    probs = torch.softmax(attn, dim=-1)
+    probs = _softmax_with_sinks(attn, sinks)
     out = torch.matmul(probs, vv).transpose(1, 2).reshape(b, s, -1)
 
     target = probs.view(b, hp, mpp, s, s).mean(dim=2).detach()
@@ -375,7 +395,7 @@ def eager_sparse(q_proxy, k_proxy, q, k, v, top_k, scale, block_indices=None, do
     return out, kl
 
 
-def eager_warmup(q_proxy, k_proxy, q, k, v, scale, doc_start=None):
+def eager_warmup(q_proxy, k_proxy, q, k, v, scale, doc_start=None, sinks=None):
     """Restatement of testing_model_warmup.py:63-104.  Differentiable."""
     b, hp, s, d = q_proxy.shape
     hq, hkv, hpkv = q.shape[1], k.shape[1], k_proxy.shape[1]
@@ -390,7 +410,7 @@ def eager_warmup(q_proxy, k_proxy, q, k, v, scale, doc_start=None):
     kk = k.repeat_interleave(g, dim=1)
     vv = v.repeat_interleave(g, dim=1)
     attn = (torch.matmul(q, kk.transpose(-2, -1)) * scale).masked_fill(future, float("-inf"))
-    probs = torch.softmax(attn, dim=-1)
+    probs = _softmax_with_sinks(attn, sinks)
     out = torch.matmul(probs, vv).transpose(1, 2).reshape(b, s, -1)
     target = probs.view(b, hp, mpp, s, s).mean(dim=2).detach().masked_fill(future, 0.0)
     logp = torch.log_softmax(proxy_scores, dim=-1).masked_fill(future, 0.0)
@@ -398,16 +418,18 @@ def eager_warmup(q_proxy, k_proxy, q, k, v, scale, doc_start=None):
     return out, kl
 
 
-def eager_forward_backward(fn, tensors, d_out, grad_kl: Optional[float] = 1.0):
+def eager_forward_backward(fn, tensors, d_out, grad_kl: Optional[float] = 1.0, extra=()):
     """Run a differentiable eager function and return its autograd gradients of
-    ``sum(out*d_out) + grad_kl*kl`` w.r.t. (q_proxy,k_proxy,q,k,v)."""
+    ``sum(out*d_out) + grad_kl*kl`` w.r.t. (q_proxy,k_proxy,q,k,v), followed by those w.r.t. the
+    tensors in ``extra`` (leaves that ``fn`` closes over, e.g. softmax sinks)."""
     leaves = [t.detach().clone().requires_grad_(True) for t in tensors]
     out, kl = fn(*leaves)
     loss = (out * d_out.to(out.dtype)).sum()
     if grad_kl is not None:
         loss = loss + float(grad_kl) * kl
-    grads = torch.autograd.grad(loss, leaves, allow_unused=True)
-    grads = [torch.zeros_like(t) if gr is None else gr for gr, t in zip(grads, leaves)]
+    wrt = leaves + list(extra)
+    grads = torch.autograd.grad(loss, wrt, allow_unused=True)
+    grads = [torch.zeros_like(t) if gr is None else gr for gr, t in zip(grads, wrt)]
     return out.detach(), kl.detach(), grads
 
 

@@ -229,3 +229,36 @@ def test_fewer_proxy_heads_than_kv_heads(fm, heads, warmup):
     yardstick_check("out", out, r32["out"], o16, 1e-3)
     for n, got, y in zip(NAMES, grads, g16):
         yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
+
+
+@pytest.mark.parametrize("warmup", [False, True])
+def test_softmax_sinks(fm, warmup):
+    """One softmax-bias logit per main head (an extension: the reference lists it as missing).  Output, all five
+    gradients and the gradient of the sinks against the oracle, whose closed forms with sinks equal autograd through
+    the eager restatement (softmax over the logits and one extra column)."""
+    cfg = dict(b=2, s=512, hq=8, hkv=2, hp=2, hpkv=1, kb=2, seed=43)
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    sinks = (torch.randn(cfg["hq"], generator=torch.Generator().manual_seed(9)) * 0.7 + 1.0).cuda().requires_grad_(True)
+    leaves = [t.detach().requires_grad_(True) for t in (qp, kp, q, k, v)]
+    fn = fm.flash_msa_warmup_func if warmup else fm.flash_msa_func
+    out, kl = fn(*leaves, cfg["kb"] * 128, SCALE, sinks=sinks)
+    ((out.float() * do.reshape(out.shape).float()).sum() + 0.7 * kl).backward()
+    sk = sinks.detach()
+    if warmup:
+        r32 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 0.7, sinks=sk)
+        sk16 = sk.to(torch.bfloat16).requires_grad_(True)
+        o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, SCALE, sinks=sk16), (qp, kp, q, k, v), do, 0.7, extra=[sk16])
+    else:
+        idx = kernel_selection(qp, kp, cfg["kb"])
+        r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 0.7, block_indices=idx, sinks=sk)
+        sk16 = sk.to(torch.bfloat16).requires_grad_(True)
+        o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE, block_indices=idx, sinks=sk16),
+                                               (qp, kp, q, k, v), do, 0.7, extra=[sk16])
+    yardstick_check("out", out, r32["out"], o16, 2e-3)
+    for n, leaf, y in zip(NAMES, leaves, g16[:5]):
+        yardstick_check(n, leaf.grad, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
+    yardstick_check("dsinks", sinks.grad, r32["dsinks"], g16[5].float(), 2e-3 * r32["dsinks"].abs().max().item())
+    # a sink that is far below every logit changes nothing
+    out0, _ = fn(qp, kp, q, k, v, cfg["kb"] * 128, SCALE)
+    out1, _ = fn(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, sinks=torch.full((cfg["hq"],), -1e4, device="cuda"))
+    assert torch.equal(out0, out1)
