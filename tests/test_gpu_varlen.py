@@ -82,7 +82,7 @@ def test_varlen_forward_backward(fm, name, grad_kl):
 
 
 def test_one_document_equals_the_plain_call(fm):
-    """cu_seqlens = [0, S] must reproduce flash_msa_func bit for bit."""
+    """cu_seqlens = [0, S] must reproduce flash_msa_func (bit for bit where the sums have a fixed order)."""
     cfg = CASES["one_document"][0]
     qp, kp, q, k, v, do = bf16_inputs(cfg)
     res = []
@@ -92,8 +92,11 @@ def test_one_document_equals_the_plain_call(fm):
         out, kl = fn(*leaves)
         ((out.float() * do.reshape(out.shape).float()).sum() + kl).backward()
         res.append([out] + [t.grad for t in leaves])
-    for a, b in zip(*res):
-        assert torch.equal(a, b)
+    for n, a, b in zip(["out"] + NAMES, *res):
+        if n in ("out", "dq", "dq_proxy"):
+            assert torch.equal(a, b), n
+        else:   # fp32 reductions whose order is free once a reverse-index row spans several sub-units
+            assert max_err(a, b) <= 2 ** -7 * b.float().abs().max().item() + 1e-6, n
 
 
 def test_varlen_argument_errors(fm):
