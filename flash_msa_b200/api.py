@@ -122,10 +122,14 @@ def _apply_sinks(out, lse_main, lse_proxy, sinks, hp):
     return out2, lse2, lse_proxy2
 
 
-def _sink_grad(out, grad_out, lse_main, sinks):
+def _sink_grad(out_kernel, grad_out, lse_main, sinks):
+    """`out_kernel` is the output as the kernels wrote it (before the sink rescaling), `lse_main` the log-sum-exp WITH the
+    sink.  delta is formed from out_kernel * (1 - p_sink) in fp32: the rescaled output that the backward kernels read
+    has been rounded a second time, and the sum over all rows of a head amplifies that (measured: twice the error)."""
     b, hq, s = lse_main.shape
-    delta = (out.view(b, s, hq, -1).float() * grad_out.reshape(b, s, hq, -1).float()).sum(-1).transpose(1, 2)   # [B,Hq,S]
-    return (-(torch.exp(sinks.detach().float().view(1, hq, 1) - lse_main) * delta).sum(dim=(0, 2))).to(sinks.dtype)
+    p_sink = torch.exp(sinks.detach().float().view(1, hq, 1) - lse_main)                                       # [B,Hq,S]
+    delta = (out_kernel.view(b, s, hq, -1).float() * grad_out.reshape(b, s, hq, -1).float()).sum(-1).transpose(1, 2) * (1.0 - p_sink)
+    return (-(p_sink * delta).sum(dim=(0, 2))).to(sinks.dtype)
 
 
 def _check_sinks(sinks, q):
@@ -154,7 +158,9 @@ class _SparseAttentionFunction(torch.autograd.Function):
         out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), rix, status=status,
                                                          doc_start=doc_start)
         _maybe_check(status, "flash_msa_func forward")
+        ctx.out_kernel = None
         if sinks is not None:
+            ctx.out_kernel = out
             out, lse_main, lse_proxy = _apply_sinks(out, lse_main, lse_proxy, sinks, q_proxy.shape[1])
         ctx.sinks = sinks
         # kl_loss is a placeholder whose gradient switches the KL branch of the backward on
@@ -183,7 +189,7 @@ class _SparseAttentionFunction(torch.autograd.Function):
                                                       doc_start=ctx.doc_start)
         _publish_kl(klv)
         _maybe_check(status, "flash_msa_func backward")
-        dsinks = _sink_grad(out, grad_out, lse_main, ctx.sinks) if ctx.sinks is not None else None
+        dsinks = _sink_grad(ctx.out_kernel, grad_out, lse_main, ctx.sinks) if ctx.sinks is not None else None
         return dqp, dkp, dq, dk, dv, None, None, None, dsinks
 
 
@@ -199,7 +205,9 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
         out, lse_main, lse_proxy = ops.attention_forward(q, k, v, q_proxy, k_proxy, float(scale), None, dense=True,
                                                          status=status, doc_start=doc_start)
         _maybe_check(status, "flash_msa_warmup_func forward")
+        ctx.out_kernel = None
         if sinks is not None:
+            ctx.out_kernel = out
             out, lse_main, lse_proxy = _apply_sinks(out, lse_main, lse_proxy, sinks, q_proxy.shape[1])
         ctx.sinks = sinks
         kl_loss = torch.zeros((), dtype=torch.float32, device=q.device)
@@ -221,7 +229,7 @@ class _WarmupSparseAttentionFunction(torch.autograd.Function):
                                                       doc_start=ctx.doc_start)
         _publish_kl(klv)
         _maybe_check(status, "flash_msa_warmup_func backward")
-        dsinks = _sink_grad(out, grad_out, lse_main, ctx.sinks) if ctx.sinks is not None else None
+        dsinks = _sink_grad(ctx.out_kernel, grad_out, lse_main, ctx.sinks) if ctx.sinks is not None else None
         return dqp, dkp, dq, dk, dv, None, None, None, dsinks
 
 
