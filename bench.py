@@ -44,6 +44,10 @@ WORKLOADS = {
                 desc="sparse MSA fwd+bwd, quarter of c2: B=1 S=8192 Hq=16 Hkv=4 Hp=4 Hpkv=4 D=128 top_k=16 blocks"),
     "c3": dict(b=4, s=4096, hq=32, hkv=8, hp=8, hpkv=8, kb=1, dense=True,
                desc="MSA warmup fwd+bwd, B=4 S=4096 Hq=32 Hkv=8 Hp=8 Hpkv=8 D=128, dense causal + proxy KL"),
+    # one batch element of config 4 (its B = 8 elements are independent): full length, full head set, skewed selection
+    "c4b1": dict(b=1, s=32768, hq=48, hkv=4, hp=8, hpkv=4, kb=64, dense=False, skew=True,
+                 desc="skewed-selection sparse MSA, one of the 8 batch elements of config 4: B=1 S=32768 Hq=48 Hkv=4 Hp=8 Hpkv=4 "
+                      "top_k=64 blocks, block-mean keys + noise, Qp x4, sink blocks"),
     "c5": dict(b=1, s=65536, hq=64, hkv=8, hp=16, hpkv=8, kb=32, dense=False,
                desc="long-context sparse MSA, B=1 S=65536 Hq=64 Hkv=8 Hp=16 Hpkv=8 top_k=32 blocks, sharded by KV group"),
 }
@@ -460,7 +464,7 @@ def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks, docs=0):
         fn = flash_msa_b200.flash_msa_warmup_varlen_func if cfg["dense"] else flash_msa_b200.flash_msa_varlen_func
         cu = [0] + [min(local["s"], i * local["s"] // docs + 37) for i in range(1, docs)] + [local["s"]]
     host = make_inputs(local["b"], local["s"], local["hq"], local["hkv"], local["hp"], local["hpkv"], seed=ctx.rank,
-                       dtype=torch.bfloat16)
+                       dtype=torch.bfloat16, skew=bool(cfg.get("skew", False)))
     host = [t.pin_memory() for t in host]
     qp, kp, q, k, v, do = [t.to(dev) for t in host]
     ones = torch.ones((), device=dev)
