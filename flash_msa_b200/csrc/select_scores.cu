@@ -241,7 +241,8 @@ int select_common(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, float*
     if (Kb == 0) return FMSA_SELECT(0);
     if (Kb <= 8) return FMSA_SELECT(8);
     if (Kb <= 16) return FMSA_SELECT(16);
-    return FMSA_SELECT(32);
+    if (Kb <= 32) return FMSA_SELECT(32);
+    return FMSA_SELECT(64);
 #undef FMSA_SELECT
 }
 

@@ -339,7 +339,7 @@ def proxy_block_scores(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: floa
     return scores
 
 
-FUSED_SELECT_MAX_BLOCKS = 32
+FUSED_SELECT_MAX_BLOCKS = 64
 
 
 def select_blocks_fused(q_proxy: torch.Tensor, k_proxy: torch.Tensor, scale: float, top_k_blocks: int, status=None,

@@ -140,7 +140,7 @@ int fmsa_select_scores(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, f
  * block_indices [B,Hp,S,top_k_blocks] (int32) itself; the fp32 block scores are never materialised.  Same result,
  * bit for bit, as fmsa_select_scores followed by fmsa_select_topk; larger top_k_blocks return FMSA_ERR_UNSUPPORTED.
  * Replaces the whole reference select kernel (flash_msa/msa_select_cutedsl.py:149-329, 481-538). */
-#define FMSA_FUSED_SELECT_MAX_BLOCKS 32
+#define FMSA_FUSED_SELECT_MAX_BLOCKS 64
 int fmsa_select_fused(const fmsa_tensor* q_proxy, const fmsa_tensor* k_proxy, int32_t* block_indices, int32_t B, int32_t Hp,
                       int32_t Hpkv, int32_t S, int32_t top_k_blocks, float scale, int32_t dtype, const int32_t* doc_start,
                       int32_t* status, void* stream);

@@ -107,7 +107,8 @@ def test_sparse_forward_fp16(ops, name):
 
 
 @pytest.mark.parametrize("s,kb,hp,hpkv", [(128, 1, 1, 1), (512, 2, 2, 1), (1024, 4, 2, 2), (2048, 8, 3, 1), (2048, 9, 2, 2), (4096, 16, 2, 1),
-                                          (4096, 17, 1, 1), (8192, 32, 2, 2), (8192, 5, 1, 1)])
+                                          (4096, 17, 1, 1), (8192, 32, 2, 2), (8192, 5, 1, 1), (8192, 33, 1, 1),
+                                          (8192, 48, 2, 1), (8192, 64, 2, 2), (16384, 64, 1, 1)])
 @pytest.mark.parametrize("docs", [False, True])
 def test_fused_selection_equals_scores_plus_topk(s, kb, hp, hpkv, docs):
     """The fused kernel (block scores and the per-row top-k in one pass, nothing materialised) must give, bit for bit,
