@@ -863,7 +863,7 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const BwdCombineParams
 
 // Wide variant for Hq/Hp <= 8: one sweep over the contiguous mpp*256-byte record of each edge.
 template <int KITER, bool SPLIT, bool FP16>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (latency bound)
-__global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 3) bwd_combine_wide_kernel(const BwdCombineParams P) {
+__global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) bwd_combine_wide_kernel(const BwdCombineParams P) {
     const int lane = threadIdx.x & 31;
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;

@@ -718,50 +718,67 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams P) {
     }
 }
 
-// Wide variant for Hq/Hp <= 8: the partial rows of all main heads of one edge are contiguous
-// (mpp * 256 bytes), so a warp reads them with 16-byte loads per lane in one sweep instead of one
-// 256-byte row at a time; weights go through shared memory.
-// KITER = number of 512-byte sweeps per edge record: Hq/Hp <= 2*KITER.  Templated so that the common
-// small head ratios keep few accumulators in registers and reach a high occupancy (the kernel is
-// bound by memory latency).
+// Wide form for Hq/Hp <= 8, two kernels.  The partial rows of all main heads of one edge are contiguous (mpp * 256
+// bytes), so a warp reads them with 16-byte loads per lane in sweeps of 512 bytes.
+//   combine_lse_kernel   one thread per (query row, edge): loads the (max, sum) pairs of all heads of its edge at once,
+//                        merges them across the row's lanes and writes the row's log-sum-exp per head (and the proxy's).
+//   combine_rows_kernel  one warp per query row: an edge's weight exp2(m_edge - m_row) / l_row equals
+//                        exp2(m_edge - lse_row * log2 e), so with the row's log-sum-exp already in memory nothing but the
+//                        edge positions stands between the kernel and its loads: the partial rows and row maxima of four
+//                        edges are in flight before the first sum.
+// As one kernel (statistics, then weights through shared memory, then the rows) the same work took 0.443 ms at B=2,
+// S=8192, Hq=32, top-k 16 blocks on a B200; the two kernels take 0.062 + 0.338 ms.
 constexpr int kWideMaxHeads = 8;
-template <int KITER, bool FP16>
-__global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel(const CombineParams P) {
-    constexpr int kWideMaxHeads = 2 * KITER;
-    __shared__ float wsm[8][32][kWideMaxHeads + 1];
-    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + wib;
-    const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;
-    if (w >= static_cast<int64_t>(P.G) * P.ppk * P.S) return;
-    const int64_t bp = bp0 + w / P.S;
-    const int q = static_cast<int>(w % P.S);
-    const int b = static_cast<int>(bp / P.Hp), p = static_cast<int>(bp % P.Hp);
-    const int64_t edge_base = P.dense ? dense_edge_base(bp0, P.S, P.NB) : static_cast<int64_t>(P.row_ptr[bp0 * P.NB]);
-    const int nslots = P.dense ? (q >> 7) + 1 : P.Kb;
-    const int lse_stride = P.mpp + 1;
-    const int32_t* erow = P.dense ? nullptr : P.edge_pos + (bp * P.S + q) * P.Kb;
-    auto slot_of = [&](int s) -> int64_t {
+
+// Slot (record number inside the partial buffers of this pass) of edge `s` of query row (bp, q), or -1.
+template <bool DENSE>
+struct CombineRow {
+    int64_t bp;
+    int q, b, p, nslots;
+    int64_t edge_base;
+    const int32_t* erow;
+    __device__ __forceinline__ CombineRow(const CombineParams& P, int64_t w) {
+        const int64_t bp0 = static_cast<int64_t>(P.g_begin) * P.ppk;
+        bp = bp0 + w / P.S;
+        q = static_cast<int>(w % P.S);
+        b = static_cast<int>(bp / P.Hp);
+        p = static_cast<int>(bp % P.Hp);
+        edge_base = DENSE ? dense_edge_base(bp0, P.S, P.NB) : static_cast<int64_t>(P.row_ptr[bp0 * P.NB]);
+        nslots = DENSE ? (q >> 7) + 1 : P.Kb;
+        erow = DENSE ? nullptr : P.edge_pos + (bp * P.S + q) * P.Kb;
+    }
+    __device__ __forceinline__ int slot_of(const CombineParams& P, int s) const {   // slot numbers of a pass fit 31 bits
         if (s >= nslots) return -1;
-        if (P.dense) return dense_edge_base(bp, P.S, P.NB) + dense_row_offset(s, P.S) + (q - s * kBlock) - edge_base;
+        if (DENSE) return static_cast<int>(dense_edge_base(bp, P.S, P.NB) + dense_row_offset(s, P.S) + (q - s * kBlock) - edge_base);
         const int e = erow[s];
-        return e < 0 ? -1 : static_cast<int64_t>(e) - edge_base;
-    };
+        return e < 0 ? -1 : static_cast<int>(e - edge_base);
+    }
+};
+
+template <int LPR, bool DENSE>   // lanes per query row: 16 (two rows per warp, at most 16 edges per row) or 32
+__global__ void __launch_bounds__(256) combine_lse_kernel(const CombineParams P) {
+    constexpr int kMaxHeads = kWideMaxHeads + 1;
+    const int lane = threadIdx.x & 31, l = lane % LPR;
+    const int64_t nrows = static_cast<int64_t>(P.G) * P.ppk * P.S;
+    const int64_t w0 = (static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * (32 / LPR) + lane / LPR;
+    const bool valid = w0 < nrows;   // (lanes of a row beyond the end still take part in the shuffles)
+    const CombineRow<DENSE> row(P, valid ? w0 : nrows - 1);
+    const int lse_stride = P.mpp + 1;
     const float2* stats = reinterpret_cast<const float2*>(P.lse_part);
     const int nheads = P.mpp + (P.lse_proxy ? 1 : 0);
-
-    // pass A: merged (max, sum) of every head over all slots
-    float hm[kWideMaxHeads + 1], hs[kWideMaxHeads + 1];
+    float hm[kMaxHeads], hs[kMaxHeads];
 #pragma unroll
-    for (int hh = 0; hh <= kWideMaxHeads; ++hh) {
+    for (int hh = 0; hh < kMaxHeads; ++hh) {
         hm[hh] = -INFINITY;
         hs[hh] = 0.f;
     }
-    for (int s0 = 0; s0 < nslots; s0 += 32) {
-        const int64_t sl = slot_of(s0 + lane);
+    for (int s0 = 0; s0 < row.nslots; s0 += LPR) {
+        const int sl = valid ? row.slot_of(P, s0 + l) : -1;
+        const float2* rec = stats + static_cast<int64_t>(sl) * lse_stride;
 #pragma unroll
-        for (int hh = 0; hh <= kWideMaxHeads; ++hh) {
+        for (int hh = 0; hh < kMaxHeads; ++hh) {
             if (hh < nheads && sl >= 0) {
-                const float2 st = stats[sl * lse_stride + hh];
+                const float2 st = rec[hh];
                 const float mn = fmaxf(hm[hh], st.x);
                 hs[hh] = hs[hh] * fast_exp2(hm[hh] - mn) + st.y * fast_exp2(st.x - mn);
                 hm[hh] = mn;
@@ -769,10 +786,10 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel
         }
     }
 #pragma unroll
-    for (int hh = 0; hh <= kWideMaxHeads; ++hh) {
+    for (int hh = 0; hh < kMaxHeads; ++hh) {
         if (hh < nheads) {
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
+            for (int off = LPR / 2; off > 0; off >>= 1) {
                 const float mo = __shfl_xor_sync(0xffffffffu, hm[hh], off);
                 const float so = __shfl_xor_sync(0xffffffffu, hs[hh], off);
                 const float mn = fmaxf(hm[hh], mo);
@@ -781,52 +798,73 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_wide_kernel
                 hs[hh] = a + c;
                 hm[hh] = mn;
             }
-            const float total = (hm[hh] + __log2f(hs[hh])) * kLn2;
-            if (lane == 0) {
-                if (hh == P.mpp) P.lse_proxy[bp * P.S + q] = total;
-                else P.lse[(static_cast<int64_t>(b) * P.Hq + p * P.mpp + hh) * P.S + q] = total;
+            if (l == 0 && valid) {
+                const float total = (hm[hh] + __log2f(hs[hh])) * kLn2;   // natural-log LSE of the whole row
+                if (hh == P.mpp) P.lse_proxy[row.bp * P.S + row.q] = total;
+                else P.lse[(static_cast<int64_t>(row.b) * P.Hq + row.p * P.mpp + hh) * P.S + row.q] = total;
             }
         }
     }
-    // pass B: lane owns 16-byte chunks ck = k*32 + lane of the mpp*128-element edge record
-    const int nchunk = P.mpp * 16;
+}
+
+template <int KITER, bool FP16, bool DENSE>   // Hq/Hp <= 2*KITER: few accumulators, high occupancy (the kernel is bound by memory latency)
+__global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_rows_kernel(const CombineParams P) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (w >= static_cast<int64_t>(P.G) * P.ppk * P.S) return;
+    const CombineRow<DENSE> row(P, w);
+    const int lse_stride = P.mpp + 1;
+    const float2* stats = reinterpret_cast<const float2*>(P.lse_part);
+    const int nchunk = P.mpp * 16;   // lane owns the 16-byte chunks ck = k*32 + lane of the mpp*128-element edge record
     float acc[KITER][8];
+    float row_lse2[KITER];   // the row's log-sum-exp of the lane's head in each sweep, in the log2 domain
 #pragma unroll
-    for (int k = 0; k < KITER; ++k)
+    for (int k = 0; k < KITER; ++k) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
-    for (int s0 = 0; s0 < nslots; s0 += 32) {
-        const int64_t sl = slot_of(s0 + lane);
-        __syncwarp();
+        const int hh = min((k * 32 + lane) >> 4, P.mpp - 1);
+        row_lse2[k] = P.lse[(static_cast<int64_t>(row.b) * P.Hq + row.p * P.mpp + hh) * P.S + row.q] * kLog2e;
+    }
+    for (int s0 = 0; s0 < row.nslots; s0 += 32) {
+        const int sl = row.slot_of(P, s0 + lane);
+        const int cnt = min(32, row.nslots - s0);
+        for (int i = 0; i < cnt; i += 4) {
+            int si[4];
 #pragma unroll
-        for (int hh = 0; hh < kWideMaxHeads; ++hh)
-            if (hh < P.mpp) wsm[wib][lane][hh] = sl >= 0 ? fast_exp2(stats[sl * lse_stride + hh].x - hm[hh]) / hs[hh] : 0.f;
-        __syncwarp();
-        const int cnt = min(32, nslots - s0);
-#pragma unroll 4
-        for (int i = 0; i < cnt; ++i) {
-            const int64_t si = __shfl_sync(0xffffffffu, sl, i);
-            if (si < 0) continue;
-            const __nv_bfloat16* rec = P.o_part + si * P.mpp * kHeadDim;
+            for (int u = 0; u < 4; ++u) {
+                const int v = __shfl_sync(0xffffffffu, sl, (i + u) & 31);
+                si[u] = (i + u < cnt) ? v : -1;
+            }
+            uint4 raw[4][KITER];
+            float em[4][KITER];
 #pragma unroll
-            for (int k = 0; k < KITER; ++k) {
-                const int ck = k * 32 + lane;
-                if (ck < nchunk) {
-                    const float wgt = wsm[wib][i][ck >> 4];
-                    const uint4 raw = *reinterpret_cast<const uint4*>(rec + ck * 8);
-                    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+            for (int u = 0; u < 4; ++u) {
+                const __nv_bfloat16* rec = P.o_part + static_cast<int64_t>(si[u]) * P.mpp * kHeadDim;
+#pragma unroll
+                for (int k = 0; k < KITER; ++k) {
+                    const int ck = k * 32 + lane;
+                    const bool ok = si[u] >= 0 && ck < nchunk;
+                    raw[u][k] = ok ? *reinterpret_cast<const uint4*>(rec + ck * 8) : make_uint4(0, 0, 0, 0);
+                    em[u][k] = ok ? stats[static_cast<int64_t>(si[u]) * lse_stride + (ck >> 4)].x : -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int k = 0; k < KITER; ++k) {
+                    const uint32_t w4[4] = {raw[u][k].x, raw[u][k].y, raw[u][k].z, raw[u][k].w};
+                    const float wgt = fast_exp2(em[u][k] - row_lse2[k]);   // an absent edge: exp2(-inf) = 0
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const uint32_t v2 = u[e];
-                        acc[k][2 * e] += wgt * act_lo<FP16>(v2);
-                        acc[k][2 * e + 1] += wgt * act_hi<FP16>(v2);
+                        acc[k][2 * e] += wgt * act_lo<FP16>(w4[e]);
+                        acc[k][2 * e + 1] += wgt * act_hi<FP16>(w4[e]);
                     }
                 }
             }
         }
     }
-    __nv_bfloat16* orow = P.out + (static_cast<int64_t>(b) * P.S + q) * (static_cast<int64_t>(P.Hq) * kHeadDim) +
-                          static_cast<int64_t>(p) * P.mpp * kHeadDim;
+    __nv_bfloat16* orow = P.out + (static_cast<int64_t>(row.b) * P.S + row.q) * (static_cast<int64_t>(P.Hq) * kHeadDim) +
+                          static_cast<int64_t>(row.p) * P.mpp * kHeadDim;
 #pragma unroll
     for (int k = 0; k < KITER; ++k) {
         const int ck = k * 32 + lane;
@@ -937,19 +975,23 @@ extern "C" int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_par
     FMSA_REQUIRE(grid <= 0x7fffffffLL);
     const dim3 cg(static_cast<unsigned>(grid));
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
-    if (pb->dtype == FMSA_DTYPE_FP16) {
-        if (P.mpp <= 2) combine_wide_kernel<1, true><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 4) combine_wide_kernel<2, true><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 6) combine_wide_kernel<3, true><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 8) combine_wide_kernel<4, true><<<cg, 256, 0, cst>>>(P);
-        else combine_kernel<true><<<cg, 256, 0, cst>>>(P);
-    } else {
-        if (P.mpp <= 2) combine_wide_kernel<1, false><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 4) combine_wide_kernel<2, false><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 6) combine_wide_kernel<3, false><<<cg, 256, 0, cst>>>(P);
-        else if (P.mpp <= 8) combine_wide_kernel<4, false><<<cg, 256, 0, cst>>>(P);
+    const bool f16 = pb->dtype == FMSA_DTYPE_FP16;
+    if (P.mpp > kWideMaxHeads) {
+        if (f16) combine_kernel<true><<<cg, 256, 0, cst>>>(P);
         else combine_kernel<false><<<cg, 256, 0, cst>>>(P);
+        return check_launch();
     }
+    if (dense) combine_lse_kernel<32, true><<<cg, 256, 0, cst>>>(P);
+    else if (P.Kb <= 16) combine_lse_kernel<16, false><<<dim3(static_cast<unsigned>((rows + 15) / 16)), 256, 0, cst>>>(P);
+    else combine_lse_kernel<32, false><<<cg, 256, 0, cst>>>(P);
+#define FMSA_ROWS2(K, F) (dense ? combine_rows_kernel<K, F, true><<<cg, 256, 0, cst>>>(P) : combine_rows_kernel<K, F, false><<<cg, 256, 0, cst>>>(P))
+#define FMSA_ROWS(K) (f16 ? FMSA_ROWS2(K, true) : FMSA_ROWS2(K, false))
+    if (P.mpp <= 2) FMSA_ROWS(1);
+    else if (P.mpp <= 4) FMSA_ROWS(2);
+    else if (P.mpp <= 6) FMSA_ROWS(3);
+    else FMSA_ROWS(4);
+#undef FMSA_ROWS2
+#undef FMSA_ROWS
     return check_launch();
 }
 

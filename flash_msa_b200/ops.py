@@ -428,7 +428,7 @@ def attention_forward(q, k, v, q_proxy, k_proxy, scale, rix, *, dense=False, wit
                 col_q, o_part.data_ptr(), lse_part.data_ptr(), slots, g0, gc, int(with_proxy), int(dense),
                 counter.data_ptr(), status.data_ptr(), st), dev)
         with _Timed("fwd_combine", dev):
-            _launch("fmsa_sparse_fwd_combine", 1, lib.fmsa_sparse_fwd_combine(
+            _launch("fmsa_sparse_fwd_combine", 2 if mpp <= 8 else 1, lib.fmsa_sparse_fwd_combine(   # log-sum-exp kernel + row kernel
                 ctypes_byref(pb), o_part.data_ptr(), lse_part.data_ptr(), edge_pos, row_ptr, out.data_ptr(), lse.data_ptr(),
                 lse_proxy.data_ptr() if with_proxy else 0, g0, gc, int(dense), st), dev)
     return out, lse, lse_proxy

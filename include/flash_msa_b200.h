@@ -166,7 +166,9 @@ int fmsa_sparse_fwd(const fmsa_problem* pb, const fmsa_tensor* q, const fmsa_ten
 
 /* Sparse forward, stage 2: merge the partials of each query row (the job of the reference's
  * merge_attention_chunk / merge_lse_chunk kernels, flash_msa/csrc/reverse_index_cuda.cu:235-354).
- *   out bf16 [B, S, Hq*128]   lse fp32 [B, Hq, S]   lse_proxy fp32 [B, Hp, S] or NULL */
+ *   out bf16 [B, S, Hq*128]   lse fp32 [B, Hq, S]   lse_proxy fp32 [B, Hp, S] or NULL
+ * Two launches for Hq/Hp <= 8 (the rows' log-sum-exp from the statistics, then the weighted sum of the partial rows,
+ * which reads lse back), one otherwise. */
 int fmsa_sparse_fwd_combine(const fmsa_problem* pb, const void* o_part, const float* lse_part,
                             const int32_t* edge_pos, const int32_t* row_ptr, void* out, float* lse, float* lse_proxy,
                             int32_t g_begin, int32_t g_count, int32_t dense, void* stream);
