@@ -235,6 +235,29 @@ def test_fewer_proxy_heads_than_kv_heads(fm, heads, warmup):
 
 
 @pytest.mark.parametrize("warmup", [False, True])
+@pytest.mark.parametrize("mpp", [5, 7, 8, 12, 16])
+def test_main_heads_per_proxy_head(fm, mpp, warmup):
+    """Hq/Hp beyond the BASELINE shapes: 5, 7 and 8 main heads per proxy head take the three- and four-sweep forms of the
+    combine kernels, 12 and 16 the one-head-at-a-time forms; 5 and 7 do not divide 128 (the reference refuses them,
+    flash_msa/flash_msa.py:153-158)."""
+    cfg = dict(b=1, s=768, hq=2 * mpp, hkv=2, hp=2, hpkv=1, kb=3, seed=50 + mpp)
+    qp, kp, q, k, v, do = bf16_inputs(cfg)
+    fn = fm.flash_msa_warmup_func if warmup else fm.flash_msa_func
+    out, grads, _ = _run_kernel(fn, (qp, kp, q, k, v), do, cfg["kb"] * 128, 0.7)
+    if warmup:
+        r32 = O.warmup_forward_backward(qp, kp, q, k, v, SCALE, do, 0.7)
+        o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, SCALE), (qp, kp, q, k, v), do, 0.7)
+    else:
+        idx = kernel_selection(qp, kp, cfg["kb"])
+        r32 = O.sparse_forward_backward(qp, kp, q, k, v, cfg["kb"] * 128, SCALE, do, 0.7, block_indices=idx)
+        o16, _, g16 = O.eager_forward_backward(lambda *t: O.eager_sparse(*t, cfg["kb"] * 128, SCALE, block_indices=idx),
+                                               (qp, kp, q, k, v), do, 0.7)
+    yardstick_check("out", out, r32["out"], o16, 1e-3)
+    for n, got, y in zip(NAMES, grads, g16):
+        yardstick_check(n, got, r32[n], y, _floors(r32[n]) if n in ("dq", "dk", "dv") else 1e-3 * r32[n].abs().max().item())
+
+
+@pytest.mark.parametrize("warmup", [False, True])
 def test_softmax_sinks(fm, warmup):
     """One softmax-bias logit per main head (an extension: the reference lists it as missing).  Output, all five
     gradients and the gradient of the sinks against the oracle, whose closed forms with sinks equal autograd through
