@@ -785,21 +785,19 @@ __global__ void __launch_bounds__(256) combine_lse_kernel(const CombineParams P)
             }
         }
     }
+    // Across the row's lanes: first the maximum, then the sums brought to it (half the instructions of merging
+    // (max, sum) pairs in every round; the kernel is bound by instruction issue, not by memory).
 #pragma unroll
     for (int hh = 0; hh < kMaxHeads; ++hh) {
         if (hh < nheads) {
+            float m = hm[hh];
 #pragma unroll
-            for (int off = LPR / 2; off > 0; off >>= 1) {
-                const float mo = __shfl_xor_sync(0xffffffffu, hm[hh], off);
-                const float so = __shfl_xor_sync(0xffffffffu, hs[hh], off);
-                const float mn = fmaxf(hm[hh], mo);
-                const float a = (hm[hh] == -INFINITY) ? 0.f : hs[hh] * fast_exp2(hm[hh] - mn);
-                const float c = (mo == -INFINITY) ? 0.f : so * fast_exp2(mo - mn);
-                hs[hh] = a + c;
-                hm[hh] = mn;
-            }
+            for (int off = LPR / 2; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+            float sum = (hm[hh] == -INFINITY) ? 0.f : hs[hh] * fast_exp2(hm[hh] - m);
+#pragma unroll
+            for (int off = LPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
             if (l == 0 && valid) {
-                const float total = (hm[hh] + __log2f(hs[hh])) * kLn2;   // natural-log LSE of the whole row
+                const float total = (m + __log2f(sum)) * kLn2;   // natural-log LSE of the whole row
                 if (hh == P.mpp) P.lse_proxy[row.bp * P.S + row.q] = total;
                 else P.lse[(static_cast<int64_t>(row.b) * P.Hq + row.p * P.mpp + hh) * P.S + row.q] = total;
             }
@@ -854,10 +852,24 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) combine_rows_kernel
                 for (int k = 0; k < KITER; ++k) {
                     const uint32_t w4[4] = {raw[u][k].x, raw[u][k].y, raw[u][k].z, raw[u][k].w};
                     const float wgt = fast_exp2(em[u][k] - row_lse2[k]);   // an absent edge: exp2(-inf) = 0
+                    // Packed two-wide FMAs pay at three and four sweeps (120-128 registers, two CTAs per SM: 4.45 -> 4.20 ms
+                    // at Hq/Hp = 6, 64 edges per row); at one and two sweeps they cost registers the 64-register budget
+                    // of four CTAs per SM does not have (0.392 -> 0.406 ms at Hq/Hp = 4, 16 edges per row).
+                    if constexpr (KITER >= 3) {
+                        const float2 wg2 = make_float2(wgt, wgt);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        acc[k][2 * e] += wgt * act_lo<FP16>(w4[e]);
-                        acc[k][2 * e + 1] += wgt * act_hi<FP16>(w4[e]);
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 a = f2_fma(wg2, make_float2(act_lo<FP16>(w4[e]), act_hi<FP16>(w4[e])),
+                                                    make_float2(acc[k][2 * e], acc[k][2 * e + 1]));
+                            acc[k][2 * e] = a.x;
+                            acc[k][2 * e + 1] = a.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[k][2 * e] += wgt * act_lo<FP16>(w4[e]);
+                            acc[k][2 * e + 1] += wgt * act_hi<FP16>(w4[e]);
+                        }
                     }
                 }
             }
