@@ -921,10 +921,20 @@ __global__ void __launch_bounds__(256, (KITER <= 2) ? 4 : 2) bwd_combine_wide_ke
 #pragma unroll
                     for (int k = 0; k < KITER; ++k) {
                         const uint32_t w4[4] = {raw[u][k].x, raw[u][k].y, raw[u][k].z, raw[u][k].w};
+                        if constexpr (KITER >= 3) {   // packed adds pay at 120-128 registers and two CTAs per SM, not at 64
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            acc[k][2 * e] += act_lo<FP16>(w4[e]);
-                            acc[k][2 * e + 1] += act_hi<FP16>(w4[e]);
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 a = f2_add(make_float2(acc[k][2 * e], acc[k][2 * e + 1]),
+                                                        make_float2(act_lo<FP16>(w4[e]), act_hi<FP16>(w4[e])));
+                                acc[k][2 * e] = a.x;
+                                acc[k][2 * e + 1] = a.y;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                acc[k][2 * e] += act_lo<FP16>(w4[e]);
+                                acc[k][2 * e + 1] += act_hi<FP16>(w4[e]);
+                            }
                         }
                     }
                     pa0 += act_lo<FP16>(praw[u].x);
