@@ -516,6 +516,7 @@ def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks, docs=0):
         ctx.sync_all()
         s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         n_e2e = max(2, min(steps, 5))
+        allocs0 = torch.cuda.memory_stats(dev).get("num_device_alloc", 0)
         s2.record()
         for _ in range(n_e2e):
             hs.run(*host, grad_kl=1.0)
@@ -525,6 +526,8 @@ def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks, docs=0):
         e2.record()
         ctx.sync_all()
         e2e_ms = ctx.max_over_ranks(s2.elapsed_time(e2))
+        # cudaMalloc calls of the caching allocator inside the timed steps (each one waits for the device): 0 in a steady pipeline
+        e2e_allocs = torch.cuda.memory_stats(dev).get("num_device_alloc", 0) - allocs0
         h2d, d2h = hs.bytes_per_step()
         # Copy-only floor: the same bytes as one contiguous pinned copy per tensor in each direction, both
         # directions at once, every rank at the same time.  What the host link gives whatever the kernels do.
@@ -553,7 +556,8 @@ def time_workload(ctx, name, steps, warmup, with_e2e, sample_clocks, docs=0):
         floor_ms = ctx.max_over_ranks(c0.elapsed_time(c1)) / 3
         total_f = flops(cfg) * (ctx.world if scaling == "weak" else 1)
         res["e2e"] = {"value": total_f * n_e2e / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                      "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e, "copy_floor_ms": floor_ms}
+                      "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e, "copy_floor_ms": floor_ms,
+                      "device_allocs_in_timed_steps": e2e_allocs}
         del hs, outs_dev
     del qp, kp, q, k, v, do, host
     torch.cuda.empty_cache()

@@ -64,7 +64,7 @@ class HostStep:
         self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
         d = 128
         self.dev_in = []      # per chunk: device copies of the six inputs
-        self.ev_in, self.ev_cmp = [], []
+        self.ev_in, self.ev_cmp, self.ev_out = [], [], []
         for c in self.chunks:
             (h0, h1), (kv0, kv1), (p0, p1), (kp0, kp1) = head_ranges(c, hq, hkv, hp, hpkv)
             nb = c.b1 - c.b0
@@ -73,10 +73,18 @@ class HostStep:
                                 torch.empty(nb, s, (h1 - h0) * d, dtype=dtype, device=self.dev)))
             self.ev_in.append(torch.cuda.Event())
             self.ev_cmp.append(torch.cuda.Event())
+            self.ev_out.append(torch.cuda.Event())
         pin = lambda *shape: torch.empty(*shape, dtype=dtype, pin_memory=True)
         self.host_out = (pin(b, s, hq * d), pin(b, hp, s, d), pin(b, hpkv, s, d), pin(b, hq, s, d), pin(b, hkv, s, d),
                          pin(b, hkv, s, d))
-        self._keep = []       # device results of the step in flight (kept alive until the next step)
+        # Device results of the step in flight, per chunk.  They are produced on the compute stream and read by the
+        # copy-out stream; a chunk's results are released only after the compute stream has been made to wait for the
+        # copy-out of that chunk, so the caching allocator hands their memory to later work of the compute stream alone
+        # and the set of blocks in use is the same every step, however far the host runs ahead of the device.
+        # (Marking them with record_stream instead lets the allocator defer their reuse by host timing: a step that
+        # found no free block called cudaMalloc, which waits for the device - measured as steps of 26-29 ms among
+        # steps of 9 ms.)
+        self._keep = [None] * len(self.chunks)
         self._first = True
 
     # -- copies ------------------------------------------------------------------------------
@@ -112,7 +120,6 @@ class HostStep:
         for t in (q_proxy, k_proxy, q, k, v, d_out):
             if t.device.type != "cpu" or not t.is_pinned() or not t.is_contiguous() or t.dtype != self.dtype:
                 raise ValueError("HostStep.run takes contiguous pinned host tensors of the configured dtype")
-        keep = []
         for ci, c in enumerate(self.chunks):
             (h0, h1), (kv0, kv1), (p0, p1), (kp0, kp1) = head_ranges(c, hq, hkv, hp, hpkv)
             dqp_d, dkp_d, dq_d, dk_d, dv_d, do_d = self.dev_in[ci]
@@ -128,6 +135,9 @@ class HostStep:
                 self.ev_in[ci].record(self.s_in)
             with torch.cuda.stream(self.s_cmp):
                 self.s_cmp.wait_event(self.ev_in[ci])
+                if not self._first:
+                    self.s_cmp.wait_event(self.ev_out[ci])    # last step's results of this chunk have reached the host
+                self._keep[ci] = None
                 leaves = [t.detach().requires_grad_(True) for t in (dqp_d, dkp_d, dq_d, dk_d, dv_d)]
                 out, kl = self.fn(*leaves, self.top_k, self.scale)
                 if grad_kl is None:
@@ -140,8 +150,6 @@ class HostStep:
                 self.ev_cmp[ci].record(self.s_cmp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_cmp[ci])
-                for r in res:
-                    r.record_stream(self.s_out)
                 ho, hdqp, hdkp, hdq, hdk, hdv = self.host_out
                 self._copy_rows(ho, res[0], c.b0, c.b1, h0, h1, hq, self.s_out)
                 self._copy_heads(hdqp, res[1], c.b0, c.b1, p0, p1, self.s_out)
@@ -149,8 +157,9 @@ class HostStep:
                 self._copy_heads(hdq, res[3], c.b0, c.b1, h0, h1, self.s_out)
                 self._copy_heads(hdk, res[4], c.b0, c.b1, kv0, kv1, self.s_out)
                 self._copy_heads(hdv, res[5], c.b0, c.b1, kv0, kv1, self.s_out)
-            keep.append(res)
-        self._keep = keep
+                self.ev_out[ci].record(self.s_out)
+            self._keep[ci] = res
+            del res, leaves, out, kl
         self._first = False
         return self.host_out
 

@@ -267,12 +267,12 @@ class DeferredStatus:
 
     def __init__(self):
         self._host = None
-        self._pending = []        # (slot, event, what)
+        self._pending = []        # (slot, event, what, status tensor: kept alive until its copy has run)
         self._next = 0
 
     def _poll(self, block: bool) -> None:
         while self._pending:
-            slot, event, what = self._pending[0]
+            slot, event, what, _ = self._pending[0]
             if block:
                 event.synchronize()
             elif not event.query():
@@ -305,8 +305,9 @@ class DeferredStatus:
         with torch.cuda.stream(side):
             self._host[slot:slot + 1].copy_(status, non_blocking=True)
             event.record(side)
-        status.record_stream(side)
-        self._pending.append((slot, event, what))
+        # (the reference held here, not record_stream: the caching allocator then never has to defer the reuse of
+        # the word's block by the side stream's progress, which would make its behaviour depend on host timing)
+        self._pending.append((slot, event, what, status))
 
     def drain(self) -> None:
         """Waits for every queued status word and raises for the first non-zero one."""
