@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sparse_fwd_kernel(const __grid
     unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     const long long trace_t0 = clock64();
 #endif
-    auto wait = [&](uint32_t bar, uint32_t parity, int kind = 1) {   // every lane of the warp calls it; the verdict is warp-uniform
+    auto wait = [&](uint32_t bar, uint32_t parity, int kind = 1) {   // every lane of the warp calls it; the result is warp-uniform
 #ifdef FMSA_TRACE
         const long long w0 = clock64();
 #endif
