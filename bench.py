@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the Flash-MSA training hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2q|c3|c4b1|c5]
 
 One step = one forward + backward of ``flash_msa_func`` (block scoring, top-k, reverse index, sparse
 forward with combine, fused backward, casts) on synthetic N(0,1) bf16 inputs of the benchmark
@@ -15,9 +15,13 @@ padding are not counted).  Timing: CUDA events on the launching stream, barrier 
 synchronize on both sides, max over ranks.  Inputs (>400 MB per step) exceed the 126 MB L2, so no
 explicit flush is needed.
 
-``--impl reference`` times the reference algorithm on the host cores instead: the oracle's
-restatement of the reference's eager model (fp32, all torch threads) on one (batch, KV-head group)
-slice of the same workload per step.
+``e2e`` is the same step through ``flash_msa_b200.host.HostStep`` on pinned host buffers (copies in both directions
+inside the timed region), with ``copy_floor_ms`` (the same copies alone) and ``device_allocs_in_timed_steps`` (cudaMalloc
+calls of the caching allocator inside the timed steps; 0 in a steady pipeline) beside it.
+
+``--impl reference`` times the reference algorithm on the host cores instead: the reference's own eager
+model from the local copy under ``oracle/_ref`` (the oracle's restatement of it when that copy is absent), fp32, all
+torch threads, on one (batch, KV-head group) slice of the same workload per step.
 """
 from __future__ import annotations
 
