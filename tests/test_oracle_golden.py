@@ -210,3 +210,54 @@ def test_doc_start_helper_matches_the_oracle_and_rejects_bad_packings():
     for bad in ([1, 512], [0, 100], [0, 300, 200, 512], [[0, 512]] * 3):
         with pytest.raises(ValueError):
             ops.doc_start_from_cu_seqlens(bad, 2, 512, "cpu")
+
+
+@pytest.mark.parametrize("warmup", [False, True])
+def test_softmax_sinks_of_the_oracle(warmup):
+    """Softmax sinks (an extension: the reference lists the softmax bias as missing) are pinned by their definition: the
+    closed forms of the oracle - output, all five gradients, the gradient of the sinks - must equal autograd through the
+    eager restatement, whose softmax simply gains one column per main head; and a sink of -inf changes nothing."""
+    import torch
+    from oracle import msa_oracle as O
+    b, s, hq, hkv, hp, hpkv = 2, 384, 8, 2, 2, 1
+    qp, kp, q, k, v, do = O.make_inputs(b, s, hq, hkv, hp, hpkv, seed=11)
+    t64 = [t.double() for t in (qp, kp, q, k, v)]
+    sinks = (torch.randn(hq, generator=torch.Generator().manual_seed(5), dtype=torch.float64) * 0.8 + 0.3).requires_grad_(True)
+    if warmup:
+        r = O.warmup_forward_backward(*t64, 0.088, do.double(), 0.6, dtype=torch.float64, sinks=sinks.detach())
+        fn = lambda *t: O.eager_warmup(*t, 0.088, sinks=sinks)
+        r_inf = O.warmup_forward_backward(*t64, 0.088, do.double(), 0.6, dtype=torch.float64,
+                                          sinks=torch.full((hq,), float("-inf"), dtype=torch.float64))
+        r_none = O.warmup_forward_backward(*t64, 0.088, do.double(), 0.6, dtype=torch.float64)
+    else:
+        r = O.sparse_forward_backward(*t64, 256, 0.088, do.double(), 0.6, dtype=torch.float64, sinks=sinks.detach())
+        idx = r["block_indices"]
+        fn = lambda *t: O.eager_sparse(*t, 256, 0.088, block_indices=idx, sinks=sinks)
+        r_inf = O.sparse_forward_backward(*t64, 256, 0.088, do.double(), 0.6, dtype=torch.float64, block_indices=idx,
+                                          sinks=torch.full((hq,), float("-inf"), dtype=torch.float64))
+        r_none = O.sparse_forward_backward(*t64, 256, 0.088, do.double(), 0.6, dtype=torch.float64, block_indices=idx)
+    out, kl, grads = O.eager_forward_backward(fn, t64, do.double(), 0.6, extra=[sinks])
+    assert (out - r["out"]).abs().max().item() < 1e-11
+    for n, g in zip(["dq_proxy", "dk_proxy", "dq", "dk", "dv", "dsinks"], grads):
+        assert (g - r[n]).abs().max().item() < 1e-11, n
+    assert r["dsinks"].abs().max().item() > 1e-3          # (the comparison above is not one of zeros)
+    for n in ("out", "dq_proxy", "dk_proxy", "dq", "dk", "dv"):
+        assert (r_inf[n] - r_none[n]).abs().max().item() < 1e-12, n
+
+
+def test_fewer_proxy_heads_than_kv_heads_by_repetition():
+    """Hp < Hkv (refused by the reference) is served by repeating every proxy query head Hkv/Hp times and summing the
+    copies' gradients.  In fp64 on the oracle that must be the gradient of the model with the original head counts: the
+    KL gradient is linear in the teacher, and the per-call factor 1/(B*Hp'*S) with Hp' = Hkv turns the copies'
+    sub-means into the mean over all main heads of the proxy head."""
+    import torch
+    from oracle import msa_oracle as O
+    b, s, hq, hkv, hp, hpkv = 2, 384, 8, 4, 2, 1
+    qp, kp, q, k, v, do = [t.double() for t in O.make_inputs(b, s, hq, hkv, hp, hpkv, seed=13)]
+    want_out, _, want = O.eager_forward_backward(lambda *t: O.eager_warmup(*t, 0.088), (qp, kp, q, k, v), do, 0.9)
+    rep = hkv // hp
+    r = O.warmup_forward_backward(qp.repeat_interleave(rep, dim=1), kp, q, k, v, 0.088, do, 0.9, dtype=torch.float64)
+    assert (r["out"] - want_out).abs().max().item() < 1e-12
+    got = [r["dq_proxy"].view(b, hp, rep, s, -1).sum(2), r["dk_proxy"], r["dq"], r["dk"], r["dv"]]
+    for n, g, w in zip(["dq_proxy", "dk_proxy", "dq", "dk", "dv"], got, want):
+        assert (g - w).abs().max().item() < 1e-11, n
