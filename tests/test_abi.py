@@ -29,3 +29,15 @@ def test_argument_errors_do_not_launch():
     assert lib.fmsa_bwd_delta(None, None, None, 1, 128, 1, 0, None) == -1
     pb = _lib.FmsaProblem(1, 100, 4, 2, 2, 2, 1, 0.1, 0)      # S is not a multiple of 128
     assert lib.fmsa_fwd_partial_slots(ctypes.byref(pb), 1, 0) <= 0
+
+
+def test_fused_selection_refuses_what_it_cannot_hold():
+    """More selected blocks than the fused kernel's register list holds is answered with FMSA_ERR_UNSUPPORTED (the caller
+    then uses the score kernel and the top-k kernel), bad sizes with FMSA_ERR_ARGUMENT - both before anything touches the device."""
+    lib = _lib.load()
+    t = _lib.FmsaTensor()                    # never dereferenced: the size checks come first
+    out = ctypes.c_void_p(16)
+    big = 129 * 128
+    assert lib.fmsa_select_fused(ctypes.byref(t), ctypes.byref(t), out, 1, 1, 1, big, 65, 0.1, 0, None, None, None) == -2
+    assert lib.fmsa_select_fused(ctypes.byref(t), ctypes.byref(t), out, 1, 1, 1, 1024, 9, 0.1, 0, None, None, None) == -1
+    assert lib.fmsa_select_fused(ctypes.byref(t), ctypes.byref(t), None, 1, 1, 1, 1024, 4, 0.1, 0, None, None, None) == -1
